@@ -1,0 +1,13 @@
+"""A small generation library for the Llama 3 dense decoder on one NVIDIA B200.
+
+Everything between a request's token ids and its next token: typed configuration and
+architecture registry, weights by tensor name, layers put together from parts, a paged
+key/value cache with per-sequence state, one step function, a generation loop, samplers,
+and hand-written sm_100a CUDA kernels underneath.  The GPU is required to run a model;
+describing one (configuration, weight table, cache bookkeeping) needs none.
+"""
+from . import cache, config, engine, parts, weights  # noqa: F401
+from .config import LlamaConfig, load_config, register_architecture
+
+__version__ = "0.1.0"
+__all__ = ["cache", "config", "engine", "parts", "weights", "LlamaConfig", "load_config", "register_architecture"]

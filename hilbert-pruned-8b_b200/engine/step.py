@@ -1,0 +1,141 @@
+"""The step function: a batch of sequences, their next tokens, logits at the wanted places.
+
+``Engine.step`` runs only the tokens it is given, as one packed batch, against the cache
+that earlier steps left, and returns the logits at the wanted places.  The sequences of a
+step may have any lengths and bring any number of tokens each: all prompts of a batch in
+one step, then one token each, is the usual use, and a long prompt may be cut into several
+steps.  It is the batched generalisation of the reference's
+``forward(tokens, n, ids, n_ids, logits)`` on one sequence with a position counter
+(cleanroom-transformer/src/transformer.h:347-364); the checks are the reference's
+(cpu_backend.c:223-228).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence as Seq
+
+import torch
+
+from ..cache.manager import CacheManager, Sequence
+from ..config.registry import load_config
+from ..parts.base import BuildContext
+from ..weights.loader import choose_prefix, folder_names, load_tensors
+from .batch import StepBatch, StepEntry, build_step
+from .model import DecoderModel
+from .workspace import Workspace
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if dtype not in _DTYPES:
+        raise ValueError(f"dtype {dtype!r} is not supported (bfloat16 or float32)")
+    return _DTYPES[dtype]
+
+
+class Engine:
+    """A model on one GPU with its cache: the object every entry point drives."""
+
+    def __init__(self, spec, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
+                 max_step_tokens: Optional[int] = None, max_sequences: Optional[int] = None):
+        from ..kernels import ops  # fails loudly without a GPU toolchain or a built library
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("engine: the model runs on a CUDA device only; there is no CPU path")
+        self.dtype = parse_dtype(dtype)
+        self.spec = spec
+        self.max_tokens = int(max_tokens)
+        self.max_step_tokens = int(max_step_tokens) if max_step_tokens else min(max(self.max_tokens, 64), 8192)
+        torch.cuda.set_device(self.device)
+        self.workspace = Workspace(self.device)
+        self.ctx = BuildContext(device=self.device, dtype=self.dtype, ops=ops.Ops(self.device), workspace=self.workspace,
+                                max_step_tokens=self.max_step_tokens)
+        self.model = DecoderModel(spec, self.ctx)
+        self.cache: Optional[CacheManager] = None
+        self._max_sequences = max_sequences
+        self.stop_token_ids = list(spec.stop_token_ids)
+        self.vocab_size = spec.vocab_size
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0", **kw) -> "Engine":
+        config = load_config(model_dir)
+        eng = cls(config.model_spec(), dtype, max_tokens, device, **kw)
+        eng.config = config
+        names = folder_names(model_dir)
+        prefix = choose_prefix(names, eng.spec.weight_prefixes, eng.model.first_weight_name())
+        table = eng.model.weight_table(prefix)
+        tensors = load_tensors(model_dir, table, eng.dtype, eng.device)
+        eng.model.bind(tensors, prefix)
+        eng._make_cache()
+        return eng
+
+    @classmethod
+    def from_random(cls, config, seed: int, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
+                    std: float = 0.02, norm_std: float = 0.0, fan_in_scale=None, **kw) -> "Engine":
+        """Random weights drawn on the device (no folder is written)."""
+        from ..weights.random_init import random_tensors
+        eng = cls(config.model_spec(), dtype, max_tokens, device, **kw)
+        eng.config = config
+        table = eng.model.weight_table()
+        # one tensor at a time would be kinder to memory; a table's worth is drawn per part
+        tensors = random_tensors(table, seed, eng.device, std, norm_std,
+                                 torch.bfloat16 if eng.dtype == torch.bfloat16 else torch.float32, fan_in_scale)
+        eng.model.bind(tensors)
+        del tensors
+        eng._make_cache()
+        return eng
+
+    def _make_cache(self) -> None:
+        self.cache = CacheManager(self.model.cache_needs(), self.model.state_needs(), self.max_tokens, self.device,
+                                  self.dtype, self._max_sequences)
+
+    # ------------------------------------------------------------------ sequences
+    def open_sequence(self) -> Sequence:
+        return self.cache.open()
+
+    def close_sequence(self, seq: Sequence) -> None:
+        self.cache.close(seq)
+
+    # ------------------------------------------------------------------ the step
+    def check_entries(self, entries: List[StepEntry]) -> None:
+        if not entries:
+            raise ValueError("step: no sequences")
+        total = 0
+        seen = set()
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError("step: no tokens")
+            if id(e.seq) in seen:
+                raise ValueError(f"step: sequence {e.seq.seq_id} appears twice in one step")
+            seen.add(id(e.seq))
+            if not e.seq.open:
+                raise ValueError(f"step: sequence {e.seq.seq_id} is closed")
+            if e.seq.length + n > self.cache.tokens_capacity():
+                raise ValueError(f"step: {e.seq.length + n} tokens exceed context {self.cache.tokens_capacity()}")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise ValueError(f"step: token {int(t)} out of range")
+            total += n
+        if total > self.max_step_tokens:
+            raise ValueError(f"step: {total} tokens exceed the step capacity {self.max_step_tokens}")
+
+    def step(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries' tokens; returns ``[wanted, vocab]`` float32 logits on the device,
+        in the order of the entries and of each entry's ``want`` (None if nothing is wanted).
+        The tensor is engine scratch: it is overwritten by the next step."""
+        self.check_entries(entries)
+        self.cache.reserve([(e.seq, e.seq.length + len(e.tokens)) for e in entries])
+        batch = build_step(entries, self.cache, self.workspace, self.device)
+        logits = self.model.forward(batch, self.cache)
+        for e, new_len in zip(entries, batch.host_len):
+            self.cache.commit(e.seq, new_len)
+        return logits
+
+    # ------------------------------------------------------------------ accounting
+    def decode_step_bytes(self, live_lengths: Seq[int]) -> int:
+        """Bytes a decode step has to read: every weight it uses once and the cache of the
+        live sequences."""
+        kv = sum(int(l) for l in live_lengths) * self.cache.bytes_per_token()
+        return self.model.step_weight_bytes() + kv

@@ -1,0 +1,157 @@
+"""Interfaces and registries of the parts a decoder layer is put together from.
+
+Kinds of part: mixer (attention, or anything else that mixes tokens of a sequence),
+feed-forward, norm, position encoding, block (the arrangement of the four in a layer),
+embedding and head.  Each kind has one registry from a name to a class; a configuration
+chooses parts by name, layer by layer.  No part knows which model it is in: sizes and
+constants arrive as parameters of its ``PartSpec``.
+
+What a part must provide:
+
+* ``params()``: its weight tensors as ``ParamSpec`` rows (name local to the part, shape,
+  kind).  The loader, the random-weights mode and the byte accounting all read this one
+  table, as the reference does with its shape table
+  (cleanroom-transformer/src/shapes.c:12-39, model.c:246-257).
+* ``bind(tensors)``: receives the loaded tensors by local name and may fuse them.
+* mixers: ``cache_need()`` (keys and values per token, or None), ``state_need()``
+  (fixed-size state per sequence, or None) and
+  ``forward(h, residual, step, cache, state, append)`` which ADDS the mixer's output to the
+  32-bit ``residual`` in place.
+* feed-forwards: ``forward(h, residual, step)``, adding likewise.
+* norms: ``forward(x, out, rows=None)``.
+* position encodings: ``prepare(step)`` once per step and whatever ``apply`` its mixer calls.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.spec import PartSpec
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    name: str
+    shape: Tuple[int, ...]
+    kind: str = "matrix"        # "matrix" | "vector" | "int_table"
+    init: str = "normal"        # random-weights mode: "normal" | "ones" | "zeros"
+    absolute: bool = False      # name is not below the decoder's prefix (lm_head.weight)
+    optional: bool = False      # may be absent (and is then not an error)
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """Keys and values a mixer keeps per token: ``window`` None keeps all of them."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Fixed-size state a mixer keeps per sequence (zeroed when a sequence starts)."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class BuildContext:
+    """What parts need to build themselves: device, activation dtype, kernels, scratch."""
+
+    device: torch.device
+    dtype: torch.dtype                      # torch.bfloat16 or torch.float32
+    ops: Any                                # the kernel library (kernels.ops)
+    workspace: Any                          # engine.workspace.Workspace
+    max_step_tokens: int
+    _shared: Dict[str, Any] = None          # parts shared between layers, by spec
+
+    def shared_part(self, registry: "Registry", spec: PartSpec) -> Any:
+        if self._shared is None:
+            self._shared = {}
+        key = registry.kind + ":" + repr(spec)
+        if key not in self._shared:
+            self._shared[key] = registry.build(spec, self)
+        return self._shared[key]
+
+
+class Part:
+    def __init__(self, spec: PartSpec, ctx: BuildContext):
+        self.spec = spec
+        self.ctx = ctx
+
+    def params(self) -> List[ParamSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights a step reads from this part (for roofline accounting)."""
+        return 0
+
+
+class Mixer(Part):
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, h, residual, step, cache, state, append: bool) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h, residual, step) -> None:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    out_dtype: torch.dtype
+
+    def forward(self, x, out, rows=None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def prepare(self, step) -> None:
+        pass
+
+
+class Registry:
+    def __init__(self, kind: str):
+        self.kind = kind
+        self._classes: Dict[str, Callable[..., Any]] = {}
+
+    def register(self, name: str) -> Callable[[Any], Any]:
+        def deco(cls):
+            self._classes[name] = cls
+            return cls
+        return deco
+
+    def unregister(self, name: str) -> None:
+        self._classes.pop(name, None)
+
+    def names(self) -> List[str]:
+        return sorted(self._classes)
+
+    def get(self, name: str) -> Callable[..., Any]:
+        if name not in self._classes:
+            raise KeyError(f"no {self.kind} named {name!r} is registered ({', '.join(self.names())})")
+        return self._classes[name]
+
+    def build(self, spec: PartSpec, ctx: BuildContext) -> Any:
+        return self.get(spec.kind)(spec, ctx)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
