@@ -1,0 +1,39 @@
+// C interface of the kernel library (loaded from Python with ctypes).
+//
+// Conventions: pointers are device pointers unless named host_*; `stream` is a cudaStream_t;
+// dtypes are HbDtype codes (0 = float32, 1 = bfloat16); row-major matrices with explicit row
+// strides in elements; every function returns 0 or sets hb_last_error().
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* hb_last_error(void);
+int hb_device_info(int device, int* sm_major, int* sm_minor, int* sm_count);
+
+int hb_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int hidden,
+             int vocab, void* stream);
+int hb_rmsnorm(const float* x, const float* weight, float eps, float offset, void* out, int out_dtype,
+               const int* rows, int n_rows, int hidden, void* stream);
+int hb_silu_mul(const void* gate_up, int in_dtype, long long in_stride, void* out, int out_dtype,
+                long long out_stride, int n_rows, int inter, void* stream);
+int hb_rope_table(const int* positions, const float* inv_freq, float* out, int n_tokens, int half, void* stream);
+int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride, const float* table, int rot,
+                      int n_heads, int n_kv_heads, int head_dim, void* k_cache, void* v_cache, int cache_dtype,
+                      const int* page_table, int pt_width, const int* tok_seq, const int* positions,
+                      int n_tokens, int append, int n_pages, void* stream);
+int hb_gemm_general(const void* a, int a_dtype, long long lda, const void* w, int w_dtype, long long ldw,
+                    void* out, int out_dtype, long long ldc, int M, int N, int K, int accumulate, void* stream);
+int hb_attention_general(const void* q, int q_dtype, long long q_stride, const void* k_cache, const void* v_cache,
+                         int cache_dtype, const int* page_table, int pt_width, const int* tok_seq,
+                         const int* positions, void* out, int out_dtype, long long out_stride, int n_tokens,
+                         int n_heads, int n_kv_heads, int head_dim, float scale, int window, void* stream);
+int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, void* stream);
+int hb_sample(const float* logits, long long stride, const float* temperature, const long long* seeds,
+              const long long* request_ids, const long long* steps, int* out, int n_rows, int vocab, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,200 @@
+// Embedding gather, RMSNorm, SiLU-multiply, rotary table and rotary + cache append.
+//
+// General-shape kernels: any hidden width, head size and head count.  Formulas follow the
+// reference (file:line cited per kernel, paths within cleanroom-transformer/src/).
+#include "api.h"
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------- embed
+// x[t,:] = float(E[token[t],:])   (cpu_backend.c:236; cuda_backend.cu:66-70)
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out,
+                             int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= vocab) tok = 0;  // the host checked the range; never read outside the table
+    const TW* row = table + (size_t)tok * hidden;
+    float* o = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+extern "C" int hb_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int hidden,
+                        int vocab, void* stream) {
+    if (n_tokens == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == HB_BF16)
+        embed_kernel<bf16><<<n_tokens, 256, 0, s>>>(tokens, (const bf16*)table, out, hidden, vocab);
+    else if (table_dtype == HB_F32)
+        embed_kernel<float><<<n_tokens, 256, 0, s>>>(tokens, (const float*)table, out, hidden, vocab);
+    else
+        return hb_fail("embed: unsupported table dtype %d", table_dtype);
+    return hb_check_launch("embed");
+}
+
+// -------------------------------------------------------------------------------- rmsnorm
+// out = x * (1 / sqrt(mean(x^2) + eps)) * (offset + w), sum of squares in float32
+// (cpu_backend.c:57-62; cuda_backend.cu:73-85).  Row r of `out` is made from row rows[r]
+// of `x` (rows == nullptr: row r).
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, float offset,
+                               TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const float* xr = x + (size_t)src * hidden;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * inv * (offset + w[i]));
+}
+
+extern "C" int hb_rmsnorm(const float* x, const float* weight, float eps, float offset, void* out, int out_dtype,
+                          const int* rows, int n_rows, int hidden, void* stream) {
+    if (n_rows == 0) return 0;
+    HB_REQUIRE(n_rows > 0 && hidden > 0, "rmsnorm: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 2048 ? 512 : 256;
+    if (out_dtype == HB_BF16)
+        rmsnorm_kernel<bf16><<<n_rows, threads, 0, s>>>(x, weight, eps, offset, (bf16*)out, rows, hidden);
+    else if (out_dtype == HB_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>(x, weight, eps, offset, (float*)out, rows, hidden);
+    else
+        return hb_fail("rmsnorm: unsupported output dtype %d", out_dtype);
+    return hb_check_launch("rmsnorm");
+}
+
+// ------------------------------------------------------------------------------- silu_mul
+// out[t,i] = silu(gu[t,i]) * gu[t,inter+i]   (cpu_backend.c:250; cuda_backend.cu:413-416)
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, long long in_stride, TO* __restrict__ out,
+                                long long out_stride, int inter) {
+    const int t = blockIdx.x;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    const TI* row = gu + (size_t)t * in_stride;
+    out[(size_t)t * out_stride + i] = from_f32<TO>(silu_f32(to_f32(row[i])) * to_f32(row[inter + i]));
+}
+
+extern "C" int hb_silu_mul(const void* gate_up, int in_dtype, long long in_stride, void* out, int out_dtype,
+                           long long out_stride, int n_rows, int inter, void* stream) {
+    if (n_rows == 0) return 0;
+    HB_REQUIRE(n_rows > 0 && inter > 0, "silu_mul: bad sizes");
+    HB_REQUIRE((inter + 255) / 256 <= 65535, "silu_mul: intermediate size %d is too large", inter);
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_rows, (inter + 255) / 256);
+    if (in_dtype == HB_BF16 && out_dtype == HB_BF16)
+        silu_mul_kernel<bf16, bf16><<<grid, 256, 0, s>>>((const bf16*)gate_up, in_stride, (bf16*)out, out_stride, inter);
+    else if (in_dtype == HB_F32 && out_dtype == HB_F32)
+        silu_mul_kernel<float, float><<<grid, 256, 0, s>>>((const float*)gate_up, in_stride, (float*)out, out_stride, inter);
+    else if (in_dtype == HB_F32 && out_dtype == HB_BF16)
+        silu_mul_kernel<float, bf16><<<grid, 256, 0, s>>>((const float*)gate_up, in_stride, (bf16*)out, out_stride, inter);
+    else
+        return hb_fail("silu_mul: unsupported dtypes %d -> %d", in_dtype, out_dtype);
+    return hb_check_launch("silu_mul");
+}
+
+// ----------------------------------------------------------------------------- rope table
+// out[t,i] = (cos, sin)(inv_freq[i] * float(position[t])), the angle a float32 product
+// (cpu_backend.c:88-93; cuda_backend.cu:232-236).
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ out, int n_tokens, int half) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tokens * half) return;
+    const int t = idx / half, i = idx - t * half;
+    const float a = __fmul_rn(inv_freq[i], (float)positions[t]);
+    float sn, cs;
+    sincosf(a, &sn, &cs);
+    out[idx] = make_float2(cs, sn);
+}
+
+extern "C" int hb_rope_table(const int* positions, const float* inv_freq, float* out, int n_tokens, int half,
+                             void* stream) {
+    if (n_tokens == 0 || half == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && half > 0, "rope_table: bad sizes");
+    const long long n = (long long)n_tokens * half;
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, (float2*)out,
+                                                                                   n_tokens, half);
+    return hb_check_launch("rope_table");
+}
+
+// --------------------------------------------------------------------- rope + cache append
+// One block per (token, head slot).  Slots 0..nh-1 are the query heads (rotated in place),
+// nh..nh+nkv-1 the key heads (rotated, written to the cache row of the token's position),
+// the rest the value heads (copied to the cache).  Rotation pairs (i, i + rot/2); dims
+// beyond `rot` pass through (cpu_backend.c:87-100; cuda_backend.cu:212-249).
+template <typename T, typename TC>
+__global__ void rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table,
+                                      int rot, int nh, int nkv, int hd, TC* __restrict__ k_cache,
+                                      TC* __restrict__ v_cache, const int* __restrict__ page_table, int pt_width,
+                                      const int* __restrict__ tok_seq, const int* __restrict__ positions,
+                                      int n_pages) {
+    const int t = blockIdx.x, slot = blockIdx.y;
+    const int half = rot >> 1;
+    T* row = qkv + (size_t)t * qkv_stride;
+    if (slot < nh) {
+        T* x = row + (size_t)slot * hd;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float2 cs = table[(size_t)t * half + i];
+            const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
+            x[i] = from_f32<T>(x1 * cs.x - x2 * cs.y);
+            x[i + half] = from_f32<T>(x2 * cs.x + x1 * cs.y);
+        }
+        return;
+    }
+    const int pos = positions[t];
+    const int page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
+    if (page < 0 || page >= n_pages) return;  // the host reserved the pages; never write outside the cache
+    if (slot < nh + nkv) {
+        const int g = slot - nh;
+        const T* x = row + (size_t)(nh + g) * hd;
+        TC* dst = k_cache + cache_offset(page, g, pos, nkv, hd);
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float2 cs = table[(size_t)t * half + i];
+            const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
+            dst[i] = from_f32<TC>(x1 * cs.x - x2 * cs.y);
+            dst[i + half] = from_f32<TC>(x2 * cs.x + x1 * cs.y);
+        }
+        for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = from_f32<TC>(to_f32(x[i]));
+    } else {
+        const int g = slot - nh - nkv;
+        const T* x = row + (size_t)(nh + nkv + g) * hd;
+        TC* dst = v_cache + cache_offset(page, g, pos, nkv, hd);
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = from_f32<TC>(to_f32(x[i]));
+    }
+}
+
+extern "C" int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride, const float* table, int rot,
+                                 int n_heads, int n_kv_heads, int head_dim, void* k_cache, void* v_cache,
+                                 int cache_dtype, const int* page_table, int pt_width, const int* tok_seq,
+                                 const int* positions, int n_tokens, int append, int n_pages, void* stream) {
+    if (n_tokens == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0, "rope_kv_append: bad sizes");
+    HB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0, "rope_kv_append: rotary size %d does not fit head size %d",
+               rot, head_dim);
+    HB_REQUIRE(rot == 0 || table != nullptr, "rope_kv_append: no rotary table");
+    const int slots = append ? n_heads + 2 * n_kv_heads : n_heads;
+    HB_REQUIRE(slots <= 65535, "rope_kv_append: too many heads");
+    if (rot == 0 && !append) return 0;
+    dim3 grid(n_tokens, slots);
+    const int threads = head_dim >= 128 ? 64 : 32;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float2* tab = (const float2*)table;
+    if (qkv_dtype == HB_BF16 && cache_dtype == HB_BF16)
+        rope_kv_append_kernel<bf16, bf16><<<grid, threads, 0, s>>>((bf16*)qkv, qkv_stride, tab, rot, n_heads, n_kv_heads,
+                                                                    head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table,
+                                                                    pt_width, tok_seq, positions, n_pages);
+    else if (qkv_dtype == HB_F32 && cache_dtype == HB_F32)
+        rope_kv_append_kernel<float, float><<<grid, threads, 0, s>>>((float*)qkv, qkv_stride, tab, rot, n_heads,
+                                                                      n_kv_heads, head_dim, (float*)k_cache,
+                                                                      (float*)v_cache, page_table, pt_width, tok_seq,
+                                                                      positions, n_pages);
+    else
+        return hb_fail("rope_kv_append: unsupported dtypes qkv %d cache %d", qkv_dtype, cache_dtype);
+    return hb_check_launch("rope_kv_append");
+}

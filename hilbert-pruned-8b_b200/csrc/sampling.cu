@@ -1,0 +1,142 @@
+// Sampling on the device: greedy (largest logit, lowest index on ties) and temperature
+// sampling by inverse CDF.  The reference samples nothing (it reads option logits and
+// takes a softmax over them, cleanroom-transformer/src/engine.c:8-14); both samplers are
+// this library's own.
+//
+// Temperature sampling: p = softmax(logits / T) in float32; a uniform u in [0,1) is derived
+// from (seed, request id, step) by a 64-bit mixing function, so a request's draw does not
+// depend on what else is in the batch; the token is the first index whose cumulative
+// probability exceeds u.  Rows whose temperature is <= 0 are taken greedily.
+#include "api.h"
+#include "common.cuh"
+
+#define SM_THREADS 1024
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    return z ^ (z >> 31);
+}
+
+// 24-bit uniform in [0, 1) from (seed, request, step)
+__device__ __forceinline__ float uniform_from(long long seed, long long request, long long step) {
+    unsigned long long z = (unsigned long long)seed * 0x9E3779B97F4A7C15ULL +
+                           (unsigned long long)request * 0xBF58476D1CE4E5B9ULL +
+                           (unsigned long long)step * 0x94D049BB133111EBULL + 0x2545F4914F6CDD1DULL;
+    z = mix64(mix64(z));
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+__device__ __forceinline__ void argmax_row(const float* __restrict__ row, int vocab, int* out_idx, float* out_max,
+                                           float* sval, int* sidx) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    // a NaN never compares greater: a row of NaNs yields index 0x7fffffff, mapped to 0 below
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) { sval[warp] = best; sidx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < nwarp ? sval[lane] : -INFINITY;
+        bi = lane < nwarp ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) { sval[32] = best; sidx[32] = (bi == 0x7fffffff) ? 0 : bi; }
+    }
+    __syncthreads();
+    *out_idx = sidx[32];
+    *out_max = sval[32];
+}
+
+__global__ void __launch_bounds__(SM_THREADS)
+argmax_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ out, int vocab) {
+    __shared__ float sval[33];
+    __shared__ int sidx[33];
+    int idx;
+    float mx;
+    argmax_row(logits + (size_t)blockIdx.x * stride, vocab, &idx, &mx, sval, sidx);
+    if (threadIdx.x == 0) out[blockIdx.x] = idx;
+}
+
+__global__ void __launch_bounds__(SM_THREADS)
+sample_kernel(const float* __restrict__ logits, long long stride, const float* __restrict__ temperature,
+              const long long* __restrict__ seeds, const long long* __restrict__ request_ids,
+              const long long* __restrict__ steps, int* __restrict__ out, int vocab) {
+    __shared__ float sval[33];
+    __shared__ int sidx[33];
+    __shared__ float prefix[SM_THREADS];
+    __shared__ int chosen;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)r * stride;
+    int amax;
+    float mx;
+    argmax_row(row, vocab, &amax, &mx, sval, sidx);
+    const float temp = temperature[r];
+    if (!(temp > 0.0f)) {
+        if (tid == 0) out[r] = amax;
+        return;
+    }
+    const float inv_t = 1.0f / temp;
+    // each thread owns a contiguous chunk so that the cumulative sum runs in index order
+    const int chunk = (vocab + SM_THREADS - 1) / SM_THREADS;
+    const int begin = min(tid * chunk, vocab), end = min(begin + chunk, vocab);
+    float part = 0.0f;
+    for (int i = begin; i < end; i++) part += expf((row[i] - mx) * inv_t);
+    // inclusive scan of the per-thread sums (Hillis-Steele over shared memory)
+    prefix[tid] = part;
+    __syncthreads();
+    for (int o = 1; o < SM_THREADS; o <<= 1) {
+        const float add = tid >= o ? prefix[tid - o] : 0.0f;
+        __syncthreads();
+        prefix[tid] += add;
+        __syncthreads();
+    }
+    const float total = prefix[SM_THREADS - 1];
+    const float u = uniform_from(seeds[r], request_ids[r], steps[r]);
+    const float target = u * total;
+    if (tid == 0) chosen = 0x7fffffff;
+    __syncthreads();
+    const float incl = prefix[tid], excl = tid > 0 ? prefix[tid - 1] : 0.0f;
+    if (begin < end && target >= excl && target < incl) {
+        float run = excl;
+        int pick = end - 1;
+        for (int i = begin; i < end; i++) {
+            run += expf((row[i] - mx) * inv_t);
+            if (run > target) { pick = i; break; }
+        }
+        atomicMin(&chosen, pick);
+    }
+    __syncthreads();
+    if (tid == 0) out[r] = (chosen == 0x7fffffff) ? amax : chosen;  // rounding left no interval: the mode
+}
+
+extern "C" int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, void* stream) {
+    if (n_rows == 0) return 0;
+    HB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
+    argmax_kernel<<<n_rows, SM_THREADS, 0, (cudaStream_t)stream>>>(logits, stride, out, vocab);
+    return hb_check_launch("argmax");
+}
+
+extern "C" int hb_sample(const float* logits, long long stride, const float* temperature, const long long* seeds,
+                         const long long* request_ids, const long long* steps, int* out, int n_rows, int vocab,
+                         void* stream) {
+    if (n_rows == 0) return 0;
+    HB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "sample: bad sizes");
+    sample_kernel<<<n_rows, SM_THREADS, 0, (cudaStream_t)stream>>>(logits, stride, temperature, seeds, request_ids,
+                                                                   steps, out, vocab);
+    return hb_check_launch("sample");
+}

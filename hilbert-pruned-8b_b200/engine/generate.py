@@ -1,0 +1,179 @@
+"""The generation loop above the step function.
+
+Requests (token-id prompts) are served in batches that start together: a batch's prompts
+run in one step (cut into several if they exceed the step capacity), then every live
+sequence gets one token per step.  A sequence ends at a stop token, at its token budget or
+when the context is full; it then leaves the batch and its cache pages and slot are given
+back at once.  No request joins a running batch; when the batch is empty the next one
+starts, reusing the slots.  The reference has no generation at all
+(cleanroom-transformer/README.md:7-10): the loop, its admission rule and its stopping rules
+are this library's own.
+
+Admission: a batch takes the next requests in order while their worst-case page needs
+(prompt plus token budget, rounded up to pages) fit the cache and the batch size limit,
+so a running batch can never run out of cache.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+from ..cache.manager import PAGE_TOKENS, pages_for
+from ..sampling.sampler import SamplingParams
+from .batch import StepEntry
+
+
+@dataclass
+class GenerationRequest:
+    prompt: Sequence[int]
+    max_new_tokens: int = 16
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_token_ids: Optional[Sequence[int]] = None   # None: the model's own (eos_token_id)
+    request_id: Optional[int] = None                 # None: position in the call
+
+
+@dataclass
+class GenerationResult:
+    request_id: int
+    tokens: List[int]
+    finish_reason: str          # "stop" | "length" | "context"
+    prompt_tokens: int
+
+
+@dataclass
+class GenerationStats:
+    batches: int = 0
+    prefill_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_tokens: int = 0
+    decode_steps: int = 0
+    decode_seconds: float = 0.0
+
+
+def plan_batch(costs: Sequence[int], pages_free: int, max_batch: int) -> int:
+    """How many of the next requests (page costs in order) start together.  At least one
+    request is taken if it fits at all; a request that can never fit raises."""
+    n, used = 0, 0
+    for c in costs:
+        if n >= max_batch or used + c > pages_free:
+            break
+        used += c
+        n += 1
+    if n == 0 and costs:
+        raise ValueError(f"generate: a request needs {costs[0]} cache pages of {PAGE_TOKENS} tokens, "
+                         f"only {pages_free} exist")
+    return n
+
+
+def finish_reason(token: int, produced: int, budget: int, length: int, context: int,
+                  stop_ids: Sequence[int]) -> Optional[str]:
+    """Why a sequence ends after producing ``token`` (None: it goes on).  ``length`` is the
+    number of tokens its cache holds once the new token is fed."""
+    if token in stop_ids:
+        return "stop"
+    if produced >= budget:
+        return "length"
+    if length + 1 > context:
+        return "context"
+    return None
+
+
+class Generator:
+    """Drives ``engine`` (anything with open_sequence/close_sequence/step and a cache) and
+    ``sampler`` (``sample(logits, temperatures, seeds, request_ids, steps) -> tokens``)."""
+
+    def __init__(self, engine, sampler, max_batch: int = 64, synchronize=None):
+        self.engine = engine
+        self.sampler = sampler
+        self.max_batch = max_batch
+        self.stats = GenerationStats()
+        self._sync = synchronize or (lambda: None)
+
+    # a request may use the whole context: prompt + budget tokens, the last one never fed
+    def _cost(self, req: GenerationRequest) -> int:
+        return pages_for(min(len(req.prompt) + req.max_new_tokens, self._context()))
+
+    def _context(self) -> int:
+        return self.engine.cache.tokens_capacity()
+
+    def generate(self, requests: Sequence[GenerationRequest]) -> List[GenerationResult]:
+        reqs = list(requests)
+        for i, r in enumerate(reqs):
+            if len(r.prompt) == 0:
+                raise ValueError(f"generate: request {i} has an empty prompt")
+            if len(r.prompt) > self._context():
+                raise ValueError(f"generate: request {i} has {len(r.prompt)} prompt tokens, context is {self._context()}")
+            if r.max_new_tokens < 0:
+                raise ValueError(f"generate: request {i} has a negative token budget")
+        results: List[Optional[GenerationResult]] = [None] * len(reqs)
+        nxt = 0
+        while nxt < len(reqs):
+            free = min(self.engine.cache.pages_free()) if self.engine.cache.groups else 1 << 30
+            n = plan_batch([self._cost(r) for r in reqs[nxt:nxt + self.max_batch]], free, self.max_batch)
+            self._run_batch(reqs, list(range(nxt, nxt + n)), results)
+            nxt += n
+        return [r for r in results if r is not None]
+
+    def _run_batch(self, reqs, idxs: List[int], results) -> None:
+        eng = self.engine
+        self.stats.batches += 1
+        live: Dict[int, dict] = {}
+        for i in idxs:
+            r = reqs[i]
+            rid = r.request_id if r.request_id is not None else i
+            stop = list(r.stop_token_ids) if r.stop_token_ids is not None else list(getattr(eng, "stop_token_ids", []))
+            if r.max_new_tokens == 0:
+                results[i] = GenerationResult(rid, [], "length", len(r.prompt))
+                continue
+            live[i] = {"req": r, "rid": rid, "stop": stop, "seq": eng.open_sequence(), "out": [], "next": None}
+        if not live:
+            return
+        try:
+            # all prompts in one step; each sequence wants the logits of its last prompt token
+            self._sync()
+            t0 = time.perf_counter()
+            order = list(live)
+            entries = [StepEntry(live[i]["seq"], list(live[i]["req"].prompt), [len(live[i]["req"].prompt) - 1])
+                       for i in order]
+            logits = eng.step_chunked(entries) if hasattr(eng, "step_chunked") else eng.step(entries)
+            toks = self._sample(logits, [live[i] for i in order], step_no=0)
+            self._sync()
+            self.stats.prefill_seconds += time.perf_counter() - t0
+            self.stats.prefill_tokens += sum(len(live[i]["req"].prompt) for i in order)
+            self._take(order, toks, live, results)
+            step_no = 1
+            while live:
+                t0 = time.perf_counter()
+                order = list(live)
+                entries = [StepEntry(live[i]["seq"], [live[i]["next"]], [0]) for i in order]
+                logits = eng.step(entries)
+                toks = self._sample(logits, [live[i] for i in order], step_no)
+                self.stats.decode_steps += 1
+                self.stats.decode_tokens += len(order)
+                self._take(order, toks, live, results)
+                self.stats.decode_seconds += time.perf_counter() - t0
+                step_no += 1
+        finally:
+            for st in live.values():
+                if st["seq"].open:
+                    eng.close_sequence(st["seq"])
+
+    def _sample(self, logits, states, step_no: int) -> List[int]:
+        toks = self.sampler.sample(logits, [s["req"].sampling.temperature for s in states],
+                                   [s["req"].sampling.seed for s in states], [s["rid"] for s in states],
+                                   [step_no] * len(states))
+        return [int(t) for t in (toks.tolist() if hasattr(toks, "tolist") else toks)]
+
+    def _take(self, order, toks, live, results) -> None:
+        """Books each sequence's new token and retires the sequences that end with it."""
+        for i, tok in zip(order, toks):
+            st = live[i]
+            st["out"].append(tok)
+            st["next"] = tok
+            why = finish_reason(tok, len(st["out"]), st["req"].max_new_tokens, st["seq"].length, self._context(),
+                                st["stop"])
+            if why is not None:
+                results[i] = GenerationResult(st["rid"], st["out"], why, len(st["req"].prompt))
+                self.engine.close_sequence(st["seq"])
+                del live[i]

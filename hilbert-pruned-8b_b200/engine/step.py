@@ -133,6 +133,44 @@ class Engine:
             self.cache.commit(e.seq, new_len)
         return logits
 
+    def step_chunked(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+        """``step`` for any number of tokens: a step larger than the step capacity is cut into
+        several, each sequence's tokens staying in order.  The logits come back in the order
+        of the entries and of each entry's ``want``, in a tensor of their own."""
+        total = sum(len(e.tokens) for e in entries)
+        if total <= self.max_step_tokens:
+            logits = self.step(entries)
+            return logits
+        self.check_entries([StepEntry(e.seq, e.tokens[:1], ()) for e in entries])
+        # row of each wanted place in the result
+        rows, r = [], 0
+        for e in entries:
+            rows.append({int(w): r + k for k, w in enumerate(e.want)})
+            if len(rows[-1]) != len(e.want):
+                raise ValueError("step: a place is wanted twice")
+            r += len(e.want)
+        result = torch.empty((r, self.vocab_size), dtype=torch.float32, device=self.device) if r else None
+        done = [0] * len(entries)
+        while any(done[i] < len(e.tokens) for i, e in enumerate(entries)):
+            room = self.max_step_tokens
+            sub: List[StepEntry] = []
+            dest: List[int] = []
+            for i, e in enumerate(entries):
+                left = len(e.tokens) - done[i]
+                if left == 0 or room == 0:
+                    continue
+                n = min(left, room)
+                lo = done[i]
+                wants = sorted(w for w in rows[i] if lo <= w < lo + n)
+                sub.append(StepEntry(e.seq, e.tokens[lo:lo + n], [w - lo for w in wants]))
+                dest.extend(rows[i][w] for w in wants)
+                done[i] += n
+                room -= n
+            logits = self.step(sub)
+            if dest:
+                result.index_copy_(0, torch.tensor(dest, dtype=torch.long, device=self.device), logits)
+        return result
+
     # ------------------------------------------------------------------ accounting
     def decode_step_bytes(self, live_lengths: Seq[int]) -> int:
         """Bytes a decode step has to read: every weight it uses once and the cache of the

@@ -1,0 +1,243 @@
+"""Python face of the CUDA kernel library: argument checks, dispatch, ctypes calls.
+
+Every op runs a hand-written kernel on the current CUDA stream of ``torch``; torch itself
+only owns the memory.  There is no CPU path and no library fallback: a missing library is
+built on first use, and a failure to build or load it raises.
+
+Dispatch rule for matrix products: the tensor-core kernel where its conditions hold
+(bfloat16 operands, 16-byte aligned rows), else the general FP32-pipe kernel, which takes
+every shape and dtype mix.  A kernel that cannot take a size refuses it with an error that
+names the size; no op returns a wrong result for an odd size.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+_SIGNATURES = {
+    "hb_device_info": [_c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
+    "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_rmsnorm": [_c_ptr, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
+    "hb_silu_mul": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
+    "hb_rope_table": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "hb_rope_kv_append": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
+                          _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_gemm_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
+                        _c_int, _c_ptr],
+    "hb_attention_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                             _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
+    "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
+    "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+}
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def load_library():
+    """Loads (building first if needed) the kernel library; raises if that is impossible."""
+    global _lib
+    if _lib is None:
+        path = build.library_path()
+        lib = ctypes.CDLL(path)
+        lib.hb_last_error.restype = ctypes.c_char_p
+        lib.hb_last_error.argtypes = []
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _c_int
+        _lib = lib
+    return _lib
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels") from None
+
+
+def _rows(t: torch.Tensor, what: str) -> int:
+    """Row stride of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{what}: expected a 2-D tensor with contiguous rows, got shape {tuple(t.shape)} "
+                          f"strides {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+class Ops:
+    """The kernels bound to one device."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KernelError("the kernels run on a CUDA device only")
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is available; the library has no CPU path")
+        self.lib = load_library()
+        major, minor, sms = _c_int(), _c_int(), _c_int()
+        idx = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._call("hb_device_info", idx, ctypes.byref(major), ctypes.byref(minor), ctypes.byref(sms))
+        self.sm = (major.value, minor.value)
+        self.sm_count = sms.value
+        if major.value != 10:
+            raise KernelError(f"the kernels are built for sm_100a; device {idx} is sm_{major.value}{minor.value}")
+        self.launches = 0  # kernels launched through this object (a claim bench.py reports)
+
+    # ------------------------------------------------------------------ plumbing
+    def _call(self, name: str, *args) -> None:
+        rc = getattr(self.lib, name)(*args)
+        if rc != 0:
+            raise KernelError(self.lib.hb_last_error().decode("utf-8", "replace"))
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _dev(self, *tensors) -> None:
+        for t in tensors:
+            if t is not None and t.device != self.device:
+                raise KernelError(f"tensor on {t.device}, kernels bound to {self.device}")
+
+    # ------------------------------------------------------------------ elementwise
+    def embed(self, tokens, table, out) -> None:
+        self._dev(tokens, table, out)
+        if tokens.dtype != torch.int32 or out.dtype != torch.float32 or not out.is_contiguous() \
+                or not table.is_contiguous():
+            raise KernelError("embed: tokens int32, contiguous table, contiguous float32 output expected")
+        T, H = out.shape
+        if table.shape[1] != H or tokens.numel() != T:
+            raise KernelError("embed: shapes do not agree")
+        self._call("hb_embed", tokens.data_ptr(), table.data_ptr(), _code(table), out.data_ptr(), T, H,
+                   table.shape[0], self._stream())
+        self.launches += 1
+
+    def rmsnorm(self, x, weight, eps: float, offset: float, out, rows=None) -> None:
+        self._dev(x, weight, out, rows)
+        if x.dtype != torch.float32 or weight.dtype != torch.float32 or not x.is_contiguous() \
+                or not out.is_contiguous() or not weight.is_contiguous():
+            raise KernelError("rmsnorm: contiguous float32 input and weight, contiguous output expected")
+        H = x.shape[1]
+        n = out.shape[0]
+        if out.shape[1] != H or weight.numel() != H:
+            raise KernelError("rmsnorm: shapes do not agree")
+        if rows is None:
+            if n != x.shape[0]:
+                raise KernelError("rmsnorm: output rows differ from input rows")
+            rp = None
+        else:
+            if rows.dtype != torch.int32 or rows.numel() != n:
+                raise KernelError("rmsnorm: rows must be int32, one per output row")
+            rp = rows.data_ptr()
+        self._call("hb_rmsnorm", x.data_ptr(), weight.data_ptr(), float(eps), float(offset), out.data_ptr(), _code(out),
+                   rp, n, H, self._stream())
+        self.launches += 1
+
+    def silu_mul(self, gate_up, out) -> None:
+        self._dev(gate_up, out)
+        inter = out.shape[1]
+        if gate_up.shape[1] != 2 * inter or gate_up.shape[0] != out.shape[0]:
+            raise KernelError("silu_mul: input must be [rows, 2 * inter]")
+        self._call("hb_silu_mul", gate_up.data_ptr(), _code(gate_up), _rows(gate_up, "silu_mul input"), out.data_ptr(),
+                   _code(out), _rows(out, "silu_mul output"), out.shape[0], inter, self._stream())
+        self.launches += 1
+
+    def rope_table(self, positions, inv_freq, out) -> None:
+        self._dev(positions, inv_freq, out)
+        T, half = out.shape[0], out.shape[1]
+        if positions.dtype != torch.int32 or positions.numel() != T or inv_freq.dtype != torch.float32 \
+                or inv_freq.numel() != half or out.dtype != torch.float32 or not out.is_contiguous() \
+                or out.shape[2] != 2:
+            raise KernelError("rope_table: shapes or dtypes do not agree")
+        self._call("hb_rope_table", positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), T, half, self._stream())
+        self.launches += 1
+
+    def rope_kv_append(self, qkv, table, rot: int, heads: int, kv_heads: int, head_dim: int, cache, step,
+                       append: bool) -> None:
+        self._dev(qkv, table, cache.k, cache.v)
+        T = qkv.shape[0]
+        need = (heads + (2 * kv_heads if append else 0)) * head_dim
+        if qkv.shape[1] < need:
+            raise KernelError("rope_kv_append: qkv rows are too short")
+        pt = step.page_tables[cache.group]
+        if rot and (table is None or table.shape[0] != T or table.shape[1] != rot // 2):
+            raise KernelError("rope_kv_append: rotary table does not match the tokens")
+        if cache.k.dtype != cache.v.dtype or not cache.k.is_contiguous() or not cache.v.is_contiguous():
+            raise KernelError("rope_kv_append: cache layers must be contiguous and of one dtype")
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim):
+            raise KernelError(f"rope_kv_append: cache layer shape {tuple(cache.k.shape)} does not match "
+                              f"{kv_heads} kv heads of size {head_dim}")
+        self._call("hb_rope_kv_append", qkv.data_ptr(), _code(qkv), _rows(qkv, "qkv"),
+                   table.data_ptr() if rot else None, rot, heads, kv_heads, head_dim, cache.k.data_ptr(),
+                   cache.v.data_ptr(), _code(cache.k), pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(),
+                   step.positions.data_ptr(), T, 1 if append else 0, cache.k.shape[0], self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ matrix products
+    def linear(self, a, w, out, accumulate: bool = False) -> None:
+        """``out[M,N] (+)= a[M,K] @ w[N,K]^T`` with float32 accumulation."""
+        self._dev(a, w, out)
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N):
+            raise KernelError(f"linear: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
+        self._call("hb_gemm_general", a.data_ptr(), _code(a), _rows(a, "linear input"), w.data_ptr(), _code(w),
+                   _rows(w, "linear weight"), out.data_ptr(), _code(out), _rows(out, "linear output"), M, N, K,
+                   1 if accumulate else 0, self._stream())
+        self.launches += 1
+
+    def linear_swiglu(self, h, w_gate_up, act, workspace, cap: int) -> None:
+        """``act = silu(h Wg^T) * (h Wu^T)`` with ``w_gate_up = [Wg; Wu]``."""
+        T = h.shape[0]
+        inter = act.shape[1]
+        gu = workspace.buffer("swiglu.gate_up", (cap, 2 * inter), torch.float32 if act.dtype == torch.float32
+                              else torch.bfloat16)[:T]
+        self.linear(h, w_gate_up, gu)
+        self.silu_mul(gu, act)
+
+    # ------------------------------------------------------------------ attention
+    def attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out, scale: float,
+                  window: Optional[int]) -> None:
+        """Causal attention of the step's tokens over the cache; queries are the first
+        ``heads * head_dim`` columns of ``qkv``."""
+        self._dev(qkv, cache.k, cache.v, out)
+        T = qkv.shape[0]
+        pt = step.page_tables[cache.group]
+        if out.shape[0] != T or out.shape[1] != heads * head_dim:
+            raise KernelError("attention: output shape does not match")
+        self._call("hb_attention_general", qkv.data_ptr(), _code(qkv), _rows(qkv, "attention queries"),
+                   cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k), pt.data_ptr(), pt.shape[1],
+                   step.tok_seq.data_ptr(), step.positions.data_ptr(), out.data_ptr(), _code(out),
+                   _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale),
+                   int(window) if window else 0, self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ sampling
+    def argmax(self, logits, out) -> None:
+        self._dev(logits, out)
+        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() != logits.shape[0]:
+            raise KernelError("argmax: float32 logits and one int32 per row expected")
+        self._call("hb_argmax", logits.data_ptr(), _rows(logits, "logits"), out.data_ptr(), logits.shape[0],
+                   logits.shape[1], self._stream())
+        self.launches += 1
+
+    def sample(self, logits, temperature, seeds, request_ids, steps, out) -> None:
+        self._dev(logits, temperature, seeds, request_ids, steps, out)
+        n = logits.shape[0]
+        if logits.dtype != torch.float32 or out.dtype != torch.int32 or temperature.dtype != torch.float32 \
+                or any(t.dtype != torch.int64 for t in (seeds, request_ids, steps)) \
+                or any(t.numel() != n for t in (temperature, seeds, request_ids, steps, out)):
+            raise KernelError("sample: float32 logits/temperature, int64 seeds/requests/steps, int32 output, "
+                              "one of each per row expected")
+        self._call("hb_sample", logits.data_ptr(), _rows(logits, "logits"), temperature.data_ptr(), seeds.data_ptr(),
+                   request_ids.data_ptr(), steps.data_ptr(), out.data_ptr(), n, logits.shape[1], self._stream())
+        self.launches += 1

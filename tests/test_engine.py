@@ -1,0 +1,109 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16: whole requests,
+the last 32 tokens one by one, batches of unequal lengths with slot reuse, long decoding
+and the first tokens of a sequence."""
+import pytest
+import torch
+
+import trace_tools as tt
+from conftest import TINY_A, TINY_B, require_gpu
+from plain_llama import PlainLlama
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+MODELS = ["strong_a", "strong_b", "paper_a", "paper_b"]
+VOCAB = {"a": TINY_A["vocab_size"], "b": TINY_B["vocab_size"]}
+
+
+def _plain(folder, dtype):
+    return PlainLlama(folder, round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+
+
+def _engine(folder, dtype, max_tokens, **kw):
+    from hilbert_pruned_8b_b200.engine.step import Engine
+    return Engine.from_folder(folder, dtype, max_tokens=max_tokens, **kw)
+
+
+def _requests(model, lengths, seed):
+    v = VOCAB[model[-1]]
+    return {f"r{i}": tt.random_tokens(n, v, seed + i) for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("model", MODELS)
+def test_whole_requests(model_folders, model, dtype):
+    require_gpu()
+    reqs = _requests(model, [1, 7, 40, 70], seed=100)
+    steps, peak = tt.trace_whole(reqs)
+    eng = _engine(model_folders[model], dtype, peak)
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "whole")
+    assert min(eng.cache.pages_free()) == eng.cache.num_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("model", ["strong_a", "strong_b"])
+def test_last_tokens_one_by_one(model_folders, model, dtype):
+    require_gpu()
+    reqs = _requests(model, [33, 70, 100], seed=200)
+    steps, peak = tt.trace_tail(reqs, tail=32)
+    eng = _engine(model_folders[model], dtype, peak)
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "tail")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("model", ["strong_a", "strong_b"])
+def test_unequal_batches_with_slot_reuse(model_folders, model, dtype):
+    require_gpu()
+    v = VOCAB[model[-1]]
+    # (total tokens, prompt length): shorter requests end earlier; three batches in a row
+    shapes = [[(9, 1), (15, 7), (24, 16)], [(21, 5), (28, 12), (49, 33), (80, 64)], [(70, 66), (3, 3), (66, 2)]]
+    batches, reqs = [], {}
+    for b, group in enumerate(shapes):
+        batch = {}
+        for i, (n, p) in enumerate(group):
+            rid = f"b{b}r{i}"
+            reqs[rid] = tt.random_tokens(n, v, 300 + 10 * b + i)
+            batch[rid] = (reqs[rid], p)
+        batches.append(batch)
+    steps, peak = tt.trace_batches(batches)
+    eng = _engine(model_folders[model], dtype, peak)
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "batches")
+    assert min(eng.cache.pages_free()) == eng.cache.num_pages and eng.cache.slots.num_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_across_pages(model_folders, dtype):
+    require_gpu()
+    model = "strong_b"
+    reqs = _requests(model, [200], seed=400)
+    steps, peak = tt.trace_tail(reqs, tail=190)
+    eng = _engine(model_folders[model], dtype, peak)
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("model", ["strong_a", "strong_b"])
+def test_first_tokens(model_folders, model, dtype):
+    require_gpu()
+    reqs = _requests(model, [4, 2], seed=500)
+    steps, peak = tt.trace_tail(reqs, tail=3)     # one token, then one by one
+    eng = _engine(model_folders[model], dtype, peak)
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_step_cut_into_chunks(model_folders, dtype):
+    """A step larger than the step capacity is cut; the logits are those of the uncut step."""
+    require_gpu()
+    model = "strong_a"
+    reqs = _requests(model, [50, 21, 90], seed=600)
+    batch = {rid: (t, len(t)) for rid, t in reqs.items()}
+    steps, peak = tt.trace_batches([batch])
+    eng = _engine(model_folders[model], dtype, peak, max_step_tokens=32)
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "chunked")
