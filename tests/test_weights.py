@@ -1,0 +1,128 @@
+"""Weight loading by name, its one error, dtype rules, and the random-weights mode (no GPU)."""
+import json
+import os
+
+import pytest
+import torch
+
+import hilbert_pruned_8b_b200 as hb
+from conftest import TINY_A, TINY_B
+from hilbert_pruned_8b_b200.engine.model import weight_table
+from hilbert_pruned_8b_b200.weights import (SafetensorsError, SafetensorsFolder, WeightError, choose_prefix,
+                                            load_tensors, random_tensors, write_random_model, write_safetensors)
+
+CPU = torch.device("cpu")
+
+
+def _table(cfg):
+    return weight_table(hb.LlamaConfig.from_dict(cfg).model_spec())
+
+
+def test_table_names_and_shapes_follow_the_reference():
+    t = _table(TINY_B)
+    assert t["model.embed_tokens.weight"].shape == (384, 160)
+    assert t["model.layers.2.self_attn.q_proj.weight"].shape == (5 * 32, 160)
+    assert t["model.layers.0.self_attn.k_proj.weight"].shape == (1 * 32, 160)
+    assert t["model.layers.0.self_attn.o_proj.weight"].shape == (160, 5 * 32)
+    assert t["model.layers.1.mlp.gate_proj.weight"].shape == (416, 160)
+    assert t["model.layers.1.mlp.down_proj.weight"].shape == (160, 416)
+    assert t["model.layers.1.post_attention_layernorm.weight"].shape == (160,)
+    assert t["model.norm.weight"].kind == "vector" and t["lm_head.weight"].shape == (384, 160)
+    assert not t["lm_head.weight"].optional
+    assert _table(TINY_A)["lm_head.weight"].optional          # tied: a stored copy is not read
+    assert len(t) == 1 + 3 * 9 + 2
+
+
+def test_random_model_folder_loads_and_is_seeded(tmp_path):
+    cfg = hb.LlamaConfig.from_dict(TINY_A)
+    d1 = write_random_model(str(tmp_path / "m1"), cfg, seed=5)
+    d2 = write_random_model(str(tmp_path / "m2"), cfg, seed=5)
+    d3 = write_random_model(str(tmp_path / "m3"), cfg, seed=6)
+    assert sorted(os.listdir(d1)) == ["config.json", "model.safetensors"]
+    assert hb.load_config(d1) == cfg
+    t1 = load_tensors(d1, _table(TINY_A), torch.bfloat16, CPU)
+    t2 = load_tensors(d2, _table(TINY_A), torch.bfloat16, CPU)
+    t3 = load_tensors(d3, _table(TINY_A), torch.bfloat16, CPU)
+    name = "model.layers.1.mlp.up_proj.weight"
+    assert torch.equal(t1[name], t2[name]) and not torch.equal(t1[name], t3[name])
+    assert t1[name].dtype == torch.bfloat16 and abs(t1[name].float().std().item() - 0.02) < 0.002
+    assert torch.all(t1["model.norm.weight"] == 1)
+    assert "lm_head.weight" not in t1
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
+    cfg = hb.LlamaConfig.from_dict(TINY_B)
+    table = _table(TINY_B)
+    tensors = random_tensors(table, 1, CPU)
+    del tensors["model.layers.1.mlp.up_proj.weight"]
+    del tensors["lm_head.weight"]
+    tensors["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(160, 161, dtype=torch.bfloat16)
+    tensors["model.layers.2.input_layernorm.weight"] = torch.zeros(159, dtype=torch.bfloat16)
+    tensors["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(160, dtype=torch.bfloat16)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)        # ignorable
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    with pytest.raises(WeightError) as ei:
+        load_tensors(str(tmp_path), table, torch.bfloat16, CPU)
+    e = ei.value
+    assert e.missing == ["lm_head.weight", "model.layers.1.mlp.up_proj.weight"]
+    assert e.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
+    assert sorted(w[0] for w in e.wrong_shape) == ["model.layers.0.self_attn.q_proj.weight",
+                                                   "model.layers.2.input_layernorm.weight"]
+    text = str(e)
+    assert "missing (2)" in text and "unexpected (1)" in text
+    assert "model.layers.0.self_attn.q_proj.weight has shape [160, 161], expected [160, 160]" in text
+
+
+def test_dtype_rules(tmp_path):
+    cfg = hb.LlamaConfig.from_dict(TINY_A)
+    table = _table(TINY_A)
+    tensors = random_tensors(table, 1, CPU)
+    exact = tensors["model.layers.0.mlp.down_proj.weight"].clone()
+    tensors["model.layers.0.mlp.gate_proj.weight"] = tensors["model.layers.0.mlp.gate_proj.weight"].to(torch.float32) * 1.001
+    tensors["model.layers.0.mlp.up_proj.weight"] = tensors["model.layers.0.mlp.up_proj.weight"].to(torch.float16)
+    tensors["model.norm.weight"] = tensors["model.norm.weight"].to(torch.float32).reshape(1, 64)   # extra unit dim
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    bf = load_tensors(str(tmp_path), table, torch.bfloat16, CPU)
+    assert bf["model.layers.0.mlp.down_proj.weight"].dtype == torch.bfloat16
+    assert bf["model.layers.0.mlp.gate_proj.weight"].dtype == torch.float32      # stored in 32-bit: stays so
+    assert bf["model.layers.0.mlp.up_proj.weight"].dtype == torch.bfloat16       # float16 is converted
+    assert bf["model.norm.weight"].shape == (64,)
+    f32 = load_tensors(str(tmp_path), table, torch.float32, CPU)
+    assert all(t.dtype == torch.float32 for t in f32.values())
+    assert torch.equal(f32["model.layers.0.mlp.down_proj.weight"], exact.float())  # widened exactly
+
+
+def test_container_errors(tmp_path):
+    (tmp_path / "model.safetensors").write_bytes(b"\x05\x00")
+    with pytest.raises(SafetensorsError, match="bad header length"):
+        SafetensorsFolder(str(tmp_path))
+    (tmp_path / "model.safetensors").write_bytes((1 << 40).to_bytes(8, "little") + b"{}")
+    with pytest.raises(SafetensorsError, match="bad header length"):
+        SafetensorsFolder(str(tmp_path))
+    hdr = json.dumps({"x": {"dtype": "F32", "shape": [4], "data_offsets": [0, 64]}}).encode()
+    (tmp_path / "model.safetensors").write_bytes(len(hdr).to_bytes(8, "little") + hdr + b"\0" * 16)
+    with pytest.raises(SafetensorsError, match="bad offsets for x"):
+        SafetensorsFolder(str(tmp_path))
+    with pytest.raises(SafetensorsError, match="cannot open"):
+        SafetensorsFolder(str(tmp_path / "nowhere"))
+
+
+def test_sharded_folder_and_prefix_choice(tmp_path):
+    cfg = hb.LlamaConfig.from_dict(TINY_A)
+    spec = cfg.model_spec()
+    table = weight_table(spec, prefix="model.language_model.")
+    tensors = random_tensors(table, 3, CPU)
+    names = list(tensors)
+    half = len(names) // 2
+    write_safetensors(str(tmp_path / "s1.safetensors"), {n: tensors[n] for n in names[:half]})
+    write_safetensors(str(tmp_path / "s2.safetensors"), {n: tensors[n] for n in names[half:]})
+    wm = {n: ("s1.safetensors" if i < half else "s2.safetensors") for i, n in enumerate(names)}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    f = SafetensorsFolder(str(tmp_path))
+    assert choose_prefix(f.names(), spec.weight_prefixes, "embed_tokens.weight") == "model.language_model."
+    f.close()
+    got = load_tensors(str(tmp_path), table, torch.bfloat16, CPU)
+    assert all(torch.equal(got[n], tensors[n]) for n in names)
+    assert choose_prefix(["model.embed_tokens.weight"], spec.weight_prefixes, "embed_tokens.weight") == "model."
