@@ -1,0 +1,315 @@
+"""Decode and prefill throughput of the Llama-3.1-8B-shaped model with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  A step is one decode step of a batch of 8 sequences whose caches hold
+about 8192 tokens each; ``value`` is decoded tokens per second from CUDA events around the
+steps; ``e2e`` is the same through the library's generation loop with host tokens in and out
+(pinned host memory -> device every step, sampled tokens device -> host every step).
+``prefill`` times one 2048-token prompt; ``roofline`` relates the decode step to the HBM
+bandwidth it needs (every weight once + the live sequences' cache); ``points`` adds decoding
+at batch 1 and 64.  Weights (15 GB) exceed L2 (126 MB), so every step reads them from HBM.
+The caches of the decode benchmark are filled with random keys and values instead of being
+prefilled; a decode step's work does not depend on their values.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Llama-3.1-8B-shaped
+MODEL_8B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", hidden_act="silu", hidden_size=4096,
+    num_hidden_layers=32, intermediate_size=14336, vocab_size=128256, num_attention_heads=32,
+    num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    tie_word_embeddings=False, max_position_embeddings=131072)
+CONTEXT = 8192
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        out = {k: float(p[k]) for k in FALLBACK_PEAKS if k in p}
+        if "hbm_gbs" in out and "bf16_tflops" in out:
+            out.setdefault("bf16_tflops_sustained", out["bf16_tflops"])
+            return out, "measured"
+    except (OSError, ValueError, KeyError, TypeError):
+        pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0])), mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def fill_cache_random(llm, seed=1):
+    """Random keys and values in the whole cache (stands for prefilled prompts)."""
+    import torch
+    g = torch.Generator(device=llm.engine.device).manual_seed(seed)
+    for grp in llm.engine.cache.groups:
+        for t in (grp.k, grp.v):
+            flat = t.view(-1)
+            step = 1 << 28
+            for i in range(0, flat.numel(), step):
+                part = flat[i:i + step]
+                part.copy_(torch.randn(part.numel(), generator=g, device=part.device, dtype=torch.float32) * 0.5)
+
+
+def open_filled(llm, batch, length):
+    """`batch` sequences whose caches already hold `length` tokens."""
+    seqs = []
+    for _ in range(batch):
+        s = llm.engine.open_sequence()
+        llm.engine.cache.reserve([(s, length)])
+        llm.engine.cache.commit(s, length)
+        seqs.append(s)
+    return seqs
+
+
+def time_decode(llm, batch, steps, warmup, length, sampler=None):
+    """Device time of `steps` decode steps of `batch` sequences at about `length` cached tokens."""
+    import torch
+    from hilbert_pruned_8b_b200.engine.batch import StepEntry
+    eng = llm.engine
+    seqs = open_filled(llm, batch, length - steps - warmup - 1)
+    gen = torch.Generator().manual_seed(5)
+    vocab = eng.vocab_size
+    toks = torch.randint(0, vocab, (steps + warmup, batch), generator=gen).tolist()
+    for w in range(warmup):
+        lg = eng.step([StepEntry(s, [toks[w][b]], [0]) for b, s in enumerate(seqs)])
+        llm.sampler.greedy(lg)
+    torch.cuda.synchronize()
+    launches0 = eng.ctx.ops.launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clocks = sampler
+    if clocks:
+        clocks.start()
+    start.record()
+    for k in range(steps):
+        lg = eng.step([StepEntry(s, [toks[warmup + k][b]], [0]) for b, s in enumerate(seqs)])
+        llm.sampler.greedy(lg)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    clock_info = clocks.stop() if clocks else None
+    launches = eng.ctx.ops.launches - launches0
+    lengths = [s.length for s in seqs]
+    step_bytes = eng.decode_step_bytes(lengths)
+    for s in seqs:
+        eng.close_sequence(s)
+    return ms, launches, step_bytes, clock_info
+
+
+def time_e2e(llm, batch, steps, warmup, length):
+    """The generation loop's decode phase: host tokens in, host tokens out, every step."""
+    import torch
+    from hilbert_pruned_8b_b200.engine.generate import GenerationRequest
+    from hilbert_pruned_8b_b200.sampling import SamplingParams
+    eng = llm.engine
+    gen = llm.generator
+    seqs = open_filled(llm, batch, length - steps - warmup - 2)
+    req = GenerationRequest([0], max_new_tokens=warmup, sampling=SamplingParams(0.0, 0), stop_token_ids=[])
+    live = {b: {"req": req, "rid": b, "stop": [], "seq": s, "out": [], "next": (17 * b + 3) % eng.vocab_size}
+            for b, s in enumerate(seqs)}
+    results = [None] * batch
+    # warm-up steps through the same loop (it closes nothing: budgets are per phase here)
+    for st in live.values():
+        st["req"] = GenerationRequest([0], max_new_tokens=10 ** 9, sampling=SamplingParams(0.0, 0), stop_token_ids=[])
+    _run_steps(gen, live, results, warmup)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    _run_steps(gen, live, results, steps)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    for s in seqs:
+        eng.close_sequence(s)
+    h2d = _step_meta_bytes(eng, batch, length)
+    return batch * steps / dt, h2d, batch * 4
+
+
+def _run_steps(gen, live, results, n):
+    """`n` steps of Generator.decode: budgets are set so that the loop returns after n tokens."""
+    from hilbert_pruned_8b_b200.engine.generate import GenerationRequest
+    from hilbert_pruned_8b_b200.sampling import SamplingParams
+    if n <= 0:
+        return
+    keep = dict(live)
+    for st in live.values():
+        st["req"] = GenerationRequest([0], max_new_tokens=len(st["out"]) + n, sampling=SamplingParams(0.0, 0),
+                                      stop_token_ids=[])
+    closed = []
+    orig_close = gen.engine.close_sequence
+    gen.engine.close_sequence = lambda seq: closed.append(seq)      # keep the caches for the next phase
+    try:
+        gen.decode(live, results)
+    finally:
+        gen.engine.close_sequence = orig_close
+    live.update(keep)
+
+
+def _step_meta_bytes(eng, batch, length):
+    """Bytes of the per-step host-to-device copy (tokens, positions, page tables, ...)."""
+    from hilbert_pruned_8b_b200.cache import pages_for
+    per_seq = 3 + 4 + pages_for(length) * max(1, len(eng.cache.groups))
+    return 4 * (batch * per_seq + 8)
+
+
+def time_prefill(llm, tokens, repeats=3, warmup=2):
+    import torch
+    from hilbert_pruned_8b_b200.engine.batch import StepEntry
+    eng = llm.engine
+    gen = torch.Generator().manual_seed(9)
+    toks = torch.randint(0, eng.vocab_size, (tokens,), generator=gen).tolist()
+    times = []
+    for i in range(warmup + repeats):
+        s = eng.open_sequence()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.step_chunked([StepEntry(s, toks, [tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+        eng.close_sequence(s)
+    return statistics.median(times)
+
+
+def prefill_flops(cfg, layers, tokens):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = 2 * tokens * (H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I)
+    attn = 2 * tokens * tokens * hd * nh          # causal: QK^T and PV over half the square each
+    return layers * (per_layer + attn) + 2 * H * V
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the installed reference package (semif-score) only scores answer options of text rows "
+                          "through transformers and needs a tokenizer and a hub revision; neither it nor the reference's "
+                          "C engine generates tokens (no decode loop or sampler: cleanroom-transformer/README.md:7-10), "
+                          "so it has no decode tokens/s to measure"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported by this single-GPU library")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.api import LLM
+
+    cfg_dict = dict(MODEL_8B)
+    full_layers = cfg_dict["num_hidden_layers"]
+    layers = a.layers or full_layers
+    cfg_dict["num_hidden_layers"] = layers
+    cfg = hb.LlamaConfig.from_dict(cfg_dict)
+    pk, pk_src = peaks()
+    max_batch = 64 if not a.skip_points else a.batch
+    max_tokens = max_batch * CONTEXT
+    t_build = time.time()
+    llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, device=0, max_batch=max_batch,
+                     max_step_tokens=PREFILL_TOKENS)
+    fill_cache_random(llm)
+    torch.cuda.synchronize()
+    build_s = time.time() - t_build
+
+    prefill_ms = time_prefill(llm, PREFILL_TOKENS)
+    pf = prefill_flops(cfg_dict, layers, PREFILL_TOKENS)
+    ms, launches, step_bytes, clocks = time_decode(llm, a.batch, a.steps, a.warmup, CONTEXT, ClockSampler())
+    e2e, h2d, d2h = time_e2e(llm, a.batch, a.steps, a.warmup, CONTEXT)
+    points = {}
+    if not a.skip_points:
+        for b in (1, 64):
+            pms, _, _, _ = time_decode(llm, b, max(4, a.steps // 2), 3, CONTEXT)
+            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    value = a.batch / (ms * 1e-3)
+    line = {
+        "metric": "decode tok/s @ batch 8, context 8192 (Llama-3.1-8B-shaped, random weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache contents",
+        "impl": "ours",
+        "config": {"model": "llama-3.1-8b-shaped", "layers": layers, "layers_in_config": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": a.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
+                   "parallelism": "single-gpu", "l2": "weights (15 GB) exceed L2; every step reads them from HBM",
+                   "peaks": pk_src, "hbm_gbs_peak": pk["hbm_gbs"], "bf16_tflops_peak": pk["bf16_tflops"]},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+        "setup_s": round(build_s, 1),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

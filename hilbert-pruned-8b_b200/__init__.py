@@ -11,3 +11,9 @@ from .config import LlamaConfig, load_config, register_architecture
 
 __version__ = "0.1.0"
 __all__ = ["cache", "config", "engine", "parts", "weights", "LlamaConfig", "load_config", "register_architecture"]
+
+
+def load(model: str, dtype: str = "bfloat16", max_tokens: int = 4096, device: int = 0, **kw):
+    """Loads a model folder onto a GPU: ``load(dir).generate([[1, 2, 3]], max_new_tokens=8)``."""
+    from .api import LLM
+    return LLM.load(model, dtype, max_tokens, device, **kw)

@@ -142,22 +142,30 @@ class Generator:
             self.stats.prefill_seconds += time.perf_counter() - t0
             self.stats.prefill_tokens += sum(len(live[i]["req"].prompt) for i in order)
             self._take(order, toks, live, results)
-            step_no = 1
-            while live:
-                t0 = time.perf_counter()
-                order = list(live)
-                entries = [StepEntry(live[i]["seq"], [live[i]["next"]], [0]) for i in order]
-                logits = eng.step(entries)
-                toks = self._sample(logits, [live[i] for i in order], step_no)
-                self.stats.decode_steps += 1
-                self.stats.decode_tokens += len(order)
-                self._take(order, toks, live, results)
-                self.stats.decode_seconds += time.perf_counter() - t0
-                step_no += 1
+            self.decode(live, results, first_step=1)
         finally:
             for st in live.values():
                 if st["seq"].open:
                     eng.close_sequence(st["seq"])
+
+    def decode(self, live: Dict[int, dict], results, first_step: int = 1) -> None:
+        """The decode phase: one token per live sequence per step until none is live.  ``live``
+        maps a result index to a state with ``req``, ``rid``, ``stop``, ``seq`` (whose cache
+        holds everything but the token in ``next``) and ``out``.  Every step copies the batch's
+        tokens to the device and the sampled tokens back."""
+        eng = self.engine
+        step_no = first_step
+        while live:
+            t0 = time.perf_counter()
+            order = list(live)
+            entries = [StepEntry(live[i]["seq"], [live[i]["next"]], [0]) for i in order]
+            logits = eng.step(entries)
+            toks = self._sample(logits, [live[i] for i in order], step_no)
+            self.stats.decode_steps += 1
+            self.stats.decode_tokens += len(order)
+            self._take(order, toks, live, results)
+            self.stats.decode_seconds += time.perf_counter() - t0
+            step_no += 1
 
     def _sample(self, logits, states, step_no: int) -> List[int]:
         toks = self.sampler.sample(logits, [s["req"].sampling.temperature for s in states],
