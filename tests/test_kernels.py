@@ -1,0 +1,347 @@
+"""Each kernel alone against a plain torch statement of the same operation, at sizes other
+than the engine's tiny models (widths and vocabularies that are no power of two, head sizes
+in steps of 16, odd head and group counts)."""
+import math
+import types
+
+import pytest
+import torch
+
+from conftest import require_gpu
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    require_gpu()
+    from hilbert_pruned_8b_b200.kernels.ops import Ops
+    return Ops(torch.device(DEV))
+
+
+def _bf(x):
+    return x.to(torch.bfloat16)
+
+
+def _rel(got, ref):
+    return ((got.double() - ref.double()).abs().max() / ref.double().abs().max().clamp(min=1e-6)).item()
+
+
+# ------------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(ops, dtype):
+    torch.manual_seed(0)
+    table = torch.randn(301, 72, device=DEV).to(dtype)
+    toks = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, device=DEV)
+    ops.embed(toks, table, out)
+    assert torch.equal(out, table[toks.long()].float())
+
+
+@pytest.mark.parametrize("hidden,eps,offset", [(72, 1e-5, 0.0), (1000, 1e-6, 1.0), (4096, 1e-5, 0.0)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(ops, hidden, eps, offset, out_dtype):
+    torch.manual_seed(1)
+    x = torch.randn(7, hidden, device=DEV) * 3
+    w = torch.randn(hidden, device=DEV)
+    ref = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * (offset + w.double())
+    out = torch.empty(7, hidden, device=DEV, dtype=out_dtype)
+    ops.rmsnorm(x, w, eps, offset, out)
+    tol = 2e-6 if out_dtype == torch.float32 else 2 ** -8
+    assert _rel(out, ref) < tol
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    sub = torch.empty(3, hidden, device=DEV, dtype=out_dtype)
+    ops.rmsnorm(x, w, eps, offset, sub, rows)
+    assert torch.equal(sub, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(ops, dtype):
+    torch.manual_seed(2)
+    gu = (torch.randn(9, 2 * 176, device=DEV) * 4).to(dtype)
+    out = torch.empty(9, 176, device=DEV, dtype=dtype)
+    ops.silu_mul(gu, out)
+    g, u = gu[:, :176].double(), gu[:, 176:].double()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert _rel(out, ref) < (1e-6 if dtype == torch.float32 else 2 ** -8)
+
+
+def test_rope_table(ops):
+    pos = torch.tensor([0, 1, 63, 64, 5000, 131071], dtype=torch.int32, device=DEV)
+    inv = (1.0 / (500000.0 ** (torch.arange(0, 24, dtype=torch.float32) / 24))).to(DEV)
+    out = torch.empty(6, 24, 2, device=DEV)
+    ops.rope_table(pos, inv, out)
+    ang = (inv[None, :] * pos.float()[:, None]).double()      # the float32 product, then exact functions
+    assert (out[..., 0].double() - torch.cos(ang)).abs().max() < 3e-7
+    assert (out[..., 1].double() - torch.sin(ang)).abs().max() < 3e-7
+
+
+def _step(tok_seq, positions, tables):
+    return types.SimpleNamespace(tok_seq=tok_seq, positions=positions, page_tables=[tables])
+
+
+def _cache(n_pages, nkv, hd, dtype):
+    from hilbert_pruned_8b_b200.cache import LayerCache
+    k = torch.zeros(n_pages, nkv, 64, hd, device=DEV, dtype=dtype)
+    return LayerCache(k, torch.zeros_like(k), 0, None)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(6, 3, 48, 48), (5, 1, 80, 40), (8, 8, 16, 16)])
+def test_rope_kv_append(ops, dtype, nh, nkv, hd, rot):
+    torch.manual_seed(3)
+    # two sequences: positions 60..69 (crossing a page) and 0..2; pages deliberately out of order
+    positions = torch.tensor(list(range(60, 70)) + [0, 1, 2], dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([0] * 10 + [1] * 3, dtype=torch.int32, device=DEV)
+    tables = torch.tensor([[5, 2], [0, -1]], dtype=torch.int32, device=DEV)
+    T = 13
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, device=DEV).to(dtype)
+    before = qkv.clone()
+    cache = _cache(7, nkv, hd, dtype)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+    table = torch.empty(T, rot // 2, 2, device=DEV)
+    ops.rope_table(positions, inv, table)
+    ops.rope_kv_append(qkv, table, rot, nh, nkv, hd, cache, _step(tok_seq, positions, tables), True)
+
+    def rotate(x):                                  # [T, heads, hd] in float64
+        cs, sn = table[..., 0].double()[:, None, :], table[..., 1].double()[:, None, :]
+        y = x.clone()
+        h = rot // 2
+        y[..., :h] = x[..., :h] * cs - x[..., h:rot] * sn
+        y[..., h:rot] = x[..., h:rot] * cs + x[..., :h] * sn
+        return y
+
+    b = before.double()
+    q_ref = rotate(b[:, :nh * hd].view(T, nh, hd))
+    k_ref = rotate(b[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd))
+    v_ref = b[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert _rel(qkv[:, :nh * hd].view(T, nh, hd), q_ref) < tol
+    assert torch.equal(qkv[:, nh * hd:], before[:, nh * hd:])             # k and v columns untouched
+    for t in range(T):
+        page = int(tables[int(tok_seq[t]), int(positions[t]) // 64])
+        off = int(positions[t]) % 64
+        assert _rel(cache.k[page, :, off], k_ref[t]) < tol
+        assert torch.equal(cache.v[page, :, off].double(), v_ref[t].to(dtype).double())
+    assert cache.k.abs().sum(dim=(1, 3))[[1, 3, 4, 6]].sum() == 0          # pages of nobody stay clean
+    # a layer that reads another layer's cache: only the queries turn, nothing is written
+    qkv2, cache2 = before.clone(), _cache(7, nkv, hd, dtype)
+    ops.rope_kv_append(qkv2, table, rot, nh, nkv, hd, cache2, _step(tok_seq, positions, tables), False)
+    assert torch.equal(qkv2[:, :nh * hd], qkv[:, :nh * hd]) and cache2.k.abs().sum() == 0
+
+
+# ------------------------------------------------------------------------------- matrix products
+SHAPES = [(1, 128, 64), (8, 256, 160), (5, 100, 176), (33, 384, 416), (64, 512, 1024), (200, 300, 72), (300, 640, 256),
+          (17, 129, 8), (2, 96, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_general_float32(ops, M, N, K):
+    torch.manual_seed(4)
+    a, w = torch.randn(M, K, device=DEV), torch.randn(N, K, device=DEV)
+    out = torch.full((M, N), 7.0, device=DEV)
+    ops.linear(a, w, out)
+    ref = a.double() @ w.double().t()
+    assert _rel(out, ref) < 1e-6 * math.sqrt(K)
+    res = torch.randn(M, N, device=DEV)
+    acc = res.clone()
+    ops.linear(a, w, acc, accumulate=True)
+    assert _rel(acc, ref + res.double()) < 1e-6 * math.sqrt(K)
+
+
+def test_gemm_general_mixed_dtypes_and_odd_k(ops):
+    torch.manual_seed(5)
+    a, w = _bf(torch.randn(9, 37, device=DEV)), torch.randn(50, 37, device=DEV)      # K = 37: no tensor-core path
+    out = torch.empty(9, 50, device=DEV, dtype=torch.bfloat16)
+    ops.linear(a, w, out)
+    assert _rel(out, a.double() @ w.double().t()) < 2 ** -8
+    a2, w2 = _bf(torch.randn(9, 37, device=DEV)), _bf(torch.randn(50, 37, device=DEV))
+    out2 = torch.empty(9, 50, device=DEV)
+    ops.linear(a2, w2, out2)
+    assert _rel(out2, a2.double() @ w2.double().t()) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_tensor_core_against_plain_and_general(ops, M, N, K):
+    torch.manual_seed(6)
+    a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
+    ref = a.double() @ w.double().t()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), 7.0, device=DEV, dtype=out_dtype)
+        ops.linear(a, w, out)
+        ops.check_errors()
+        assert _rel(out, ref) < (2 ** -8 if out_dtype == torch.bfloat16 else 2e-6 * math.sqrt(K))
+    res = torch.randn(M, N, device=DEV)
+    acc = res.clone()
+    ops.linear(a, w, acc, accumulate=True)
+    ops.check_errors()
+    assert _rel(acc, ref + res.double()) < 2e-6 * math.sqrt(K)
+    # the general kernel on the same operands
+    ops.use_tensor_cores = False
+    try:
+        gen = torch.empty(M, N, device=DEV)
+        ops.linear(a, w, gen)
+    finally:
+        ops.use_tensor_cores = True
+    out = torch.empty(M, N, device=DEV)
+    ops.linear(a, w, out)
+    assert _rel(out, gen) < 2e-6 * math.sqrt(K)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 512, 1024, 4), (1, 384, 4096, 3), (64, 256, 2048, 8), (5, 100, 416, 2)])
+def test_gemm_tensor_core_split_k(ops, M, N, K, splits):
+    torch.manual_seed(7)
+    a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
+    ref = a.double() @ w.double().t()
+    res = torch.randn(M, N, device=DEV)
+    for rep in range(2):                    # twice: the tile counters must come back to zero
+        acc = res.clone()
+        ops.linear(a, w, acc, accumulate=True, splits=splits)
+        ops.check_errors()
+        assert _rel(acc, ref + res.double()) < 2e-6 * math.sqrt(K)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.linear(a, w, out, splits=splits)
+    assert _rel(out, ref) < 2 ** -8
+    assert int(ops._splitk_counters.abs().sum()) == 0
+    again = torch.empty_like(out)
+    ops.linear(a, w, again, splits=splits)
+    assert torch.equal(out, again)          # the sum order is fixed
+
+
+@pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 300), (8, 4096, 512)])
+def test_linear_swiglu(ops, M, K, I):
+    from hilbert_pruned_8b_b200.engine.workspace import Workspace
+    torch.manual_seed(8)
+    h = _bf(torch.randn(M, K, device=DEV))
+    w = _bf(torch.randn(2 * I, K, device=DEV) / math.sqrt(K))
+    act = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+    ws = Workspace(torch.device(DEV))
+    ops.linear_swiglu(h, w, act, ws, M)
+    ops.check_errors()
+    g, u = h.double() @ w[:I].double().t(), h.double() @ w[I:].double().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert _rel(act, ref) < 2 ** -7
+    ops.use_tensor_cores = False
+    try:
+        slow = torch.empty_like(act)
+        ops.linear_swiglu(h, w, slow, ws, M)
+    finally:
+        ops.use_tensor_cores = True
+    assert _rel(slow, ref) < 2 ** -6     # the unfused path rounds gate and up to bfloat16 first
+
+
+# ------------------------------------------------------------------------------- attention
+def _attention_reference(q, keys, values, lens_before, new, nh, nkv, hd, scale, window):
+    """q [T, nh, hd]; keys/values: per sequence [len, nkv, hd] float64."""
+    out, t = [], 0
+    for b, n in enumerate(new):
+        for i in range(n):
+            p = lens_before[b] + i
+            lo = max(0, p - window + 1) if window else 0
+            rows = []
+            for j in range(nh):
+                g = j // (nh // nkv)
+                sc = (keys[b][lo:p + 1, g] @ q[t, j]) * scale
+                rows.append(torch.softmax(sc, 0) @ values[b][lo:p + 1, g])
+            out.append(torch.stack(rows))
+            t += 1
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(6, 3, 48, None), (5, 1, 80, None), (4, 4, 16, 70), (8, 2, 128, None),
+                                              (3, 1, 256, 33)])
+def test_attention_general(ops, dtype, nh, nkv, hd, window):
+    torch.manual_seed(9)
+    lens_before, new = [130, 0, 63], [3, 70, 1]             # decode-like, prefill and a page edge in one batch
+    total = [a + b for a, b in zip(lens_before, new)]
+    keys = [torch.randn(n, nkv, hd, dtype=torch.float64) for n in total]
+    values = [torch.randn(n, nkv, hd, dtype=torch.float64) for n in total]
+    keys = [k.to(dtype).double() for k in keys]
+    values = [v.to(dtype).double() for v in values]
+    cache = _cache(9, nkv, hd, dtype)
+    tables = torch.tensor([[7, 1, 4], [3, 8, -1], [0, -1, -1]], dtype=torch.int32, device=DEV)
+    for b, n in enumerate(total):
+        for s in range(n):
+            page = int(tables[b, s // 64])
+            cache.k[page, :, s % 64] = keys[b][s].to(dtype).to(DEV)
+            cache.v[page, :, s % 64] = values[b][s].to(dtype).to(DEV)
+    T = sum(new)
+    q = torch.randn(T, nh, hd, dtype=torch.float64).to(dtype)
+    qkv = torch.zeros(T, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
+    qkv[:, :nh * hd] = q.reshape(T, nh * hd).to(DEV)
+    tok_seq = torch.tensor(sum(([b] * n for b, n in enumerate(new)), []), dtype=torch.int32, device=DEV)
+    positions = torch.tensor(sum((list(range(l, l + n)) for l, n in zip(lens_before, new)), []), dtype=torch.int32,
+                             device=DEV)
+    out = torch.empty(T, nh * hd, device=DEV, dtype=dtype)
+    scale = 1.0 / math.sqrt(hd)
+    ops.attention(qkv, nh, nkv, hd, cache, _step(tok_seq, positions, tables), out, scale, window)
+    ref = _attention_reference(q.double(), keys, values, lens_before, new, nh, nkv, hd, scale, window)
+    assert _rel(out.view(T, nh, hd).cpu(), ref) < (2e-6 if dtype == torch.float32 else 2 ** -7)
+
+
+def test_attention_finds_a_far_key(ops):
+    """One key among hundreds matches the query: the output must be that key's value."""
+    nh, nkv, hd, n = 4, 2, 32, 700
+    torch.manual_seed(10)
+    cache = _cache(12, nkv, hd, torch.float32)
+    tables = torch.arange(11, -1, -1, dtype=torch.int32, device=DEV).view(1, 12)
+    k = torch.randn(n, nkv, hd) * 0.1
+    v = torch.randn(n, nkv, hd)
+    needle = 137
+    k[needle, 1] = torch.ones(hd) * 3.0
+    for s in range(n):
+        cache.k[int(tables[0, s // 64]), :, s % 64] = k[s].to(DEV)
+        cache.v[int(tables[0, s // 64]), :, s % 64] = v[s].to(DEV)
+    qkv = torch.zeros(1, (nh + 2 * nkv) * hd, device=DEV)
+    qkv[0, 3 * hd:4 * hd] = 10.0                                   # head 3 reads kv head 1
+    out = torch.empty(1, nh * hd, device=DEV)
+    step = _step(torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV), tables)
+    ops.attention(qkv, nh, nkv, hd, cache, step, out, 1.0 / math.sqrt(hd), None)
+    assert (out[0, 3 * hd:].cpu() - v[needle, 1]).abs().max() < 1e-4
+    assert (out[0, :hd].cpu() - v[:, 0].mean(0)).abs().max() < 1e-4   # a zero query averages the values
+
+
+# ------------------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("vocab", [7, 384, 5003, 128256])
+def test_argmax_lowest_index_on_ties(ops, vocab):
+    torch.manual_seed(11)
+    lg = torch.randn(5, vocab, device=DEV)
+    lg[1, vocab - 1] = 9.0
+    lg[2, 3] = lg[2, vocab // 2] = 11.0
+    lg[3] = 0.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(lg, out)
+    want = [int(lg[0].argmax()), vocab - 1, 3, 0, int(lg[4].argmax())]
+    assert out.tolist() == want
+
+
+@pytest.mark.parametrize("vocab", [11, 384, 50257])
+def test_temperature_sampling_follows_the_cdf(ops, vocab):
+    from hilbert_pruned_8b_b200.sampling import uniform_from
+    torch.manual_seed(12)
+    n = 64
+    lg = torch.randn(n, vocab, device=DEV) * 2
+    temps = [0.8] * (n - 2) + [0.0, 1.7]
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    seeds = torch.full((n,), 1234, dtype=torch.int64, device=DEV)
+    reqs = torch.arange(n, dtype=torch.int64, device=DEV)
+    steps = torch.full((n,), 5, dtype=torch.int64, device=DEV)
+    ops.sample(lg, torch.tensor(temps, device=DEV), seeds, reqs, steps, out)
+    got = out.tolist()
+    for r in range(n):
+        if temps[r] == 0.0:
+            assert got[r] == int(lg[r].argmax())
+            continue
+        p = torch.softmax(lg[r].double().cpu() / temps[r], 0)
+        c = torch.cumsum(p, 0)
+        u = uniform_from(1234, r, 5)
+        lo = float(c[got[r] - 1]) if got[r] > 0 else 0.0
+        assert lo - 1e-5 <= u <= float(c[got[r]]) + 1e-5, f"row {r}: u={u} outside the chosen token's interval"
+    again = torch.empty_like(out)
+    ops.sample(lg, torch.tensor(temps, device=DEV), seeds, reqs, steps, again)
+    assert torch.equal(out, again)
+    ops.sample(lg, torch.tensor(temps, device=DEV), seeds, reqs, steps + 1, again)
+    assert not torch.equal(out, again)
