@@ -36,6 +36,17 @@ int hb_attention_general(const void* q, int q_dtype, long long q_stride, const v
                          int cache_dtype, const int* page_table, int pt_width, const int* tok_seq,
                          const int* positions, void* out, int out_dtype, long long out_stride, int n_tokens,
                          int n_heads, int n_kv_heads, int head_dim, float scale, int window, void* stream);
+int hb_attention_decode_supported(int n_heads, int n_kv_heads, int head_dim);
+long long hb_attention_decode_scratch_floats(int batch, int n_heads, int head_dim, int splits);
+int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                        const int* page_table, int pt_width, const int* positions, float* scratch, void* out,
+                        long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim, float scale,
+                        int window, int splits, int max_pages, int n_pages, void* stream);
+int hb_attention_prefill_supported(int n_heads, int n_kv_heads, int head_dim);
+int hb_attention_prefill(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                         const int* page_table, int pt_width, const int* seq_start, const int* seq_pos0, void* out,
+                         long long out_stride, int n_seqs, int q_blocks, int n_heads, int n_kv_heads, int head_dim,
+                         float scale, int window, int n_pages, void* stream);
 int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, void* stream);
 int hb_sample(const float* logits, long long stride, const float* temperature, const long long* seeds,
               const long long* request_ids, const long long* steps, int* out, int n_rows, int vocab, void* stream);

@@ -1,0 +1,296 @@
+// Decode attention over the paged bfloat16 cache: one query token per sequence, the keys
+// split over several CTAs (split-K), partial results combined by a second kernel.
+//
+// Per (sequence, kv head, split): the CTA streams its pages of keys and values once through a
+// 3-stage cp.async pipeline and serves all query heads of the group at once (the group's
+// heads are the rows of a 16-row mma.sync tile), so a key is read once per kv head, not once
+// per query head.  Scores, running maximum and sum are float32; the split's unnormalised
+// output with its maximum and sum goes to scratch; the combine kernel merges the splits with
+// log-sum-exp weights and writes bfloat16.  Formula: cleanroom-transformer/src/cpu_backend.c:102-124
+// (the reference's GPU kernel reads every key once per query head: cuda_backend.cu:254-306).
+//
+// Sizes: head size 64 or 128, group size up to 16; anything else is the general kernel's.
+#include "api.h"
+#include "mma.cuh"
+
+#define AD_THREADS 128
+#define AD_STAGES 3
+#define AD_LOG2E 1.4426950408889634f
+
+template <int HD>
+__global__ void __launch_bounds__(AD_THREADS)
+attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                   const int* __restrict__ page_table, int pt_width, const int* __restrict__ positions,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, float scale_log2e,
+                   int window, int pages_per_split, int n_pages) {
+    constexpr int ROW_BYTES = HD * 2;
+    constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;        // one page of K (or V) of one kv head
+    constexpr int CHUNKS = ROW_BYTES / 16;
+    constexpr int KSTEPS = HD / 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z, S = gridDim.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = nh / nkv;
+    const int len = positions[b] + 1;
+    const int lo = (window > 0 && len - window > 0) ? len - window : 0;
+    const int p_begin = max(z * pages_per_split, lo / HB_PAGE_TOKENS);
+    const int p_end = min((z + 1) * pages_per_split, (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS);
+    const int* pt = page_table + (size_t)b * pt_width;
+
+    if (p_begin >= p_end) {                       // nothing to read: an empty partial
+        if (tid < G) {
+            float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.0f;
+        }
+        return;
+    }
+
+    // query fragments: row r of the tile is head g*G + r (rows >= G are zero)
+    uint32_t qf[KSTEPS][4];
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+        const bf16* q0 = q + (size_t)b * q_stride + (size_t)(g * G + r0) * HD;
+        const bf16* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c) : 0u;
+            qf[ks][1] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c) : 0u;
+            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c + 8) : 0u;
+            qf[ks][3] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c + 8) : 0u;
+        }
+    }
+
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    auto load_page = [&](int stage, int page_idx) {
+        if (page_idx < p_end) {
+            int page = pt[page_idx];
+            if (page < 0 || page >= n_pages) page = 0;      // never read outside the cache
+            const uint8_t* ksrc = (const uint8_t*)(kc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
+            const uint8_t* vsrc = (const uint8_t*)(vc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
+            const uint32_t kdst = smem_base + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
+#pragma unroll
+            for (int i = tid; i < HB_PAGE_TOKENS * CHUNKS; i += AD_THREADS) {
+                const int row = i / CHUNKS, ch = i % CHUNKS;
+                const uint32_t off = swizzled<ROW_BYTES>(row, ch);
+                cp_async_16(kdst + off, ksrc + (size_t)i * 16);
+                cp_async_16(vdst + off, vsrc + (size_t)i * 16);
+            }
+        }
+        cp_async_commit();
+    };
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+#pragma unroll
+    for (int s = 0; s < AD_STAGES - 1; s++) load_page(s, p_begin + s);
+
+    for (int pi = p_begin; pi < p_end; pi++) {
+        const int it = pi - p_begin;
+        cp_async_wait<AD_STAGES - 2>();
+        __syncthreads();
+        load_page((it + AD_STAGES - 1) % AD_STAGES, pi + AD_STAGES - 1);
+        const uint32_t kt = smem_base + (it % AD_STAGES) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
+
+        // scores of this warp's 16 keys of the page
+        float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+        const int key_row = warp * 16 + ((lane >> 4) << 3) + (lane & 7);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            uint32_t kf[4];
+            ldmatrix_x4(kf, kt + swizzled<ROW_BYTES>(key_row, 2 * ks + ((lane >> 3) & 1)));
+            mma_bf16_16816(s[0], qf[ks], kf[0], kf[1]);
+            mma_bf16_16816(s[1], qf[ks], kf[2], kf[3]);
+        }
+        const int key0 = pi * HB_PAGE_TOKENS + warp * 16 + (lane & 3) * 2;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int key = key0 + nt * 8 + (e & 1);
+                const float v = (key >= lo && key < len) ? s[nt][e] * scale_log2e : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        uint32_t pa[4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            float r = mx[h];
+            r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, 1));
+            r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, 2));
+            const float m_new = fmaxf(m[h], r);
+            const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = exp2f(m[h] - m_safe);
+            m[h] = m_new;
+            float sum = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float p = exp2f(s[nt][2 * h + e] - m_safe);
+                    s[nt][2 * h + e] = p;
+                    sum += p;
+                }
+            l[h] = l[h] * corr + sum;
+#pragma unroll
+            for (int i = 0; i < HD / 8; i++) {
+                o[i][2 * h] *= corr;
+                o[i][2 * h + 1] *= corr;
+            }
+        }
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+        const int v_row = warp * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int dn = 0; dn < HD / 16; dn++) {
+            uint32_t vf[4];
+            ldmatrix_x4_trans(vf, vt + swizzled<ROW_BYTES>(v_row, 2 * dn + (lane >> 4)));
+            mma_bf16_16816(o[2 * dn], pa, vf[0], vf[1]);
+            mma_bf16_16816(o[2 * dn + 1], pa, vf[2], vf[3]);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the four warps (each saw a quarter of every page) and write the split's partial
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    float* so = reinterpret_cast<float*>(smem);                       // [4 warps][16 rows][HD]
+    float* sm = so + 4 * 16 * HD;                                      // [4][16]
+    float* sl = sm + 4 * 16;
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+        for (int i = 0; i < HD / 8; i++) {
+            float* row0 = so + ((size_t)(warp * 16 + r0) * HD) + i * 8 + c;
+            float* row1 = row0 + 8 * HD;
+            row0[0] = o[i][0];
+            row0[1] = o[i][1];
+            row1[0] = o[i][2];
+            row1[1] = o[i][3];
+        }
+        if ((lane & 3) == 0) {
+            sm[warp * 16 + r0] = m[0];
+            sm[warp * 16 + r0 + 8] = m[1];
+            sl[warp * 16 + r0] = l[0];
+            sl[warp * 16 + r0 + 8] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += AD_THREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, sm[w * 16 + r]);
+        float acc = 0.0f, L = 0.0f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float e = exp2f(sm[w * 16 + r] - M);
+                acc += so[(size_t)(w * 16 + r) * HD + d] * e;
+                L += sl[w * 16 + r] * e;
+            }
+        }
+        const size_t base = ((size_t)b * nh + g * G + r) * S + z;
+        part_o[base * HD + d] = acc;
+        if (d == 0) {
+            part_ml[base * 2] = M;
+            part_ml[base * 2 + 1] = L;
+        }
+    }
+}
+
+// out[b, head, :] = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M)
+template <typename TO>
+__global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           TO* __restrict__ out, long long out_stride, int nh, int hd, int S) {
+    const int b = blockIdx.x, head = blockIdx.y;
+    const size_t base = ((size_t)b * nh + head) * S;
+    float M = -INFINITY;
+    for (int z = 0; z < S; z++) M = fmaxf(M, part_ml[(base + z) * 2]);
+    float L = 0.0f;
+    for (int z = 0; z < S; z++) {
+        const float mz = part_ml[(base + z) * 2];
+        if (mz != -INFINITY) L += part_ml[(base + z) * 2 + 1] * exp2f(mz - M);
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int z = 0; z < S; z++) {
+            const float mz = part_ml[(base + z) * 2];
+            if (mz != -INFINITY) acc += part_o[(base + z) * hd + d] * exp2f(mz - M);
+        }
+        out[(size_t)b * out_stride + (size_t)head * hd + d] = from_f32<TO>(acc * inv);
+    }
+}
+
+extern "C" int hb_attention_decode_supported(int n_heads, int n_kv_heads, int head_dim) {
+    return (head_dim == 64 || head_dim == 128) && n_kv_heads > 0 && n_heads % n_kv_heads == 0 &&
+           n_heads / n_kv_heads <= 16;
+}
+
+// Scratch floats a call needs: partial outputs and (max, sum) pairs.
+extern "C" long long hb_attention_decode_scratch_floats(int batch, int n_heads, int head_dim, int splits) {
+    return (long long)batch * n_heads * splits * (head_dim + 2);
+}
+
+template <int HD>
+static int launch_decode(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
+                         int pt_width, const int* positions, float* scratch, void* out, long long out_stride, int batch,
+                         int nh, int nkv, float scale, int window, int splits, int pages_per_split, int n_pages,
+                         cudaStream_t s) {
+    constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
+    constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
+    constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return hb_fail("attention_decode: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)batch * nh * splits * HD;
+    dim3 grid(splits, nkv, batch);
+    attn_decode_kernel<HD><<<grid, AD_THREADS, SMEM, s>>>((const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
+                                                          pt_width, positions, part_o, part_ml, nh, nkv, scale * AD_LOG2E,
+                                                          window, pages_per_split, n_pages);
+    if (hb_check_launch("attention_decode")) return 1;
+    dim3 cgrid(batch, nh);
+    attn_decode_combine_kernel<bf16><<<cgrid, HD, 0, s>>>(part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
+    return hb_check_launch("attention_decode_combine");
+}
+
+// q: [batch, q_stride] bfloat16 with head j at columns [j*hd, (j+1)*hd); positions[b] is the
+// query's position (its own key, already in the cache, is the last one it sees).  `scratch`
+// holds hb_attention_decode_scratch_floats floats.  `max_pages` bounds the pages of any
+// sequence of the batch; the keys are cut into `splits` ranges of whole pages.
+extern "C" int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                   const int* page_table, int pt_width, const int* positions, float* scratch, void* out,
+                                   long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                   int window, int splits, int max_pages, int n_pages, void* stream) {
+    if (batch == 0) return 0;
+    HB_REQUIRE(hb_attention_decode_supported(n_heads, n_kv_heads, head_dim),
+               "attention_decode: head size %d with %d heads over %d kv heads is not built (64 or 128, groups up to 16)",
+               head_dim, n_heads, n_kv_heads);
+    HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && scratch != nullptr, "attention_decode: bad sizes");
+    HB_REQUIRE(batch <= 65535 && n_kv_heads <= 65535, "attention_decode: batch or kv heads too large for one launch");
+    HB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q & 3) == 0, "attention_decode: queries must be 4-byte aligned");
+    HB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_decode: cache must be 16-byte aligned");
+    if (splits > max_pages) splits = max_pages;
+    const int pps = (max_pages + splits - 1) / splits;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_dim == 128)
+        return launch_decode<128>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride,
+                                  batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+    return launch_decode<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride, batch,
+                             n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+}

@@ -34,6 +34,10 @@ _SIGNATURES = {
                    _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "hb_attention_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                              _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
+    "hb_attention_decode": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
+                            _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_attention_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
+                             _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr],
     "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
 }
@@ -61,6 +65,10 @@ def load_library():
         lib.hb_gemm_tc_token_tile.argtypes, lib.hb_gemm_tc_token_tile.restype = [_c_int], _c_int
         lib.hb_gemm_tc_scratch_floats.argtypes, lib.hb_gemm_tc_scratch_floats.restype = [_c_int, _c_int, _c_int], _c_ll
         lib.hb_gemm_tc_tiles.argtypes, lib.hb_gemm_tc_tiles.restype = [_c_int, _c_int], _c_ll
+        for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported"):
+            getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
+        lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
+        lib.hb_attention_decode_scratch_floats.restype = _c_ll
         _lib = lib
     return _lib
 
@@ -104,6 +112,9 @@ class Ops:
         # split-K scratch: float32 partial tiles and one counter per output tile (kept zero)
         self._splitk_partials = torch.empty(8 << 20, dtype=torch.float32, device=self.device)
         self._splitk_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
+        # split-K decode attention scratch: partial outputs with their maxima and sums
+        self._decode_scratch = torch.empty(4 << 20, dtype=torch.float32, device=self.device)
+        self.use_fast_attention = True  # tests switch this off to compare with the general kernel
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
@@ -265,20 +276,49 @@ class Ops:
         self.silu_mul(gu, act)
 
     # ------------------------------------------------------------------ attention
+    def decode_splits_for(self, batch: int, kv_heads: int, max_pages: int) -> int:
+        """Key splits of decode attention so that about two CTAs per SM stream the cache."""
+        return max(1, min(max_pages, -(-2 * self.sm_count // max(1, batch * kv_heads))))
+
     def attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out, scale: float,
-                  window: Optional[int]) -> None:
+                  window: Optional[int], splits: Optional[int] = None) -> None:
         """Causal attention of the step's tokens over the cache; queries are the first
-        ``heads * head_dim`` columns of ``qkv``."""
+        ``heads * head_dim`` columns of ``qkv``.  bfloat16 with head size 64 or 128 runs the
+        tensor-core kernels (split-K for one token per sequence, flash-style otherwise);
+        everything else runs the general kernel."""
         self._dev(qkv, cache.k, cache.v, out)
         T = qkv.shape[0]
         pt = step.page_tables[cache.group]
         if out.shape[0] != T or out.shape[1] != heads * head_dim:
             raise KernelError("attention: output shape does not match")
+        win = int(window) if window else 0
+        fast = (self.use_fast_attention and qkv.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+                and out.dtype == torch.bfloat16 and cache.k.is_contiguous() and cache.v.is_contiguous())
+        if fast and step.is_decode and self.lib.hb_attention_decode_supported(heads, kv_heads, head_dim):
+            max_pages = (step.max_len + 63) // 64
+            n_splits = splits if splits is not None else self.decode_splits_for(T, kv_heads, max_pages)
+            n_splits = max(1, min(n_splits, max_pages))
+            need = self.lib.hb_attention_decode_scratch_floats(T, heads, head_dim, n_splits)
+            if need > self._decode_scratch.numel():
+                self._decode_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+            self._call("hb_attention_decode", qkv.data_ptr(), _rows(qkv, "attention queries"), cache.k.data_ptr(),
+                       cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.positions.data_ptr(),
+                       self._decode_scratch.data_ptr(), out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,
+                       head_dim, float(scale), win, n_splits, max_pages, cache.k.shape[0], self._stream())
+            self.launches += 2
+            return
+        if fast and self.lib.hb_attention_prefill_supported(heads, kv_heads, head_dim):
+            q_blocks = sum((n + 63) // 64 for n in step.host_new)
+            self._call("hb_attention_prefill", qkv.data_ptr(), _rows(qkv, "attention queries"), cache.k.data_ptr(),
+                       cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(),
+                       out.data_ptr(), _rows(out, "attention output"), step.num_seqs, q_blocks, heads, kv_heads, head_dim,
+                       float(scale), win, cache.k.shape[0], self._stream())
+            self.launches += 1
+            return
         self._call("hb_attention_general", qkv.data_ptr(), _code(qkv), _rows(qkv, "attention queries"),
                    cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k), pt.data_ptr(), pt.shape[1],
                    step.tok_seq.data_ptr(), step.positions.data_ptr(), out.data_ptr(), _code(out),
-                   _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale),
-                   int(window) if window else 0, self._stream())
+                   _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale), win, self._stream())
         self.launches += 1
 
     # ------------------------------------------------------------------ sampling

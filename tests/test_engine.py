@@ -5,14 +5,15 @@ import pytest
 import torch
 
 import trace_tools as tt
-from conftest import TINY_A, TINY_B, require_gpu
+from conftest import TINY_A, TINY_B, TINY_C, TINY_D, require_gpu
 from plain_llama import PlainLlama
 
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-MODELS = ["strong_a", "strong_b", "paper_a", "paper_b"]
-VOCAB = {"a": TINY_A["vocab_size"], "b": TINY_B["vocab_size"]}
+MODELS = ["strong_a", "strong_b", "strong_c", "strong_d", "paper_a", "paper_b"]
+STRONG = ["strong_a", "strong_b", "strong_c", "strong_d"]
+VOCAB = {"a": TINY_A["vocab_size"], "b": TINY_B["vocab_size"], "c": TINY_C["vocab_size"], "d": TINY_D["vocab_size"]}
 
 
 def _plain(folder, dtype):
@@ -42,7 +43,7 @@ def test_whole_requests(model_folders, model, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("model", ["strong_a", "strong_b"])
+@pytest.mark.parametrize("model", STRONG)
 def test_last_tokens_one_by_one(model_folders, model, dtype):
     require_gpu()
     reqs = _requests(model, [33, 70, 100], seed=200)
@@ -53,7 +54,7 @@ def test_last_tokens_one_by_one(model_folders, model, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("model", ["strong_a", "strong_b"])
+@pytest.mark.parametrize("model", STRONG)
 def test_unequal_batches_with_slot_reuse(model_folders, model, dtype):
     require_gpu()
     v = VOCAB[model[-1]]
@@ -75,9 +76,9 @@ def test_unequal_batches_with_slot_reuse(model_folders, model, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding_across_pages(model_folders, dtype):
+@pytest.mark.parametrize("model", ["strong_b", "strong_c"])
+def test_long_decoding_across_pages(model_folders, model, dtype):
     require_gpu()
-    model = "strong_b"
     reqs = _requests(model, [200], seed=400)
     steps, peak = tt.trace_tail(reqs, tail=190)
     eng = _engine(model_folders[model], dtype, peak)
@@ -86,7 +87,7 @@ def test_long_decoding_across_pages(model_folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("model", ["strong_a", "strong_b"])
+@pytest.mark.parametrize("model", STRONG)
 def test_first_tokens(model_folders, model, dtype):
     require_gpu()
     reqs = _requests(model, [4, 2], seed=500)

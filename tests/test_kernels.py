@@ -78,7 +78,8 @@ def test_rope_table(ops):
 
 
 def _step(tok_seq, positions, tables):
-    return types.SimpleNamespace(tok_seq=tok_seq, positions=positions, page_tables=[tables])
+    return types.SimpleNamespace(tok_seq=tok_seq, positions=positions, page_tables=[tables], is_decode=False,
+                                 host_new=[], num_seqs=0, max_len=0)
 
 
 def _cache(n_pages, nkv, hd, dtype):
@@ -277,9 +278,64 @@ def test_attention_general(ops, dtype, nh, nkv, hd, window):
                              device=DEV)
     out = torch.empty(T, nh * hd, device=DEV, dtype=dtype)
     scale = 1.0 / math.sqrt(hd)
-    ops.attention(qkv, nh, nkv, hd, cache, _step(tok_seq, positions, tables), out, scale, window)
+    ops.use_fast_attention = False          # this test is about the general kernel
+    try:
+        ops.attention(qkv, nh, nkv, hd, cache, _step(tok_seq, positions, tables), out, scale, window)
+    finally:
+        ops.use_fast_attention = True
     ref = _attention_reference(q.double(), keys, values, lens_before, new, nh, nkv, hd, scale, window)
     assert _rel(out.view(T, nh, hd).cpu(), ref) < (2e-6 if dtype == torch.float32 else 2 ** -7)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, None), (3, 1, 64, None), (16, 1, 64, 100), (5, 5, 128, None),
+                                              (12, 4, 128, 65)])
+def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
+    """Split-K decode attention and flash prefill attention against the plain statement and the
+    general kernel: a batch with lengths at page edges, several splits, a window."""
+    torch.manual_seed(13)
+    dtype = torch.bfloat16
+    scale = 1.0 / math.sqrt(hd)
+    for lens_before, new in (([130, 0, 63, 300], [1, 1, 1, 1]), ([130, 0, 63, 5], [3, 70, 1, 129])):
+        total = [a + b for a, b in zip(lens_before, new)]
+        keys = [torch.randn(n, nkv, hd, dtype=torch.float64).to(dtype).double() for n in total]
+        values = [torch.randn(n, nkv, hd, dtype=torch.float64).to(dtype).double() for n in total]
+        cache = _cache(16, nkv, hd, dtype)
+        cache.k.normal_()            # stale contents of pages and page tails must not matter
+        cache.v.normal_()
+        tables = torch.tensor([[7, 1, 4, -1, -1], [3, 8, -1, -1, -1], [0, 15, -1, -1, -1], [9, 10, 11, 12, 13]],
+                              dtype=torch.int32, device=DEV)
+        for b, n in enumerate(total):
+            for s0 in range(0, n, 64):
+                page = int(tables[b, s0 // 64])
+                seg = slice(s0, min(n, s0 + 64))
+                cache.k[page, :, :seg.stop - s0] = keys[b][seg].to(dtype).transpose(0, 1).to(DEV)
+                cache.v[page, :, :seg.stop - s0] = values[b][seg].to(dtype).transpose(0, 1).to(DEV)
+        T = sum(new)
+        q = torch.randn(T, nh, hd, dtype=torch.float64).to(dtype)
+        qkv = torch.zeros(T, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
+        qkv[:, :nh * hd] = q.reshape(T, nh * hd).to(DEV)
+        step = _step(torch.tensor(sum(([b] * n for b, n in enumerate(new)), []), dtype=torch.int32, device=DEV),
+                     torch.tensor(sum((list(range(l, l + n)) for l, n in zip(lens_before, new)), []), dtype=torch.int32,
+                                  device=DEV), tables)
+        starts = [0]
+        for n in new:
+            starts.append(starts[-1] + n)
+        step.seq_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+        step.seq_pos0 = torch.tensor(lens_before, dtype=torch.int32, device=DEV)
+        step.is_decode = all(n == 1 for n in new)
+        step.host_new, step.num_seqs, step.max_len = new, len(new), max(total)
+        ref = _attention_reference(q.double(), keys, values, lens_before, new, nh, nkv, hd, scale, window)
+        for splits in ((None, 1, 3) if step.is_decode else (None,)):
+            out = torch.full((T, nh * hd), 9.0, device=DEV, dtype=dtype)
+            ops.attention(qkv, nh, nkv, hd, cache, step, out, scale, window, splits=splits)
+            assert _rel(out.view(T, nh, hd).cpu(), ref) < 2 ** -7, f"splits={splits} decode={step.is_decode}"
+        ops.use_fast_attention = False
+        try:
+            gen = torch.empty(T, nh * hd, device=DEV, dtype=dtype)
+            ops.attention(qkv, nh, nkv, hd, cache, step, gen, scale, window)
+        finally:
+            ops.use_fast_attention = True
+        assert _rel(out, gen.double()) < 2 ** -7
 
 
 def test_attention_finds_a_far_key(ops):
