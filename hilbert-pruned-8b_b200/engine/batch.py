@@ -47,14 +47,18 @@ class StepBatch:
     host_new: List[int]
     host_len: List[int]
     shared: Dict[str, Any] = field(default_factory=dict)
+    tag: str = ""               # suffix of buffers whose size follows the batch (captured steps keep their own)
 
 
 def _round4(n: int) -> int:
     return (n + 3) & ~3
 
 
-def build_step(entries: List[StepEntry], cache: CacheManager, workspace, device) -> StepBatch:
-    """Packs ``entries`` (already reserved in the cache) into device metadata."""
+def build_step(entries: List[StepEntry], cache: CacheManager, workspace, device, table_width: Optional[int] = None,
+               meta_name: str = "step.meta") -> StepBatch:
+    """Packs ``entries`` (already reserved in the cache) into device metadata.  A fixed
+    ``table_width`` (pages per page-table row) and a ``meta_name`` of its own give a layout
+    and addresses that stay the same from step to step, which a captured graph needs."""
     B = len(entries)
     new = [len(e.tokens) for e in entries]
     pos0 = [e.seq.length for e in entries]
@@ -62,7 +66,10 @@ def build_step(entries: List[StepEntry], cache: CacheManager, workspace, device)
     T = sum(new)
     n_want = sum(len(e.want) for e in entries)
     groups = cache.groups
-    widths = [max(1, max(pages_for(l) for l in lens)) for _ in groups]
+    need = max(1, max(pages_for(l) for l in lens))
+    if table_width is not None and table_width < need:
+        raise ValueError("step: the fixed page-table width is smaller than a sequence needs")
+    widths = [need if table_width is None else table_width for _ in groups]
 
     # layout of the packed int32 array (every segment starts on a 16-byte boundary)
     off: Dict[str, int] = {}
@@ -107,7 +114,7 @@ def build_step(entries: List[StepEntry], cache: CacheManager, workspace, device)
         a[off[f"pt{gi}"]: off[f"pt{gi}"] + B * w] = table.reshape(-1)
 
     cap = 1 << max(10, (total - 1).bit_length())
-    dev = workspace.buffer("step.meta", (cap,), torch.int32)[:total]
+    dev = workspace.buffer(meta_name, (cap,), torch.int32)[:total]
     dev.copy_(host, non_blocking=True)
 
     def seg(name: str, n: int) -> torch.Tensor:

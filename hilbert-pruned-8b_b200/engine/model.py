@@ -129,9 +129,9 @@ class DecoderModel:
         n = step.num_wanted
         if n == 0:
             return None
-        hn = ws.buffer("model.head_in", (n, H), self.ctx.dtype)
+        hn = ws.buffer("model.head_in" + step.tag, (n, H), self.ctx.dtype)
         self.final_norm.forward(x, hn, rows=step.want_rows)
-        logits = ws.buffer("model.logits", (n, V), torch.float32)
+        logits = ws.buffer("model.logits" + step.tag, (n, V), torch.float32)
         self.head.forward(hn, logits)
         return logits
 

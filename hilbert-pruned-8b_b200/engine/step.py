@@ -53,6 +53,11 @@ class Engine:
         self.model = DecoderModel(spec, self.ctx)
         self.cache: Optional[CacheManager] = None
         self._max_sequences = max_sequences
+        # decode steps (one token per sequence) are captured in CUDA graphs, one per
+        # (batch size, page-table width): a step is then one small copy and one graph launch
+        self.use_graphs = True
+        self._graphs: Dict[tuple, object] = {}
+        self.graph_replays = 0
         self.stop_token_ids = list(spec.stop_token_ids)
         self.vocab_size = spec.vocab_size
 
@@ -127,11 +132,50 @@ class Engine:
         The tensor is engine scratch: it is overwritten by the next step."""
         self.check_entries(entries)
         self.cache.reserve([(e.seq, e.seq.length + len(e.tokens)) for e in entries])
-        batch = build_step(entries, self.cache, self.workspace, self.device)
-        logits = self.model.forward(batch, self.cache)
+        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            logits, batch = self._decode_step(entries)
+        else:
+            batch = build_step(entries, self.cache, self.workspace, self.device)
+            logits = self.model.forward(batch, self.cache)
         for e, new_len in zip(entries, batch.host_len):
             self.cache.commit(e.seq, new_len)
         return logits
+
+    def _decode_step(self, entries: List[StepEntry]):
+        """A decode step through a captured graph.  The first step of a shape runs eagerly
+        (it also allocates every buffer), the second captures, later ones replay."""
+        from ..cache.manager import pages_for
+        B = len(entries)
+        need = max(pages_for(e.seq.length + 1) for e in entries)
+        width = 1 << (need - 1).bit_length()
+        key = (B, width)
+        batch = build_step(entries, self.cache, self.workspace, self.device, table_width=width,
+                           meta_name=f"step.meta.decode.{B}.{width}")
+        batch.max_len = width * 64          # kernel launch shapes depend on the bucket only
+        batch.tag = f".decode.{B}"
+        state = self._graphs.get(key)
+        if state is None:
+            self._graphs[key] = "warm"
+            return self.model.forward(batch, self.cache), batch
+        if state == "warm":
+            ops = self.ctx.ops
+            torch.cuda.synchronize(self.device)
+            before = ops.launches
+            graph = torch.cuda.CUDAGraph()
+            self.workspace.capturing = True
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self.model.forward(batch, self.cache)
+            finally:
+                self.workspace.capturing = False
+            state = (graph, logits, ops.launches - before)
+            ops.launches = before
+            self._graphs[key] = state
+        graph, logits, launches = state
+        graph.replay()
+        self.ctx.ops.launches += launches
+        self.graph_replays += 1
+        return logits, batch
 
     def step_chunked(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
         """``step`` for any number of tokens: a step larger than the step capacity is cut into

@@ -15,7 +15,8 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._buffers: Dict[str, torch.Tensor] = {}
-        self.frozen = False  # set while CUDA graphs that captured these addresses are alive
+        self.capturing = False      # set while a CUDA graph is being captured
+        self._pinned = set()        # buffers whose addresses a captured graph holds: they must not move
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         numel = 1
@@ -23,8 +24,12 @@ class Workspace:
             numel *= int(s)
         key = f"{name}|{dtype}"
         flat = self._buffers.get(key)
+        if self.capturing:
+            if flat is None or flat.numel() < numel:
+                raise RuntimeError(f"workspace: buffer {name} would be allocated inside a graph capture")
+            self._pinned.add(key)
         if flat is None or flat.numel() < numel:
-            if self.frozen and flat is not None:
+            if key in self._pinned:
                 raise RuntimeError(f"workspace: buffer {name} would move while a captured graph uses it")
             flat = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._buffers[key] = flat

@@ -114,6 +114,7 @@ class Ops:
         self._splitk_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
         # split-K decode attention scratch: partial outputs with their maxima and sums
         self._decode_scratch = torch.empty(4 << 20, dtype=torch.float32, device=self.device)
+        self._retired = []              # outgrown scratch, kept alive for graphs that captured it
         self.use_fast_attention = True  # tests switch this off to compare with the general kernel
 
     # ------------------------------------------------------------------ plumbing
@@ -236,8 +237,10 @@ class Ops:
             need = self.lib.hb_gemm_tc_scratch_floats(M, N, splits)
             tiles = self.lib.hb_gemm_tc_tiles(M, N)
             if need > self._splitk_partials.numel():
+                self._retired.append(self._splitk_partials)     # a captured graph may still write there
                 self._splitk_partials = torch.empty(need, dtype=torch.float32, device=self.device)
             if tiles > self._splitk_counters.numel():
+                self._retired.append(self._splitk_counters)
                 self._splitk_counters = torch.zeros(tiles, dtype=torch.int32, device=self.device)
             partials, counters = self._splitk_partials.data_ptr(), self._splitk_counters.data_ptr()
         self._call("hb_gemm_tc", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), _rows(w, "linear weight"),
@@ -300,6 +303,7 @@ class Ops:
             n_splits = max(1, min(n_splits, max_pages))
             need = self.lib.hb_attention_decode_scratch_floats(T, heads, head_dim, n_splits)
             if need > self._decode_scratch.numel():
+                self._retired.append(self._decode_scratch)
                 self._decode_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
             self._call("hb_attention_decode", qkv.data_ptr(), _rows(qkv, "attention queries"), cache.k.data_ptr(),
                        cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.positions.data_ptr(),
