@@ -46,6 +46,7 @@ class StepBatch:
     is_decode: bool
     host_new: List[int]
     host_len: List[int]
+    host_state_slots: List[int] = field(default_factory=list)
     shared: Dict[str, Any] = field(default_factory=dict)
     tag: str = ""               # suffix of buffers whose size follows the batch (captured steps keep their own)
 
@@ -127,4 +128,4 @@ def build_step(entries: List[StepEntry], cache: CacheManager, workspace, device,
         state_slots=seg("state_slots", B), want_rows=seg("want", n_want) if n_want else None,
         page_tables=[seg(f"pt{gi}", B * w).view(B, w) for gi, w in enumerate(widths)],
         max_new=max(new), max_len=max(lens), is_decode=all(n == 1 for n in new),
-        host_new=new, host_len=lens)
+        host_new=new, host_len=lens, host_state_slots=[e.seq.state_slot for e in entries])

@@ -38,6 +38,7 @@ class DecoderModel:
         self.final_norm = NORMS.build(spec.final_norm, ctx)
         self.head = HEADS.build(spec.head, ctx)
         self.prefix = spec.weight_prefixes[-1]
+        self.graph_safe = all(getattr(part, "graph_safe", True) for _, part in self.named_parts())
 
     # ------------------------------------------------------------------ weights
     def named_parts(self) -> List[Tuple[str, object]]:

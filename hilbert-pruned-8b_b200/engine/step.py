@@ -132,7 +132,7 @@ class Engine:
         The tensor is engine scratch: it is overwritten by the next step."""
         self.check_entries(entries)
         self.cache.reserve([(e.seq, e.seq.length + len(e.tokens)) for e in entries])
-        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        if self.use_graphs and self.model.graph_safe and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             logits, batch = self._decode_step(entries)
         else:
             batch = build_step(entries, self.cache, self.workspace, self.device)

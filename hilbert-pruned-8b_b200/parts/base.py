@@ -20,6 +20,8 @@ What a part must provide:
 * feed-forwards: ``forward(h, residual, step)``, adding likewise.
 * norms: ``forward(x, out, rows=None)``.
 * position encodings: ``prepare(step)`` once per step and whatever ``apply`` its mixer calls.
+* ``graph_safe`` (class attribute, default True): whether ``forward`` only enqueues work on
+  the current stream, so that a decode step can be captured in a CUDA graph.
 """
 from __future__ import annotations
 
@@ -79,6 +81,10 @@ class BuildContext:
 
 
 class Part:
+    # False for a part whose forward reads device values on the host or allocates: the engine
+    # then runs its decode steps eagerly instead of replaying a captured CUDA graph
+    graph_safe = True
+
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         self.spec = spec
         self.ctx = ctx
