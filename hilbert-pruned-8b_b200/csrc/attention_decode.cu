@@ -294,3 +294,52 @@ extern "C" int hb_attention_decode(const void* q, long long q_stride, const void
     return launch_decode<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride, batch,
                              n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+// See noalloc.h.  The scratch of the split-K kernels is this file-scope device array.  In
+// host code the array's name is only a handle: its device address comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+#include <mutex>
+
+#include "noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[HB_NOALLOC_SCRATCH_FLOATS];
+static float* g_noalloc_address[64];
+static std::mutex g_noalloc_mutex;
+
+static int noalloc_scratch_address(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return hb_fail("attention_decode_noalloc: no current device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return hb_fail("attention_decode_noalloc: device index %d is not supported", dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_address[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return hb_fail("attention_decode_noalloc: cannot find the scratch array on device %d: %s", dev,
+                           cudaGetErrorString(e));
+        g_noalloc_address[dev] = p;
+    }
+    *out = g_noalloc_address[dev];
+    return 0;
+}
+
+extern "C" int hb_attention_decode_noalloc(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                           const int* page_table, int pt_width, const int* positions, void* out,
+                                           long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim,
+                                           float scale, int window, int splits, int max_pages, int n_pages,
+                                           void* stream) {
+    if (batch == 0) return 0;
+    HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && n_heads > 0, "attention_decode_noalloc: bad sizes");
+    const int used_splits = splits > max_pages ? max_pages : splits;
+    const long long need = hb_attention_decode_scratch_floats(batch, n_heads, head_dim, used_splits);
+    HB_REQUIRE(need <= (long long)HB_NOALLOC_SCRATCH_FLOATS,
+               "attention_decode_noalloc: batch %d x %d heads x %d splits needs %lld scratch floats, the built-in area "
+               "holds %d; lower the batch or the splits, or use hb_attention_decode with scratch of your own",
+               batch, n_heads, used_splits, need, (int)HB_NOALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (noalloc_scratch_address(&scratch)) return 1;
+    return hb_attention_decode(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride,
+                               batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
+}
