@@ -23,6 +23,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
                    const int* __restrict__ page_table, int pt_width, const int* __restrict__ positions,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, float scale_log2e,
                    int window, int pages_per_split, int n_pages) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int ROW_BYTES = HD * 2;
     constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;        // one page of K (or V) of one kv head
     constexpr int CHUNKS = ROW_BYTES / 16;
@@ -213,6 +215,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
 template <typename TO>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            TO* __restrict__ out, long long out_stride, int nh, int hd, int S) {
+    pdl_trigger();
+    pdl_wait();
     const int b = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)b * nh + head) * S;
     float M = -INFINITY;
@@ -260,12 +264,12 @@ static int launch_decode(const void* q, long long q_stride, const void* kc, cons
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)batch * nh * splits * HD;
     dim3 grid(splits, nkv, batch);
-    attn_decode_kernel<HD><<<grid, AD_THREADS, SMEM, s>>>((const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
+    hb_launch(attn_decode_kernel<HD>, dim3(grid), dim3(AD_THREADS), SMEM, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
                                                           pt_width, positions, part_o, part_ml, nh, nkv, scale * AD_LOG2E,
                                                           window, pages_per_split, n_pages);
     if (hb_check_launch("attention_decode")) return 1;
     dim3 cgrid(batch, nh);
-    attn_decode_combine_kernel<bf16><<<cgrid, HD, 0, s>>>(part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
+    hb_launch(attn_decode_combine_kernel<bf16>, dim3(cgrid), dim3(HD), 0, s, part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
     return hb_check_launch("attention_decode_combine");
 }
 

@@ -19,6 +19,8 @@ attention_general_kernel(const TQ* __restrict__ q, long long q_stride, const TC*
                          const TC* __restrict__ v_cache, const int* __restrict__ page_table, int pt_width,
                          const int* __restrict__ tok_seq, const int* __restrict__ positions, TO* __restrict__ out,
                          long long out_stride, int nh, int nkv, int hd, float scale, int window) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float qs[AG_MAX_HD];
     __shared__ float ps[AG_THREADS];
     __shared__ int pages[AG_THREADS / HB_PAGE_TOKENS + 2];
@@ -106,7 +108,7 @@ extern "C" int hb_attention_general(const void* q, int q_dtype, long long q_stri
     dim3 grid(n_tokens, n_heads);
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_AG_LAUNCH(TQ, TC, TO)                                                                                      \
-    attention_general_kernel<TQ, TC, TO><<<grid, AG_THREADS, 0, s>>>(                                                 \
+    hb_launch(attention_general_kernel<TQ, TC, TO>, dim3(grid), dim3(AG_THREADS), 0, s,                                                  \
         (const TQ*)q, q_stride, (const TC*)k_cache, (const TC*)v_cache, page_table, pt_width, tok_seq, positions,     \
         (TO*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window)
     if (q_dtype == HB_F32 && cache_dtype == HB_F32 && out_dtype == HB_F32) HB_AG_LAUNCH(float, float, float);

@@ -24,6 +24,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
                     const int* __restrict__ page_table, int pt_width, const int* __restrict__ seq_start,
                     const int* __restrict__ seq_pos0, bf16* __restrict__ out, long long out_stride, int n_seqs, int nh,
                     int nkv, float scale_log2e, int window, int n_pages) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int ROW_BYTES = HD * 2;
     constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;
     constexpr int CHUNKS = ROW_BYTES / 16;
@@ -216,7 +218,7 @@ static int launch_prefill(const void* q, long long q_stride, const void* kc, con
         attr_set = true;
     }
     dim3 grid(q_blocks, nh);
-    attn_prefill_kernel<HD><<<grid, AP_THREADS, SMEM, s>>>((const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
+    hb_launch(attn_prefill_kernel<HD>, dim3(grid), dim3(AP_THREADS), SMEM, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
                                                            pt_width, seq_start, seq_pos0, (bf16*)out, out_stride, n_seqs, nh, nkv,
                                                            scale * AP_LOG2E, window, n_pages);
     return hb_check_launch("attention_prefill");

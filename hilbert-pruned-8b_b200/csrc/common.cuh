@@ -22,6 +22,33 @@ int hb_check_launch(const char* what);
 
 typedef __nv_bfloat16 bf16;
 
+// Programmatic dependent launch.  Every kernel of the library is launched with the
+// "programmatic stream serialization" attribute, so it may be scheduled while the kernel
+// before it in the stream is still running; it calls pdl_wait() before it touches anything
+// that kernel may have written (for most kernels: first thing) and pdl_trigger() to let the
+// kernel after it be scheduled early in turn.  What runs before pdl_wait() may only read
+// memory that no kernel of a step writes (weights) and set up on-chip state.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool hb_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t hb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = hb_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 

@@ -10,6 +10,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out,
                              int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= vocab) tok = 0;  // the host checked the range; never read outside the table
@@ -24,9 +26,9 @@ extern "C" int hb_embed(const int* tokens, const void* table, int table_dtype, f
     HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == HB_BF16)
-        embed_kernel<bf16><<<n_tokens, 256, 0, s>>>(tokens, (const bf16*)table, out, hidden, vocab);
+        hb_launch(embed_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, out, hidden, vocab);
     else if (table_dtype == HB_F32)
-        embed_kernel<float><<<n_tokens, 256, 0, s>>>(tokens, (const float*)table, out, hidden, vocab);
+        hb_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, out, hidden, vocab);
     else
         return hb_fail("embed: unsupported table dtype %d", table_dtype);
     return hb_check_launch("embed");
@@ -39,6 +41,8 @@ extern "C" int hb_embed(const int* tokens, const void* table, int table_dtype, f
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, float offset,
                                TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -61,9 +65,9 @@ extern "C" int hb_rmsnorm(const float* x, const float* weight, float eps, float 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 2048 ? 512 : 256;
     if (out_dtype == HB_BF16)
-        rmsnorm_kernel<bf16><<<n_rows, threads, 0, s>>>(x, weight, eps, offset, (bf16*)out, rows, hidden);
+        hb_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, x, weight, eps, offset, (bf16*)out, rows, hidden);
     else if (out_dtype == HB_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>(x, weight, eps, offset, (float*)out, rows, hidden);
+        hb_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, x, weight, eps, offset, (float*)out, rows, hidden);
     else
         return hb_fail("rmsnorm: unsupported output dtype %d", out_dtype);
     return hb_check_launch("rmsnorm");
@@ -74,6 +78,8 @@ extern "C" int hb_rmsnorm(const float* x, const float* weight, float eps, float 
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, long long in_stride, TO* __restrict__ out,
                                 long long out_stride, int inter) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= inter) return;
@@ -89,11 +95,11 @@ extern "C" int hb_silu_mul(const void* gate_up, int in_dtype, long long in_strid
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_rows, (inter + 255) / 256);
     if (in_dtype == HB_BF16 && out_dtype == HB_BF16)
-        silu_mul_kernel<bf16, bf16><<<grid, 256, 0, s>>>((const bf16*)gate_up, in_stride, (bf16*)out, out_stride, inter);
+        hb_launch(silu_mul_kernel<bf16, bf16>, dim3(grid), dim3(256), 0, s, (const bf16*)gate_up, in_stride, (bf16*)out, out_stride, inter);
     else if (in_dtype == HB_F32 && out_dtype == HB_F32)
-        silu_mul_kernel<float, float><<<grid, 256, 0, s>>>((const float*)gate_up, in_stride, (float*)out, out_stride, inter);
+        hb_launch(silu_mul_kernel<float, float>, dim3(grid), dim3(256), 0, s, (const float*)gate_up, in_stride, (float*)out, out_stride, inter);
     else if (in_dtype == HB_F32 && out_dtype == HB_BF16)
-        silu_mul_kernel<float, bf16><<<grid, 256, 0, s>>>((const float*)gate_up, in_stride, (bf16*)out, out_stride, inter);
+        hb_launch(silu_mul_kernel<float, bf16>, dim3(grid), dim3(256), 0, s, (const float*)gate_up, in_stride, (bf16*)out, out_stride, inter);
     else
         return hb_fail("silu_mul: unsupported dtypes %d -> %d", in_dtype, out_dtype);
     return hb_check_launch("silu_mul");
@@ -104,6 +110,8 @@ extern "C" int hb_silu_mul(const void* gate_up, int in_dtype, long long in_strid
 // (cpu_backend.c:88-93; cuda_backend.cu:232-236).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float2* __restrict__ out, int n_tokens, int half) {
+    pdl_trigger();
+    pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_tokens * half) return;
     const int t = idx / half, i = idx - t * half;
@@ -118,7 +126,7 @@ extern "C" int hb_rope_table(const int* positions, const float* inv_freq, float*
     if (n_tokens == 0 || half == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && half > 0, "rope_table: bad sizes");
     const long long n = (long long)n_tokens * half;
-    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, (float2*)out,
+    hb_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, positions, inv_freq, (float2*)out,
                                                                                    n_tokens, half);
     return hb_check_launch("rope_table");
 }
@@ -134,6 +142,8 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride,
                                       TC* __restrict__ v_cache, const int* __restrict__ page_table, int pt_width,
                                       const int* __restrict__ tok_seq, const int* __restrict__ positions,
                                       int n_pages) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x, slot = blockIdx.y;
     const int half = rot >> 1;
     T* row = qkv + (size_t)t * qkv_stride;
@@ -186,11 +196,11 @@ extern "C" int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride,
     cudaStream_t s = (cudaStream_t)stream;
     const float2* tab = (const float2*)table;
     if (qkv_dtype == HB_BF16 && cache_dtype == HB_BF16)
-        rope_kv_append_kernel<bf16, bf16><<<grid, threads, 0, s>>>((bf16*)qkv, qkv_stride, tab, rot, n_heads, n_kv_heads,
+        hb_launch(rope_kv_append_kernel<bf16, bf16>, dim3(grid), dim3(threads), 0, s, (bf16*)qkv, qkv_stride, tab, rot, n_heads, n_kv_heads,
                                                                     head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table,
                                                                     pt_width, tok_seq, positions, n_pages);
     else if (qkv_dtype == HB_F32 && cache_dtype == HB_F32)
-        rope_kv_append_kernel<float, float><<<grid, threads, 0, s>>>((float*)qkv, qkv_stride, tab, rot, n_heads,
+        hb_launch(rope_kv_append_kernel<float, float>, dim3(grid), dim3(threads), 0, s, (float*)qkv, qkv_stride, tab, rot, n_heads,
                                                                       n_kv_heads, head_dim, (float*)k_cache,
                                                                       (float*)v_cache, page_table, pt_width, tok_seq,
                                                                       positions, n_pages);

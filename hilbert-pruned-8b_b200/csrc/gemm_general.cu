@@ -21,6 +21,8 @@ template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_general_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long ldw,
                     TO* __restrict__ C, long long ldc, int M, int N, int K, int accumulate) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[GB_K][GB_M + 4];
     __shared__ float Ws[GB_K][GB_N + 4];
     const int tid = threadIdx.x;
@@ -79,10 +81,10 @@ static int launch_out(const void* a, long long lda, const void* w, long long ldw
     dim3 grid((N + GB_N - 1) / GB_N, (M + GB_M - 1) / GB_M);
     if (grid.y > 65535) return hb_fail("gemm_general: %d rows are too many for one call", M);
     if (out_dtype == HB_F32)
-        gemm_general_kernel<TA, TW, float><<<grid, 256, 0, s>>>((const TA*)a, lda, (const TW*)w, ldw, (float*)out, ldc, M,
+        hb_launch(gemm_general_kernel<TA, TW, float>, dim3(grid), dim3(256), 0, s, (const TA*)a, lda, (const TW*)w, ldw, (float*)out, ldc, M,
                                                                  N, K, accumulate);
     else if (out_dtype == HB_BF16)
-        gemm_general_kernel<TA, TW, bf16><<<grid, 256, 0, s>>>((const TA*)a, lda, (const TW*)w, ldw, (bf16*)out, ldc, M, N,
+        hb_launch(gemm_general_kernel<TA, TW, bf16>, dim3(grid), dim3(256), 0, s, (const TA*)a, lda, (const TW*)w, ldw, (bf16*)out, ldc, M, N,
                                                                 K, accumulate);
     else
         return hb_fail("gemm_general: unsupported output dtype %d", out_dtype);

@@ -173,16 +173,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            int armed = 0;
-            for (int i = 0; i < nkb; i++) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                if (*abort_flag || !mbar_wait(empty0 + 8 * s, ph ^ 1)) {
-                    if (!*abort_flag) { atomicExch(error_flag, 1); *abort_flag = 1; }
+            int armed = 0, s = 0;
+            uint32_t ph = 0;
+            // The weights are written by no kernel of a step: the first stages' weight tiles are
+            // requested before waiting for the kernel in front, whose output is only the
+            // activation operand.
+            const int early = min(nkb, STAGES);
+            for (int i = 0; i < early; i++) {
+                const uint32_t stage = smem_base + i * L::STAGE_BYTES;
+                const int k = (kb0 + i) * TC_BK;
+                mbar_expect_tx(full0 + 8 * i, L::STAGE_BYTES);
+                tma_load_2d(stage, &map_w, full0 + 8 * i, k, n0);
+                if (DUAL) tma_load_2d(stage + L::W_BYTES, &map_w, full0 + 8 * i, k, up_row0 + n0);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; i++)
+                tma_load_2d(smem_base + i * L::STAGE_BYTES + L::W_BYTES * (DUAL ? 2 : 1), &map_a, full0 + 8 * i,
+                            (kb0 + i) * TC_BK, m0);
+            armed = early;
+            if (early == STAGES) ph = 1; else s = early;
+            for (int i = early; i < nkb; i++) {
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) {
+                    atomicExch(error_flag, 1);
+                    *abort_flag = 1;
                     break;
                 }
                 const uint32_t stage = smem_base + s * L::STAGE_BYTES;
@@ -192,6 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (DUAL) tma_load_2d(stage + L::W_BYTES, &map_w, full0 + 8 * s, k, up_row0 + n0);
                 tma_load_2d(stage + L::W_BYTES * (DUAL ? 2 : 1), &map_a, full0 + 8 * s, k, m0);
                 armed = i + 1;
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             // copies in flight must land before the CTA may exit: wait (bounded) for the
             // stages armed last; a stage the MMA thread already consumed answers at once
@@ -200,28 +219,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
+        // One thread issues every MMA of the tile, so its instruction stream is the critical
+        // path for few-token tiles: descriptors are advanced with one 32-bit add per MMA
+        // (the high word is constant) and nothing else is recomputed inside the loop.
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16(BN);
-            bool ok = true;
-            for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
-                if (*abort_flag || !mbar_wait(full0 + 8 * s, ph)) {
-                    if (!*abort_flag) { atomicExch(error_flag, 3); *abort_flag = 1; }
-                    ok = false;
+            const uint64_t desc0 = smem_desc_sw128(smem_base);
+            const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
+            constexpr uint32_t STAGE_STEP = L::STAGE_BYTES >> 4, A_OFF = (L::W_BYTES * (DUAL ? 2 : 1)) >> 4,
+                               UP_OFF = L::W_BYTES >> 4;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int i = 0; i < nkb; i++) {
+                if (!mbar_wait(full0 + 8 * s, ph)) {
+                    atomicExch(error_flag, 3);
+                    *abort_flag = 1;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t stage = smem_base + s * L::STAGE_BYTES;
-                const uint32_t a_addr = stage + L::W_BYTES * (DUAL ? 2 : 1);
+                const uint32_t w_lo = desc_lo0 + s * STAGE_STEP;
 #pragma unroll
                 for (int kk = 0; kk < TC_BK / 16; kk++) {
-                    const uint64_t bdesc = smem_desc_sw128(a_addr + kk * 32);
-                    const uint32_t acc = (i > 0 || kk > 0) ? 1u : 0u;
-                    umma_bf16(tmem_base, smem_desc_sw128(stage + kk * 32), bdesc, idesc, acc);
-                    if (DUAL) umma_bf16(tmem_base + BN, smem_desc_sw128(stage + L::W_BYTES + kk * 32), bdesc, idesc, acc);
+                    const uint64_t wdesc = ((uint64_t)desc_hi << 32) | (w_lo + 2 * kk);
+                    const uint64_t tdesc = ((uint64_t)desc_hi << 32) | (w_lo + A_OFF + 2 * kk);
+                    const uint32_t acc = (i | kk) ? 1u : 0u;
+                    umma_bf16(tmem_base, wdesc, tdesc, idesc, acc);
+                    if (DUAL) umma_bf16(tmem_base + BN, ((uint64_t)desc_hi << 32) | (w_lo + UP_OFF + 2 * kk), tdesc, idesc, acc);
                 }
                 umma_commit(empty0 + 8 * s);      // frees the stage when these MMAs have read it
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             umma_commit(accum);                    // arrives when every MMA above has finished
         }
@@ -230,6 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;                    // TMEM lane quarter this warp may read
         const int f = n0 + q * 32 + lane;          // feature of this thread
         bool ok = true;
+        pdl_wait();                                // the output, the scratch and the counters belong to earlier kernels until now
         if (!mbar_wait(accum, 0)) {
             atomicExch(error_flag, 4);
             *abort_flag = 1;
@@ -359,7 +386,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, lo
         attr_set = true;
     }
     dim3 grid((M + BN - 1) / BN, (N + TC_BM - 1) / TC_BM, splits);
-    gemm_tc_kernel<BN, MODE, STAGES><<<grid, TC_THREADS, SMEM, s>>>(mw, ma, out, ldc, M, N, K, up_row0, partials, counters, error_flag);
+    hb_launch(gemm_tc_kernel<BN, MODE, STAGES>, dim3(grid), dim3(TC_THREADS), SMEM, s, mw, ma, out, ldc, M, N, K, up_row0, partials, counters, error_flag);
     return hb_check_launch("gemm_tc");
 }
 
@@ -368,7 +395,7 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& ma, voi
                        int up_row0, int splits, float* partials, int* counters, int* error_flag, cudaStream_t s) {
     constexpr bool DUAL = MODE == TC_SWIGLU_BF16;
     switch (bn) {
-        case 16: return launch_tc<16, MODE, DUAL ? 6 : 8>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
+        case 16: return launch_tc<16, MODE, DUAL ? 6 : 12>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
         case 32: return launch_tc<32, MODE, DUAL ? 5 : 8>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
         case 64: return launch_tc<64, MODE, DUAL ? 5 : 8>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
         case 128: return launch_tc<128, MODE, DUAL ? 4 : 6>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);

@@ -1,6 +1,7 @@
 // Error reporting and device queries of the kernel library.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "api.h"
 #include "common.cuh"
@@ -22,6 +23,16 @@ int hb_check_launch(const char* what) {
         return hb_fail("%s: launch failed: %s", what, cudaGetErrorString(e));
     }
     return 0;
+}
+
+// HILBERT_B200_PDL=0 launches every kernel fully serialised (for debugging).
+bool hb_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("HILBERT_B200_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
 }
 
 extern "C" const char* hb_last_error(void) { return g_error; }

@@ -64,6 +64,8 @@ __device__ __forceinline__ void argmax_row(const float* __restrict__ row, int vo
 
 __global__ void __launch_bounds__(SM_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ out, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sval[33];
     __shared__ int sidx[33];
     int idx;
@@ -76,6 +78,8 @@ __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(const float* __restrict__ logits, long long stride, const float* __restrict__ temperature,
               const long long* __restrict__ seeds, const long long* __restrict__ request_ids,
               const long long* __restrict__ steps, int* __restrict__ out, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sval[33];
     __shared__ int sidx[33];
     __shared__ float prefix[SM_THREADS];
@@ -127,7 +131,7 @@ sample_kernel(const float* __restrict__ logits, long long stride, const float* _
 extern "C" int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, void* stream) {
     if (n_rows == 0) return 0;
     HB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
-    argmax_kernel<<<n_rows, SM_THREADS, 0, (cudaStream_t)stream>>>(logits, stride, out, vocab);
+    hb_launch(argmax_kernel, dim3(n_rows), dim3(SM_THREADS), 0, (cudaStream_t)stream, logits, stride, out, vocab);
     return hb_check_launch("argmax");
 }
 
@@ -136,7 +140,7 @@ extern "C" int hb_sample(const float* logits, long long stride, const float* tem
                          void* stream) {
     if (n_rows == 0) return 0;
     HB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "sample: bad sizes");
-    sample_kernel<<<n_rows, SM_THREADS, 0, (cudaStream_t)stream>>>(logits, stride, temperature, seeds, request_ids,
+    hb_launch(sample_kernel, dim3(n_rows), dim3(SM_THREADS), 0, (cudaStream_t)stream, logits, stride, temperature, seeds, request_ids,
                                                                    steps, out, vocab);
     return hb_check_launch("sample");
 }
