@@ -315,15 +315,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     for (int j = 0; j < 16; j++) v[j] = u[j] = 0.0f;
                 }
                 if (f < N) {
+                    if (MODE == TC_ADD_F32) {
+                        // all loads of the residual first, then the stores: written one by one the
+                        // compiler must keep each load behind the store before it (they may alias)
+                        float r[16];
+                        float* po = (float*)out + (size_t)(m0 + c) * ldc + f;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int m = m0 + c + j;
-                        if (m < M) {
-                            const size_t o = (size_t)m * ldc + f;
-                            if (MODE == TC_STORE_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(v[j]);
-                            else if (MODE == TC_STORE_F32) ((float*)out)[o] = v[j];
-                            else if (MODE == TC_ADD_F32) ((float*)out)[o] += v[j];
-                            else ((bf16*)out)[o] = __float2bfloat16_rn(silu_f32(v[j]) * u[j]);
+                        for (int j = 0; j < 16; j++) r[j] = (m0 + c + j < M) ? __ldcg(po + (size_t)j * ldc) : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (m0 + c + j < M) po[(size_t)j * ldc] = r[j] + v[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int m = m0 + c + j;
+                            if (m < M) {
+                                const size_t o = (size_t)m * ldc + f;
+                                if (MODE == TC_STORE_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(v[j]);
+                                else if (MODE == TC_STORE_F32) ((float*)out)[o] = v[j];
+                                else ((bf16*)out)[o] = __float2bfloat16_rn(silu_f32(v[j]) * u[j]);
+                            }
                         }
                     }
                 }

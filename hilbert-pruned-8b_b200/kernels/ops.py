@@ -280,8 +280,10 @@ class Ops:
 
     # ------------------------------------------------------------------ attention
     def decode_splits_for(self, batch: int, kv_heads: int, max_pages: int) -> int:
-        """Key splits of decode attention so that about two CTAs per SM stream the cache."""
-        return max(1, min(max_pages, -(-2 * self.sm_count // max(1, batch * kv_heads))))
+        """Key splits of decode attention: at most two CTAs per SM in one wave, at least eight
+        pages per split, at most 16 splits (measured: more splits cost more in the combine
+        than they gain)."""
+        return max(1, min(2 * self.sm_count // max(1, batch * kv_heads), -(-max_pages // 8), 16))
 
     def attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out, scale: float,
                   window: Optional[int], splits: Optional[int] = None) -> None:
