@@ -27,11 +27,11 @@ int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride, const floa
 int hb_gemm_general(const void* a, int a_dtype, long long lda, const void* w, int w_dtype, long long ldw,
                     void* out, int out_dtype, long long ldc, int M, int N, int K, int accumulate, void* stream);
 int hb_gemm_tc_token_tile(int M);
-long long hb_gemm_tc_scratch_floats(int M, int N, int splits);
-long long hb_gemm_tc_tiles(int M, int N);
+long long hb_gemm_tc_scratch_floats(int M, int N, int K, int mode, int schedule);
+long long hb_gemm_tc_tiles(int M, int N, int mode);
 int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,
-               int M, int N, int K, int mode, int up_row0, int splits, float* partials, int* tile_counters,
-               int* error_flag, void* stream);
+               int M, int N, int K, int mode, int up_row0, int schedule, float* partials, long long partials_capacity,
+               int* tile_counters, long long counters_capacity, int* error_flag, void* stream);
 int hb_attention_general(const void* q, int q_dtype, long long q_stride, const void* k_cache, const void* v_cache,
                          int cache_dtype, const int* page_table, int pt_width, const int* tok_seq,
                          const int* positions, void* out, int out_dtype, long long out_stride, int n_tokens,

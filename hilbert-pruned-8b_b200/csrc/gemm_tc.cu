@@ -3,25 +3,32 @@
 // kernel and its few-row kernel (cleanroom-transformer/src/cuda_backend.cu:93-177) for
 // prefill and for decode alike.
 //
-// Orientation.  The weight tile is the M operand of the MMA (128 output features on the
-// 128 TMEM lanes) and the tokens are its N operand (16..256 columns).  A decode step with a
-// handful of tokens therefore streams each weight exactly once through a 128 x 64 tile
-// pipeline with an N of 16, and a prefill step uses the same kernel with N = 256.
+// Orientation.  The weight tile is the M operand of the MMA (128 weight rows on the 128 TMEM
+// lanes) and the tokens are its N operand (16..256 columns).  A decode step with a handful
+// of tokens streams each weight exactly once through a 128 x 64 tile pipeline with an N of
+// 16; a prefill step uses the same kernel with N = 256.
 //
-// One CTA = one (token tile, feature tile[, K split]).  192 threads:
+// Persistent CTAs (one per SM), 192 threads each:
 //   warp 0     TMA producer: one thread arms full[s] with the stage's byte count and issues
-//              the tile loads (cp.async.bulk.tensor, 128-byte swizzle, zero fill outside)
+//              the tile loads (cp.async.bulk.tensor, 128-byte swizzle, zero fill outside);
+//              it runs ahead across work items, so the pipeline never drains between tiles
 //   warp 1     allocates tensor memory; one thread issues tcgen05.mma (K = 16 per
-//              instruction, 4 per 64-wide stage) and commits to empty[s] / accum
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (lane = feature, column = token) and
-//              store / add to the residual / apply SiLU(gate) * up
+//              instruction, 4 per 64-wide stage) into one of two accumulator buffers and
+//              commits to empty[s] / acc_full[buffer]
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (lane = weight row, column = token),
+//              write the result, hand the buffer back (acc_empty) -- while the MMA thread
+//              already fills the other buffer with the next work item
 // Epilogues: STORE (bf16 or f32), ADD (f32 residual += acc; the reference's fused residual
-// add, cuda_backend.cu:130,807), SWIGLU (two accumulators, gate and up rows of the same
-// features; the reference's fused decode kernel, cuda_backend.cu:551-559).
+// add, cuda_backend.cu:130,807), SWIGLU (the tile's 128 weight rows are 64 gate rows and
+// the 64 up rows of the same features; the epilogue pairs lanes i and i + 64 through shared
+// memory; the reference's fused decode kernel, cuda_backend.cu:551-559).
 //
-// Split-K (decode only): grid.z CTAs each reduce a K range into float32 partial tiles in a
-// scratch buffer; the last CTA of a tile to finish (a counter per tile) adds the partials in
-// split order and runs the epilogue, so the sum order is fixed.
+// Work split.  Many-token products: output tiles round-robin over the CTAs.  Few-token
+// products (one token tile, decode): stream-K -- the (tile, K block) space is cut into one
+// contiguous range per CTA, so every SM streams the same number of weight bytes; a CTA that
+// holds only part of a tile's K range writes a float32 partial tile to scratch, and the last
+// contributor of a tile (a counter per tile) adds the partials in K order and runs the
+// epilogue, so the sum order is fixed.
 //
 // Every wait is bounded: a wait that runs out sets *error_flag, the CTA stops issuing work,
 // waits (bounded) for its own copies in flight, frees its tensor memory and returns.
@@ -48,6 +55,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -120,49 +130,127 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 }
 
-template <int BN, bool DUAL>
+template <int BN, int MODE>
 struct TcLayout {
-    static constexpr int W_BYTES = TC_BM * TC_BK * 2;                 // 16 KB
+    static constexpr bool SWIGLU = MODE == TC_SWIGLU_BF16;
+    static constexpr int FEAT = SWIGLU ? 64 : TC_BM;                   // output features per tile
+    static constexpr int W_BYTES = TC_BM * TC_BK * 2;                  // 16 KB: 128 weight rows
     static constexpr int A_BYTES = BN * TC_BK * 2;
-    static constexpr int STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + A_BYTES;
-    static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
-    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+    static constexpr int NBUF = 2;                                     // accumulator buffers
+    static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
+    static constexpr int XCHG_BYTES = SWIGLU ? (2 * 16 * 64 * 4 + 2 * 16 * 64 * 2) : 0;
+};
+
+struct TcParams {
+    void* out;
+    long long ldc;
+    int M, N, K;
+    int up_row0;          // SWIGLU: row of W where the up rows start
+    int tiles_m, tiles_n;
+    int kb_total;         // K blocks per tile
+    int stream_k;         // 0: whole tiles round-robin; 1: contiguous (tile, K block) ranges per CTA;
+                          // 2: every tile cut into `split` equal K ranges, one per CTA
+    int split;
+    int max_slots;        // partial tiles per output tile in scratch (stream-K)
+    float* partials;
+    int* counters;
+    int* error_flag;
+};
+
+// The work items of one CTA, in order: (tile, first K block, end K block).
+struct TcSchedule {
+    int tiles, kbt, stream_k, split, per;
+    int cur, end, step;       // stream-K: unit cursor and range end; tiles: tile cursor and stride
+    long long base;
+    int rem, grid;
+    __device__ __forceinline__ void init(const TcParams& p) {
+        tiles = p.tiles_m * p.tiles_n;
+        kbt = p.kb_total;
+        stream_k = p.stream_k;
+        split = p.split;
+        grid = gridDim.x;
+        if (stream_k == 2) {
+            per = (kbt + split - 1) / split;
+            const int t = blockIdx.x / split, part = blockIdx.x - t * split;
+            cur = t * kbt + part * per;                       // as a unit range of the flat space
+            end = t * kbt + min(kbt, (part + 1) * per);
+            if (t >= tiles) end = cur;
+        } else if (stream_k) {
+            const long long units = (long long)tiles * kbt;
+            base = units / grid;
+            rem = (int)(units % grid);
+            const long long b = blockIdx.x;
+            cur = (int)(b * base + (b < rem ? b : rem));
+            end = cur + (int)base + (b < rem ? 1 : 0);
+        } else {
+            cur = blockIdx.x;
+            step = grid;
+            end = tiles;
+        }
+    }
+    __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1) {
+        if (cur >= end) return false;
+        if (stream_k) {
+            tile = cur / kbt;
+            kb0 = cur - tile * kbt;
+            kb1 = min(kbt, kb0 + (end - cur));
+            cur += kb1 - kb0;
+        } else {
+            tile = cur;
+            kb0 = 0;
+            kb1 = kbt;
+            cur += step;
+        }
+        return true;
+    }
+    // stream-K: the CTA that holds work unit u
+    __device__ __forceinline__ int cta_of(long long u) const {
+        const long long big = (long long)rem * (base + 1);
+        return u < big ? (int)(u / (base + 1)) : rem + (int)((u - big) / base);
+    }
+    // how many CTAs contribute to `tile` and which of them this CTA is (in K order)
+    __device__ __forceinline__ void contributors(int tile, int& n, int& slot) const {
+        if (stream_k == 2) {
+            n = (kbt + per - 1) / per;
+            slot = blockIdx.x - tile * split;
+        } else {
+            const long long u0 = (long long)tile * kbt;
+            const int c_lo = cta_of(u0);
+            n = cta_of(u0 + kbt - 1) - c_lo + 1;
+            slot = blockIdx.x - c_lo;
+        }
+    }
 };
 
 // ------------------------------------------------------------------------------- kernel
 template <int BN, int MODE, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, void* __restrict__ out,
-               long long ldc, int M, int N, int K, int up_row0, float* __restrict__ partials,
-               int* __restrict__ tile_counters, int* __restrict__ error_flag) {
-    constexpr bool DUAL = MODE == TC_SWIGLU_BF16;
-    using L = TcLayout<BN, DUAL>;
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
+    using L = TcLayout<BN, MODE>;
+    constexpr bool SWIGLU = L::SWIGLU;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);      // full[S], empty[S], accum
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    uint8_t* xchg = smem + STAGES * L::STAGE_BYTES;
+    uint64_t* bars = (uint64_t*)(xchg + L::XCHG_BYTES);        // full[S], empty[S], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* last_flag = (int*)(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BN;          // first token of the tile
-    const int n0 = blockIdx.y * TC_BM;       // first feature of the tile
-    const int splits = gridDim.z, split = blockIdx.z;
-    const int kb_total = (K + TC_BK - 1) / TC_BK;
-    const int kb_per = (kb_total + splits - 1) / splits;
-    const int kb0 = split * kb_per;
-    const int kb1 = min(kb_total, kb0 + kb_per);
-    const int nkb = max(0, kb1 - kb0);
-
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum = smem_u32(bars + 2 * STAGES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accum, 1);
+        for (int b = 0; b < L::NBUF; b++) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, 128);
+        }
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -175,170 +263,231 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     pdl_trigger();
 
+    TcSchedule sched;
+    sched.init(p);
+    int tile, kb0, kb1;
+
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            int armed = 0, s = 0;
-            uint32_t ph = 0;
+            auto load_w = [&](int s, int t, int kb) {
+                const int n0 = (t / p.tiles_m) * L::FEAT, k = kb * TC_BK;
+                const uint32_t stage = smem_base + s * L::STAGE_BYTES;
+                if (SWIGLU) {
+                    tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
+                    tma_load_2d(stage + L::W_BYTES / 2, &map_w, full0 + 8 * s, k, p.up_row0 + n0);
+                } else {
+                    tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
+                }
+            };
+            auto load_a = [&](int s, int t, int kb) {
+                tma_load_2d(smem_base + s * L::STAGE_BYTES + L::W_BYTES, &map_a, full0 + 8 * s, kb * TC_BK,
+                            (t % p.tiles_m) * BN);
+            };
             // The weights are written by no kernel of a step: the first stages' weight tiles are
             // requested before waiting for the kernel in front, whose output is only the
             // activation operand.
-            const int early = min(nkb, STAGES);
-            for (int i = 0; i < early; i++) {
-                const uint32_t stage = smem_base + i * L::STAGE_BYTES;
-                const int k = (kb0 + i) * TC_BK;
-                mbar_expect_tx(full0 + 8 * i, L::STAGE_BYTES);
-                tma_load_2d(stage, &map_w, full0 + 8 * i, k, n0);
-                if (DUAL) tma_load_2d(stage + L::W_BYTES, &map_w, full0 + 8 * i, k, up_row0 + n0);
-            }
-            pdl_wait();
-            for (int i = 0; i < early; i++)
-                tma_load_2d(smem_base + i * L::STAGE_BYTES + L::W_BYTES * (DUAL ? 2 : 1), &map_a, full0 + 8 * i,
-                            (kb0 + i) * TC_BK, m0);
-            armed = early;
-            if (early == STAGES) ph = 1; else s = early;
-            for (int i = early; i < nkb; i++) {
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) {
-                    atomicExch(error_flag, 1);
-                    *abort_flag = 1;
-                    break;
+            int early = 0;
+            {
+                TcSchedule peek = sched;
+                if (peek.next(tile, kb0, kb1)) {
+                    early = min(kb1 - kb0, STAGES);
+                    for (int j = 0; j < early; j++) {
+                        mbar_expect_tx(full0 + 8 * j, L::STAGE_BYTES);
+                        load_w(j, tile, kb0 + j);
+                    }
                 }
-                const uint32_t stage = smem_base + s * L::STAGE_BYTES;
-                const int k = (kb0 + i) * TC_BK;
-                mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
-                tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
-                if (DUAL) tma_load_2d(stage + L::W_BYTES, &map_w, full0 + 8 * s, k, up_row0 + n0);
-                tma_load_2d(stage + L::W_BYTES * (DUAL ? 2 : 1), &map_a, full0 + 8 * s, k, m0);
-                armed = i + 1;
-                if (++s == STAGES) { s = 0; ph ^= 1; }
+                pdl_wait();
+                for (int j = 0; j < early; j++) load_a(j, tile, kb0 + j);
+            }
+            int g = 0;                    // K blocks issued so far (all work items)
+            bool alive = true;
+            while (alive && sched.next(tile, kb0, kb1)) {
+                for (int kb = kb0; kb < kb1; kb++, g++) {
+                    if (g < early) continue;
+                    const int s = g % STAGES;
+                    if (!mbar_wait(empty0 + 8 * s, ((g / STAGES) & 1) ^ 1)) {
+                        atomicExch(p.error_flag, 1);
+                        *abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
+                    load_w(s, tile, kb);
+                    load_a(s, tile, kb);
+                }
             }
             // copies in flight must land before the CTA may exit: wait (bounded) for the
             // stages armed last; a stage the MMA thread already consumed answers at once
-            for (int i = max(0, armed - STAGES); i < armed; i++)
-                if (!mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1)) atomicExch(error_flag, 2);
+            for (int i = max(0, g - STAGES); i < g; i++)
+                if (!mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1)) atomicExch(p.error_flag, 2);
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        // One thread issues every MMA of the tile, so its instruction stream is the critical
-        // path for few-token tiles: descriptors are advanced with one 32-bit add per MMA
-        // (the high word is constant) and nothing else is recomputed inside the loop.
+        // One thread issues every MMA, so its instruction stream is the critical path for
+        // few-token tiles: descriptors advance with one 32-bit add per MMA (the high word is
+        // constant) and nothing else is recomputed inside the loop.
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16(BN);
             const uint64_t desc0 = smem_desc_sw128(smem_base);
             const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
-            constexpr uint32_t STAGE_STEP = L::STAGE_BYTES >> 4, A_OFF = (L::W_BYTES * (DUAL ? 2 : 1)) >> 4,
-                               UP_OFF = L::W_BYTES >> 4;
-            int s = 0;
+            constexpr uint32_t STAGE_STEP = L::STAGE_BYTES >> 4, A_OFF = L::W_BYTES >> 4;
+            int s = 0, item = 0;
             uint32_t ph = 0;
-            for (int i = 0; i < nkb; i++) {
-                if (!mbar_wait(full0 + 8 * s, ph)) {
-                    atomicExch(error_flag, 3);
+            bool alive = true;
+            while (alive && sched.next(tile, kb0, kb1)) {
+                const int buf = item & 1;
+                if (!mbar_wait(acce0 + 8 * buf, ((item >> 1) & 1) ^ 1)) {
+                    atomicExch(p.error_flag, 5);
                     *abort_flag = 1;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t w_lo = desc_lo0 + s * STAGE_STEP;
+                const uint32_t acc_addr = tmem_base + buf * BN;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(full0 + 8 * s, ph)) {
+                        atomicExch(p.error_flag, 3);
+                        *abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t w_lo = desc_lo0 + s * STAGE_STEP;
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; kk++) {
-                    const uint64_t wdesc = ((uint64_t)desc_hi << 32) | (w_lo + 2 * kk);
-                    const uint64_t tdesc = ((uint64_t)desc_hi << 32) | (w_lo + A_OFF + 2 * kk);
-                    const uint32_t acc = (i | kk) ? 1u : 0u;
-                    umma_bf16(tmem_base, wdesc, tdesc, idesc, acc);
-                    if (DUAL) umma_bf16(tmem_base + BN, ((uint64_t)desc_hi << 32) | (w_lo + UP_OFF + 2 * kk), tdesc, idesc, acc);
+                    for (int kk = 0; kk < TC_BK / 16; kk++) {
+                        const uint64_t wdesc = ((uint64_t)desc_hi << 32) | (w_lo + 2 * kk);
+                        const uint64_t tdesc = ((uint64_t)desc_hi << 32) | (w_lo + A_OFF + 2 * kk);
+                        umma_bf16(acc_addr, wdesc, tdesc, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);      // frees the stage when these MMAs have read it
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
-                umma_commit(empty0 + 8 * s);      // frees the stage when these MMAs have read it
-                if (++s == STAGES) { s = 0; ph ^= 1; }
+                umma_commit(accf0 + 8 * buf);          // arrives when the item's MMAs have finished
+                item++;
             }
-            umma_commit(accum);                    // arrives when every MMA above has finished
         }
     } else {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;                    // TMEM lane quarter this warp may read
-        const int f = n0 + q * 32 + lane;          // feature of this thread
-        bool ok = true;
+        const int row = q * 32 + lane;             // weight row of the tile = TMEM lane
+        const int et = (warp - 2) * 32 + lane;     // 0..127 among the epilogue threads
         pdl_wait();                                // the output, the scratch and the counters belong to earlier kernels until now
-        if (!mbar_wait(accum, 0)) {
-            atomicExch(error_flag, 4);
-            *abort_flag = 1;
-            ok = false;
-        }
-        if (*abort_flag) ok = false;
-        tc_fence_after();
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        const bool have_acc = nkb > 0;
-        if (ok && splits > 1) {
-            // partial tile to scratch: [tile][split][token][feature], float32
-            const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
-            float* p = partials + (tile * splits + split) * (size_t)(BN * TC_BM);
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                float v[16];
-                if (have_acc) tmem_ld16(lane_addr + c, v);
-#pragma unroll
-                for (int j = 0; j < 16; j++) p[(size_t)(c + j) * TC_BM + q * 32 + lane] = have_acc ? v[j] : 0.0f;
+        int item = 0;
+        while (sched.next(tile, kb0, kb1)) {
+            const int buf = item & 1;
+            if (!mbar_wait(accf0 + 8 * buf, (item >> 1) & 1)) {
+                atomicExch(p.error_flag, 4);
+                *abort_flag = 1;
+                break;
             }
-            __threadfence();
-        }
-        // the four epilogue warps agree on who finishes the tile
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (splits > 1) {
-            if (threadIdx.x == 64) {
-                const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
-                const int prev = atomicAdd(tile_counters + tile, 1);
-                const int last = (prev == splits - 1) ? 1 : 0;
-                if (last) tile_counters[tile] = 0;      // ready for the next launch
-                *last_flag = last;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (!*last_flag) ok = false;
-            __threadfence();
-        }
-        if (ok) {
-            const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+            if (*abort_flag) break;
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
+            const int m0 = (tile % p.tiles_m) * BN, n0 = (tile / p.tiles_m) * L::FEAT;
+            const bool whole = kb0 == 0 && kb1 == p.kb_total;
+            bool finish = whole;
+            int contributors = 1;
+            if (!whole) {
+                // partial tile to scratch: [tile][slot][token][row], float32
+                int slot;
+                sched.contributors(tile, contributors, slot);
+                float* dst = p.partials + ((size_t)tile * p.max_slots + slot) * (size_t)(BN * TC_BM);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                if (m0 + c >= M) break;
-                float v[16], u[16];
-                if (splits > 1) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = 0.0f;
-                    for (int z = 0; z < splits; z++) {
-                        const float* p = partials + (tile * splits + z) * (size_t)(BN * TC_BM);
-#pragma unroll
-                        for (int j = 0; j < 16; j++) v[j] += __ldcg(p + (size_t)(c + j) * TC_BM + q * 32 + lane);
-                    }
-                } else if (have_acc) {
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
                     tmem_ld16(lane_addr + c, v);
-                    if (DUAL) tmem_ld16(lane_addr + BN + c, u);
-                } else {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = u[j] = 0.0f;
+                    for (int j = 0; j < 16; j++) dst[(size_t)(c + j) * TC_BM + row] = v[j];
                 }
-                if (f < N) {
-                    if (MODE == TC_ADD_F32) {
-                        // all loads of the residual first, then the stores: written one by one the
-                        // compiler must keep each load behind the store before it (they may alias)
-                        float r[16];
-                        float* po = (float*)out + (size_t)(m0 + c) * ldc + f;
-#pragma unroll
-                        for (int j = 0; j < 16; j++) r[j] = (m0 + c + j < M) ? __ldcg(po + (size_t)j * ldc) : 0.0f;
-#pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            if (m0 + c + j < M) po[(size_t)j * ldc] = r[j] + v[j];
+                tc_fence_before();
+                mbar_arrive(acce0 + 8 * buf);                  // the accumulator buffer is free again
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) {
+                    const int prev = atomicAdd(p.counters + tile, 1);
+                    const int last = (prev == contributors - 1) ? 1 : 0;
+                    if (last) p.counters[tile] = 0;            // ready for the next launch
+                    *last_flag = last;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                finish = *last_flag != 0;
+                __threadfence();
+            }
+            if (finish) {
+                const float* src = p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    if (m0 + c >= p.M) break;
+                    float v[16];
+                    if (whole) {
+                        tmem_ld16(lane_addr + c, v);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int m = m0 + c + j;
-                            if (m < M) {
-                                const size_t o = (size_t)m * ldc + f;
-                                if (MODE == TC_STORE_BF16) ((bf16*)out)[o] = __float2bfloat16_rn(v[j]);
-                                else if (MODE == TC_STORE_F32) ((float*)out)[o] = v[j];
-                                else ((bf16*)out)[o] = __float2bfloat16_rn(silu_f32(v[j]) * u[j]);
+                        for (int j = 0; j < 16; j++) v[j] = 0.0f;
+                        for (int z = 0; z < contributors; z++) {
+                            const float* pz = src + (size_t)z * (BN * TC_BM);
+#pragma unroll
+                            for (int j = 0; j < 16; j++) v[j] += __ldcg(pz + (size_t)(c + j) * TC_BM + row);
+                        }
+                    }
+                    if (SWIGLU) {
+                        // rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same
+                        // features: pair them through shared memory, then store 16 bytes per thread
+                        float* xf = (float*)xchg + ((c >> 4) & 1) * (16 * 64);
+                        bf16* yb = (bf16*)(xchg + 2 * 16 * 64 * 4) + ((c >> 4) & 1) * (16 * 64);
+                        if (q >= 2) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) xf[j * 64 + row - 64] = v[j];
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (q < 2) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) yb[j * 64 + row] = __float2bfloat16_rn(silu_f32(v[j]) * xf[j * 64 + row]);
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        const int r = et >> 3, ch = et & 7;                 // token row of the chunk, 8-feature group
+                        const int m = m0 + c + r, n = n0 + ch * 8;
+                        if (m < p.M && n < p.N) {
+                            bf16* o = (bf16*)p.out + (size_t)m * p.ldc + n;
+                            if (n + 8 <= p.N) {
+                                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(yb + r * 64 + ch * 8);
+                            } else {
+                                for (int e = 0; e < p.N - n; e++) o[e] = yb[r * 64 + ch * 8 + e];
+                            }
+                        }
+                    } else {
+                        const int f = n0 + row;
+                        if (f < p.N) {
+                            if (MODE == TC_ADD_F32) {
+                                // all loads of the residual first, then the stores: written one by one
+                                // the compiler must keep each load behind the store before it
+                                float r[16];
+                                float* po = (float*)p.out + (size_t)(m0 + c) * p.ldc + f;
+#pragma unroll
+                                for (int j = 0; j < 16; j++) r[j] = (m0 + c + j < p.M) ? __ldcg(po + (size_t)j * p.ldc) : 0.0f;
+#pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    if (m0 + c + j < p.M) po[(size_t)j * p.ldc] = r[j] + v[j];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; j++) {
+                                    const int m = m0 + c + j;
+                                    if (m < p.M) {
+                                        const size_t o = (size_t)m * p.ldc + f;
+                                        if (MODE == TC_STORE_BF16) ((bf16*)p.out)[o] = __float2bfloat16_rn(v[j]);
+                                        else ((float*)p.out)[o] = v[j];
+                                    }
+                                }
                             }
                         }
                     }
                 }
             }
+            if (whole) {
+                tc_fence_before();
+                mbar_arrive(acce0 + 8 * buf);
+            }
+            item++;
         }
     }
     tc_fence_before();
@@ -359,11 +508,11 @@ static EncodeTiledFn get_encode() {
     static bool tried = false;
     if (!tried) {
         tried = true;
-        void* p = nullptr;
+        void* ptr = nullptr;
         cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
+            fn = (EncodeTiledFn)ptr;
     }
     return fn;
 }
@@ -384,11 +533,80 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return 0;
 }
 
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 1;
+    }
+    return n;
+}
+
+extern "C" int hb_gemm_tc_token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+// The work split of a product: tiles, grid, stream-K or not, scratch.  schedule: 0 automatic,
+// 1 whole tiles round-robin, 2 stream-K.
+struct TcPlan {
+    int bn, feat, tiles_m, tiles_n, kb_total, grid, stream_k, max_slots, split;
+    long long scratch_floats, tiles;
+};
+
+static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
+    TcPlan pl;
+    pl.bn = hb_gemm_tc_token_tile(M);
+    pl.feat = mode == TC_SWIGLU_BF16 ? 64 : TC_BM;
+    pl.tiles_m = (M + pl.bn - 1) / pl.bn;
+    pl.tiles_n = (N + pl.feat - 1) / pl.feat;
+    pl.tiles = (long long)pl.tiles_m * pl.tiles_n;
+    pl.kb_total = (K + TC_BK - 1) / TC_BK;
+    const int sms = sm_count();
+    const long long units = pl.tiles * pl.kb_total;
+    pl.stream_k = schedule == 2 || (schedule == 0 && pl.tiles_m == 1 && pl.bn <= 64);
+    pl.split = 1;
+    if (pl.stream_k) {
+        // Few tiles: either every SM takes one contiguous range of the whole (tile, K block)
+        // space, or each tile is cut into floor(SMs / tiles) equal K ranges (one work item per
+        // CTA, fewer partial tiles).  Costs in K blocks; a work item costs about six K blocks
+        // of fixed time (partial tile, counter, reduction).
+        long long g = units / 4;                  // at least four K blocks per CTA
+        g = g < 1 ? 1 : g > sms ? sms : g;
+        if (schedule == 0 && pl.tiles < sms) {
+            const long long split = sms / pl.tiles;
+            const long long aligned_cost = (pl.kb_total + split - 1) / split + 6;
+            const long long stream_cost = units / g + 12;
+            if (aligned_cost <= stream_cost && pl.kb_total / split >= 4) {
+                pl.stream_k = 2;
+                pl.split = (int)split;
+                g = pl.tiles * split;
+            }
+        }
+        pl.grid = (int)g;
+        const long long base = units / pl.grid;
+        pl.max_slots = pl.stream_k == 2 ? pl.split : (int)(pl.kb_total / base) + 2;
+        if (pl.max_slots > pl.grid) pl.max_slots = pl.grid;
+        pl.scratch_floats = pl.tiles * pl.max_slots * (long long)pl.bn * TC_BM;
+    } else {
+        pl.grid = (int)(pl.tiles < sms ? pl.tiles : sms);
+        pl.max_slots = 0;
+        pl.scratch_floats = 0;
+    }
+    return pl;
+}
+
+// Scratch a product needs: float32 partial tiles (hb_gemm_tc_scratch_floats) and one int
+// counter per output tile (hb_gemm_tc_tiles; zero before the first use, the kernel leaves
+// them zero).
+extern "C" long long hb_gemm_tc_scratch_floats(int M, int N, int K, int mode, int schedule) {
+    return make_plan(M, N, K, mode, schedule).scratch_floats;
+}
+extern "C" long long hb_gemm_tc_tiles(int M, int N, int mode) { return make_plan(M, N, 64, mode, 1).tiles; }
+
 template <int BN, int MODE, int STAGES>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, long long ldc, int M, int N, int K,
-                     int up_row0, int splits, float* partials, int* counters, int* error_flag, cudaStream_t s) {
-    using L = TcLayout<BN, MODE == TC_SWIGLU_BF16>;
-    constexpr int SMEM = STAGES * L::STAGE_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024;
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
+    using L = TcLayout<BN, MODE>;
+    constexpr int SMEM = STAGES * L::STAGE_BYTES + L::XCHG_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(SMEM <= 227 * 1024, "tile pipeline does not fit shared memory");
     static bool attr_set = false;
     if (!attr_set) {
@@ -396,48 +614,31 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, lo
         if (e != cudaSuccess) return hb_fail("gemm_tc: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
-    dim3 grid((M + BN - 1) / BN, (N + TC_BM - 1) / TC_BM, splits);
-    hb_launch(gemm_tc_kernel<BN, MODE, STAGES>, dim3(grid), dim3(TC_THREADS), SMEM, s, mw, ma, out, ldc, M, N, K, up_row0, partials, counters, error_flag);
+    cudaError_t e = hb_launch(gemm_tc_kernel<BN, MODE, STAGES>, dim3(grid), dim3(TC_THREADS), SMEM, s, mw, ma, prm);
+    if (e != cudaSuccess) return hb_fail("gemm_tc: launch failed: %s", cudaGetErrorString(e));
     return hb_check_launch("gemm_tc");
 }
 
 template <int MODE>
-static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& ma, void* out, long long ldc, int M, int N, int K,
-                       int up_row0, int splits, float* partials, int* counters, int* error_flag, cudaStream_t s) {
-    constexpr bool DUAL = MODE == TC_SWIGLU_BF16;
+static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
     switch (bn) {
-        case 16: return launch_tc<16, MODE, DUAL ? 6 : 12>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
-        case 32: return launch_tc<32, MODE, DUAL ? 5 : 8>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
-        case 64: return launch_tc<64, MODE, DUAL ? 5 : 8>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
-        case 128: return launch_tc<128, MODE, DUAL ? 4 : 6>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
-        case 256: return launch_tc<256, MODE, DUAL ? 3 : 4>(mw, ma, out, ldc, M, N, K, up_row0, splits, partials, counters, error_flag, s);
+        case 16: return launch_tc<16, MODE, 11>(mw, ma, prm, grid, s);
+        case 32: return launch_tc<32, MODE, 10>(mw, ma, prm, grid, s);
+        case 64: return launch_tc<64, MODE, 8>(mw, ma, prm, grid, s);
+        case 128: return launch_tc<128, MODE, 6>(mw, ma, prm, grid, s);
+        case 256: return launch_tc<256, MODE, 4>(mw, ma, prm, grid, s);
     }
     return hb_fail("gemm_tc: token tile %d is not built", bn);
 }
 
-extern "C" int hb_gemm_tc_token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
-
-// Scratch floats that a split-K launch needs: one BN x 128 partial tile per (tile, split).
-extern "C" long long hb_gemm_tc_scratch_floats(int M, int N, int splits) {
-    if (splits <= 1) return 0;
-    const int bn = hb_gemm_tc_token_tile(M);
-    const long long tiles = (long long)((M + bn - 1) / bn) * ((N + TC_BM - 1) / TC_BM);
-    return tiles * splits * bn * TC_BM;
-}
-
-extern "C" long long hb_gemm_tc_tiles(int M, int N) {
-    const int bn = hb_gemm_tc_token_tile(M);
-    return (long long)((M + bn - 1) / bn) * ((N + TC_BM - 1) / TC_BM);
-}
-
 // mode: 0 store bf16, 1 store f32, 2 add into f32, 3 silu(gate) * up -> bf16 (W holds the gate
-// rows [0, N) and the up rows [up_row0, up_row0 + N)).  splits > 1 needs `partials`
-// (hb_gemm_tc_scratch_floats floats) and `tile_counters` (hb_gemm_tc_tiles ints, zero before the
-// first use; the kernel leaves them zero).  `error_flag` is a device int the kernel sets
-// when a wait ran out.
+// rows [0, N) and the up rows [up_row0, up_row0 + N)).  `partials` and `tile_counters` are the
+// scratch described above (capacities in floats and ints); `error_flag` is a device int the
+// kernel sets when a wait ran out.
 extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,
-                          long long ldc, int M, int N, int K, int mode, int up_row0, int splits, float* partials,
-                          int* tile_counters, int* error_flag, void* stream) {
+                          long long ldc, int M, int N, int K, int mode, int up_row0, int schedule, float* partials,
+                          long long partials_capacity, int* tile_counters, long long counters_capacity, int* error_flag,
+                          void* stream) {
     if (M == 0 || N == 0) return 0;
     HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     HB_REQUIRE(mode >= 0 && mode <= 3, "gemm_tc: unknown epilogue %d", mode);
@@ -445,18 +646,38 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
     HB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: row strides %lld and %lld must be multiples of 8 elements", lda, ldw);
     HB_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_tc: a row stride is smaller than its row");
     HB_REQUIRE(error_flag != nullptr, "gemm_tc: no error flag");
-    HB_REQUIRE(splits >= 1 && splits <= 32, "gemm_tc: %d K splits", splits);
-    HB_REQUIRE(splits == 1 || (partials && tile_counters && mode != TC_SWIGLU_BF16), "gemm_tc: split-K needs scratch and no SwiGLU");
     HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 + N <= w_rows, "gemm_tc: up rows lie outside the weight matrix");
-    const int bn = hb_gemm_tc_token_tile(M);
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || (ldc % 8 == 0 && ((uintptr_t)out & 15) == 0),
+               "gemm_tc: the SwiGLU output needs 16-byte aligned rows");
+    const TcPlan pl = make_plan(M, N, K, mode, schedule);
+    if (pl.stream_k) {
+        HB_REQUIRE(partials && tile_counters && partials_capacity >= pl.scratch_floats && counters_capacity >= pl.tiles,
+                   "gemm_tc: stream-K needs %lld scratch floats and %lld counters", pl.scratch_floats, pl.tiles);
+    }
     CUtensorMap mw, ma;
-    if (make_map(&mw, w, w_rows, K, ldw, TC_BM)) return 1;
-    if (make_map(&ma, a, M, K, lda, bn)) return 1;
+    if (make_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM)) return 1;
+    if (make_map(&ma, a, M, K, lda, pl.bn)) return 1;
+    TcParams prm;
+    prm.out = out;
+    prm.ldc = ldc;
+    prm.M = M;
+    prm.N = N;
+    prm.K = K;
+    prm.up_row0 = up_row0;
+    prm.tiles_m = pl.tiles_m;
+    prm.tiles_n = pl.tiles_n;
+    prm.kb_total = pl.kb_total;
+    prm.stream_k = pl.stream_k;
+    prm.split = pl.split;
+    prm.max_slots = pl.max_slots;
+    prm.partials = partials;
+    prm.counters = tile_counters;
+    prm.error_flag = error_flag;
     cudaStream_t s = (cudaStream_t)stream;
     switch (mode) {
-        case TC_STORE_BF16: return dispatch_bn<TC_STORE_BF16>(bn, mw, ma, out, ldc, M, N, K, up_row0, splits, partials, tile_counters, error_flag, s);
-        case TC_STORE_F32: return dispatch_bn<TC_STORE_F32>(bn, mw, ma, out, ldc, M, N, K, up_row0, splits, partials, tile_counters, error_flag, s);
-        case TC_ADD_F32: return dispatch_bn<TC_ADD_F32>(bn, mw, ma, out, ldc, M, N, K, up_row0, splits, partials, tile_counters, error_flag, s);
-        default: return dispatch_bn<TC_SWIGLU_BF16>(bn, mw, ma, out, ldc, M, N, K, up_row0, splits, partials, tile_counters, error_flag, s);
+        case TC_STORE_BF16: return dispatch_bn<TC_STORE_BF16>(pl.bn, mw, ma, prm, pl.grid, s);
+        case TC_STORE_F32: return dispatch_bn<TC_STORE_F32>(pl.bn, mw, ma, prm, pl.grid, s);
+        case TC_ADD_F32: return dispatch_bn<TC_ADD_F32>(pl.bn, mw, ma, prm, pl.grid, s);
+        default: return dispatch_bn<TC_SWIGLU_BF16>(pl.bn, mw, ma, prm, pl.grid, s);
     }
 }

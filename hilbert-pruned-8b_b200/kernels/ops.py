@@ -31,7 +31,7 @@ _SIGNATURES = {
     "hb_gemm_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
                         _c_int, _c_ptr],
     "hb_gemm_tc": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+                   _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr],
     "hb_attention_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                              _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
     "hb_attention_decode": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
@@ -63,8 +63,9 @@ def load_library():
             fn.argtypes = args
             fn.restype = _c_int
         lib.hb_gemm_tc_token_tile.argtypes, lib.hb_gemm_tc_token_tile.restype = [_c_int], _c_int
-        lib.hb_gemm_tc_scratch_floats.argtypes, lib.hb_gemm_tc_scratch_floats.restype = [_c_int, _c_int, _c_int], _c_ll
-        lib.hb_gemm_tc_tiles.argtypes, lib.hb_gemm_tc_tiles.restype = [_c_int, _c_int], _c_ll
+        lib.hb_gemm_tc_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int, _c_int]
+        lib.hb_gemm_tc_scratch_floats.restype = _c_ll
+        lib.hb_gemm_tc_tiles.argtypes, lib.hb_gemm_tc_tiles.restype = [_c_int, _c_int, _c_int], _c_ll
         for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported"):
             getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
@@ -218,38 +219,28 @@ class Ops:
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
                 and _rows(a, "linear input") % 8 == 0 and _rows(w, "linear weight") % 8 == 0)
 
-    def split_k_for(self, M: int, N: int, K: int) -> int:
-        """K splits of a few-token product so that about one CTA per SM streams weights."""
-        if M > 64:
-            return 1
-        tiles = (N + 127) // 128
-        kb = (K + 63) // 64
-        splits = max(1, min(self.sm_count // max(tiles, 1), kb // 4, 16))
-        if splits > 1:
-            per = (kb + splits - 1) // splits
-            splits = (kb + per - 1) // per          # no split without work
-        return splits
+    SCHEDULES = {None: 0, "auto": 0, "tiles": 1, "stream_k": 2}
 
-    def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, splits: int = 1) -> None:
+    def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None) -> None:
         M, K = a.shape
-        partials = counters = None
-        if splits > 1:
-            need = self.lib.hb_gemm_tc_scratch_floats(M, N, splits)
-            tiles = self.lib.hb_gemm_tc_tiles(M, N)
-            if need > self._splitk_partials.numel():
-                self._retired.append(self._splitk_partials)     # a captured graph may still write there
-                self._splitk_partials = torch.empty(need, dtype=torch.float32, device=self.device)
-            if tiles > self._splitk_counters.numel():
-                self._retired.append(self._splitk_counters)
-                self._splitk_counters = torch.zeros(tiles, dtype=torch.int32, device=self.device)
-            partials, counters = self._splitk_partials.data_ptr(), self._splitk_counters.data_ptr()
+        sched = self.SCHEDULES[schedule]
+        need = self.lib.hb_gemm_tc_scratch_floats(M, N, K, mode, sched)
+        tiles = self.lib.hb_gemm_tc_tiles(M, N, mode)
+        if need > self._splitk_partials.numel():
+            self._retired.append(self._splitk_partials)     # a captured graph may still write there
+            self._splitk_partials = torch.empty(need, dtype=torch.float32, device=self.device)
+        if tiles > self._splitk_counters.numel():
+            self._retired.append(self._splitk_counters)
+            self._splitk_counters = torch.zeros(tiles, dtype=torch.int32, device=self.device)
         self._call("hb_gemm_tc", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), _rows(w, "linear weight"),
-                   w.shape[0], out.data_ptr(), _rows(out, "linear output"), M, N, K, mode, up_row0, splits, partials,
-                   counters, self.error_flag.data_ptr(), self._stream())
+                   w.shape[0], out.data_ptr(), _rows(out, "linear output"), M, N, K, mode, up_row0, sched,
+                   self._splitk_partials.data_ptr(), self._splitk_partials.numel(), self._splitk_counters.data_ptr(),
+                   self._splitk_counters.numel(), self.error_flag.data_ptr(), self._stream())
         self.launches += 1
 
-    def linear(self, a, w, out, accumulate: bool = False, splits=None) -> None:
-        """``out[M,N] (+)= a[M,K] @ w[N,K]^T`` with float32 accumulation."""
+    def linear(self, a, w, out, accumulate: bool = False, schedule=None) -> None:
+        """``out[M,N] (+)= a[M,K] @ w[N,K]^T`` with float32 accumulation.  ``schedule`` forces
+        the tensor-core kernel's work split ("tiles" or "stream_k"; default: by shape)."""
         self._dev(a, w, out)
         M, K = a.shape
         N = w.shape[0]
@@ -257,21 +248,22 @@ class Ops:
             raise KernelError(f"linear: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
         if self._tensor_core_operands(a, w) and (out.dtype == torch.float32 or not accumulate):
             mode = 2 if accumulate else (1 if out.dtype == torch.float32 else 0)
-            self._gemm_tc(a, w, out, mode, N, 0, self.split_k_for(M, N, K) if splits is None else splits)
+            self._gemm_tc(a, w, out, mode, N, 0, schedule)
             return
         self._call("hb_gemm_general", a.data_ptr(), _code(a), _rows(a, "linear input"), w.data_ptr(), _code(w),
                    _rows(w, "linear weight"), out.data_ptr(), _code(out), _rows(out, "linear output"), M, N, K,
                    1 if accumulate else 0, self._stream())
         self.launches += 1
 
-    def linear_swiglu(self, h, w_gate_up, act, workspace, cap: int) -> None:
+    def linear_swiglu(self, h, w_gate_up, act, workspace, cap: int, schedule=None) -> None:
         """``act = silu(h Wg^T) * (h Wu^T)`` with ``w_gate_up = [Wg; Wu]``."""
         T = h.shape[0]
         inter = act.shape[1]
         if w_gate_up.shape[0] != 2 * inter or act.shape[0] != T:
             raise KernelError("linear_swiglu: weight must be [2 * inter, hidden]")
-        if self._tensor_core_operands(h, w_gate_up) and act.dtype == torch.bfloat16:
-            self._gemm_tc(h, w_gate_up, act, 3, inter, up_row0=inter)
+        if (self._tensor_core_operands(h, w_gate_up) and act.dtype == torch.bfloat16 and act.data_ptr() % 16 == 0
+                and _rows(act, "swiglu output") % 8 == 0):
+            self._gemm_tc(h, w_gate_up, act, 3, inter, up_row0=inter, schedule=schedule)
             return
         gu = workspace.buffer("swiglu.gate_up", (cap, 2 * inter), torch.float32 if act.dtype == torch.float32
                               else torch.bfloat16)[:T]

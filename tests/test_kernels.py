@@ -191,35 +191,40 @@ def test_gemm_tensor_core_against_plain_and_general(ops, M, N, K):
     assert _rel(out, gen) < 2e-6 * math.sqrt(K)
 
 
-@pytest.mark.parametrize("M,N,K,splits", [(8, 512, 1024, 4), (1, 384, 4096, 3), (64, 256, 2048, 8), (5, 100, 416, 2)])
-def test_gemm_tensor_core_split_k(ops, M, N, K, splits):
+@pytest.mark.parametrize("M,N,K", [(8, 512, 1024), (1, 384, 4096), (64, 256, 2048), (5, 100, 416), (40, 4096, 512),
+                                   (16, 20000, 256), (200, 384, 1024)])
+def test_gemm_tensor_core_stream_k_and_tiles(ops, M, N, K):
+    """Both work splits of the tensor-core kernel: stream-K (partial tiles in scratch, summed
+    in K order by the last contributor) and whole tiles round-robin (several per CTA)."""
     torch.manual_seed(7)
     a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
     ref = a.double() @ w.double().t()
     res = torch.randn(M, N, device=DEV)
-    for rep in range(2):                    # twice: the tile counters must come back to zero
-        acc = res.clone()
-        ops.linear(a, w, acc, accumulate=True, splits=splits)
-        ops.check_errors()
-        assert _rel(acc, ref + res.double()) < 2e-6 * math.sqrt(K)
-    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-    ops.linear(a, w, out, splits=splits)
-    assert _rel(out, ref) < 2 ** -8
-    assert int(ops._splitk_counters.abs().sum()) == 0
-    again = torch.empty_like(out)
-    ops.linear(a, w, again, splits=splits)
-    assert torch.equal(out, again)          # the sum order is fixed
+    for schedule in ("stream_k", "tiles"):
+        for rep in range(2):                    # twice: the tile counters must come back to zero
+            acc = res.clone()
+            ops.linear(a, w, acc, accumulate=True, schedule=schedule)
+            ops.check_errors()
+            assert _rel(acc, ref + res.double()) < 2e-6 * math.sqrt(K), schedule
+        out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.linear(a, w, out, schedule=schedule)
+        assert _rel(out, ref) < 2 ** -8
+        assert int(ops._splitk_counters.abs().sum()) == 0
+        again = torch.empty_like(out)
+        ops.linear(a, w, again, schedule=schedule)
+        assert torch.equal(out, again)          # the sum order is fixed
 
 
-@pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 300), (8, 4096, 512)])
-def test_linear_swiglu(ops, M, K, I):
+@pytest.mark.parametrize("schedule", ["tiles", "stream_k"])
+@pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 304), (8, 4096, 512), (300, 512, 1000)])
+def test_linear_swiglu(ops, M, K, I, schedule):
     from hilbert_pruned_8b_b200.engine.workspace import Workspace
     torch.manual_seed(8)
     h = _bf(torch.randn(M, K, device=DEV))
     w = _bf(torch.randn(2 * I, K, device=DEV) / math.sqrt(K))
     act = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
     ws = Workspace(torch.device(DEV))
-    ops.linear_swiglu(h, w, act, ws, M)
+    ops.linear_swiglu(h, w, act, ws, M, schedule=schedule)
     ops.check_errors()
     g, u = h.double() @ w[:I].double().t(), h.double() @ w[I:].double().t()
     ref = g / (1 + torch.exp(-g)) * u
