@@ -35,7 +35,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     const int head = blockIdx.y, g = head / (nh / nkv);
 
     // which sequence and which block of its new tokens this CTA serves
-    int b = 0, blk = blockIdx.x;
+    // blocks are taken from the back: late query blocks see the most keys and should start first
+    int b = 0, blk = gridDim.x - 1 - blockIdx.x;
     for (; b < n_seqs; b++) {
         const int nb = (seq_start[b + 1] - seq_start[b] + AP_ROWS - 1) / AP_ROWS;
         if (blk < nb) break;

@@ -58,16 +58,79 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * inv * (offset + w[i]));
 }
 
+// The same, reading each row once: a thread keeps its 4 * VEC elements in registers between
+// the sum of squares and the scaling.  For rows of a multiple of 4 up to 4 * VEC * 256 floats.
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, float offset,
+                    TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    const int n4 = hidden >> 2;
+    float4 v[VEC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        const int c = threadIdx.x + i * 256;
+        v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[i].x, v[i].x, ss);
+        ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss);
+        ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+#pragma unroll
+    for (int i = 0; i < VEC; i++) {
+        const int c = threadIdx.x + i * 256;
+        if (c < n4) {
+            const float4 g = wr[c];
+            const float a = v[i].x * inv * (offset + g.x), b = v[i].y * inv * (offset + g.y);
+            const float cc = v[i].z * inv * (offset + g.z), d = v[i].w * inv * (offset + g.w);
+            if (sizeof(TO) == 2) {
+                uint2 pk;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(cc, d);
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(o) + 4 * c) = pk;
+            } else {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + 4 * c) = make_float4(a, b, cc, d);
+            }
+        }
+    }
+}
+
+template <typename TO>
+static void launch_rmsnorm(const float* x, const float* weight, float eps, float offset, TO* out, const int* rows,
+                           int n_rows, int hidden, cudaStream_t s) {
+    const bool vec = hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 &&
+                     ((uintptr_t)out & 15) == 0;
+    if (vec && hidden <= 4 * 256 * 2)
+        hb_launch(rmsnorm_rows_kernel<TO, 2>, dim3(n_rows), dim3(256), 0, s, x, weight, eps, offset, out, rows, hidden);
+    else if (vec && hidden <= 4 * 256 * 4)
+        hb_launch(rmsnorm_rows_kernel<TO, 4>, dim3(n_rows), dim3(256), 0, s, x, weight, eps, offset, out, rows, hidden);
+    else if (vec && hidden <= 4 * 256 * 8)
+        hb_launch(rmsnorm_rows_kernel<TO, 8>, dim3(n_rows), dim3(256), 0, s, x, weight, eps, offset, out, rows, hidden);
+    else
+        hb_launch(rmsnorm_kernel<TO>, dim3(n_rows), dim3(hidden >= 2048 ? 512 : 256), 0, s, x, weight, eps, offset, out, rows,
+                  hidden);
+}
+
 extern "C" int hb_rmsnorm(const float* x, const float* weight, float eps, float offset, void* out, int out_dtype,
                           const int* rows, int n_rows, int hidden, void* stream) {
     if (n_rows == 0) return 0;
     HB_REQUIRE(n_rows > 0 && hidden > 0, "rmsnorm: bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = hidden >= 2048 ? 512 : 256;
     if (out_dtype == HB_BF16)
-        hb_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, x, weight, eps, offset, (bf16*)out, rows, hidden);
+        launch_rmsnorm<bf16>(x, weight, eps, offset, (bf16*)out, rows, n_rows, hidden, s);
     else if (out_dtype == HB_F32)
-        hb_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, x, weight, eps, offset, (float*)out, rows, hidden);
+        launch_rmsnorm<float>(x, weight, eps, offset, (float*)out, rows, n_rows, hidden, s);
     else
         return hb_fail("rmsnorm: unsupported output dtype %d", out_dtype);
     return hb_check_launch("rmsnorm");
@@ -132,50 +195,54 @@ extern "C" int hb_rope_table(const int* positions, const float* inv_freq, float*
 }
 
 // --------------------------------------------------------------------- rope + cache append
-// One block per (token, head slot).  Slots 0..nh-1 are the query heads (rotated in place),
-// nh..nh+nkv-1 the key heads (rotated, written to the cache row of the token's position),
-// the rest the value heads (copied to the cache).  Rotation pairs (i, i + rot/2); dims
-// beyond `rot` pass through (cpu_backend.c:87-100; cuda_backend.cu:212-249).
+// One block per token; its threads walk all (head, pair) combinations.  Query heads are
+// rotated in place, key heads are rotated into the cache row of the token's position, value
+// heads are copied to the cache.  Rotation pairs (i, i + rot/2); dims beyond `rot` pass
+// through (cpu_backend.c:87-100; cuda_backend.cu:212-249).
 template <typename T, typename TC>
-__global__ void rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table,
-                                      int rot, int nh, int nkv, int hd, TC* __restrict__ k_cache,
-                                      TC* __restrict__ v_cache, const int* __restrict__ page_table, int pt_width,
-                                      const int* __restrict__ tok_seq, const int* __restrict__ positions,
-                                      int n_pages) {
+__global__ void __launch_bounds__(256)
+rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot, int nh,
+                      int nkv, int hd, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                      const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
+                      const int* __restrict__ positions, int n_pages, int append) {
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x, slot = blockIdx.y;
+    const int t = blockIdx.x;
     const int half = rot >> 1;
     T* row = qkv + (size_t)t * qkv_stride;
-    if (slot < nh) {
-        T* x = row + (size_t)slot * hd;
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float2 cs = table[(size_t)t * half + i];
-            const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
-            x[i] = from_f32<T>(x1 * cs.x - x2 * cs.y);
-            x[i + half] = from_f32<T>(x2 * cs.x + x1 * cs.y);
-        }
-        return;
+    const float2* cs_row = table + (size_t)t * half;
+    // query heads: rotate in place
+    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        T* x = row + (size_t)h * hd;
+        const float2 cs = cs_row[i];
+        const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
+        x[i] = from_f32<T>(x1 * cs.x - x2 * cs.y);
+        x[i + half] = from_f32<T>(x2 * cs.x + x1 * cs.y);
     }
+    if (!append) return;
     const int pos = positions[t];
     const int page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
-    if (page < 0 || page >= n_pages) return;  // the host reserved the pages; never write outside the cache
-    if (slot < nh + nkv) {
-        const int g = slot - nh;
-        const T* x = row + (size_t)(nh + g) * hd;
+    if (page < 0 || page >= n_pages) return;   // the host reserved the pages; never write outside the cache
+    const T* krow = row + (size_t)nh * hd;
+    const T* vrow = krow + (size_t)nkv * hd;
+    for (int idx = threadIdx.x; idx < nkv * half; idx += blockDim.x) {
+        const int g = idx / half, i = idx - g * half;
+        const T* x = krow + (size_t)g * hd;
         TC* dst = k_cache + cache_offset(page, g, pos, nkv, hd);
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float2 cs = table[(size_t)t * half + i];
-            const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
-            dst[i] = from_f32<TC>(x1 * cs.x - x2 * cs.y);
-            dst[i + half] = from_f32<TC>(x2 * cs.x + x1 * cs.y);
-        }
-        for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = from_f32<TC>(to_f32(x[i]));
-    } else {
-        const int g = slot - nh - nkv;
-        const T* x = row + (size_t)(nh + nkv + g) * hd;
-        TC* dst = v_cache + cache_offset(page, g, pos, nkv, hd);
-        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = from_f32<TC>(to_f32(x[i]));
+        const float2 cs = cs_row[i];
+        const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
+        dst[i] = from_f32<TC>(x1 * cs.x - x2 * cs.y);
+        dst[i + half] = from_f32<TC>(x2 * cs.x + x1 * cs.y);
+    }
+    const int tail = hd - rot;
+    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
+        const int g = idx / tail, i = rot + idx - g * tail;
+        k_cache[cache_offset(page, g, pos, nkv, hd) + i] = from_f32<TC>(to_f32(krow[(size_t)g * hd + i]));
+    }
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+        const int g = idx / hd, i = idx - g * hd;
+        v_cache[cache_offset(page, g, pos, nkv, hd) + i] = from_f32<TC>(to_f32(vrow[idx]));
     }
 }
 
@@ -188,22 +255,19 @@ extern "C" int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride,
     HB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0, "rope_kv_append: rotary size %d does not fit head size %d",
                rot, head_dim);
     HB_REQUIRE(rot == 0 || table != nullptr, "rope_kv_append: no rotary table");
-    const int slots = append ? n_heads + 2 * n_kv_heads : n_heads;
-    HB_REQUIRE(slots <= 65535, "rope_kv_append: too many heads");
     if (rot == 0 && !append) return 0;
-    dim3 grid(n_tokens, slots);
-    const int threads = head_dim >= 128 ? 64 : 32;
+    const long long work = (long long)(n_heads + n_kv_heads) * (rot / 2) + (long long)n_kv_heads * head_dim;
+    const int threads = work >= 1024 ? 256 : work >= 256 ? 128 : 64;
     cudaStream_t s = (cudaStream_t)stream;
     const float2* tab = (const float2*)table;
     if (qkv_dtype == HB_BF16 && cache_dtype == HB_BF16)
-        hb_launch(rope_kv_append_kernel<bf16, bf16>, dim3(grid), dim3(threads), 0, s, (bf16*)qkv, qkv_stride, tab, rot, n_heads, n_kv_heads,
-                                                                    head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table,
-                                                                    pt_width, tok_seq, positions, n_pages);
+        hb_launch(rope_kv_append_kernel<bf16, bf16>, dim3(n_tokens), dim3(threads), 0, s, (bf16*)qkv, qkv_stride, tab, rot,
+                  n_heads, n_kv_heads, head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table, pt_width, tok_seq, positions,
+                  n_pages, append);
     else if (qkv_dtype == HB_F32 && cache_dtype == HB_F32)
-        hb_launch(rope_kv_append_kernel<float, float>, dim3(grid), dim3(threads), 0, s, (float*)qkv, qkv_stride, tab, rot, n_heads,
-                                                                      n_kv_heads, head_dim, (float*)k_cache,
-                                                                      (float*)v_cache, page_table, pt_width, tok_seq,
-                                                                      positions, n_pages);
+        hb_launch(rope_kv_append_kernel<float, float>, dim3(n_tokens), dim3(threads), 0, s, (float*)qkv, qkv_stride, tab, rot,
+                  n_heads, n_kv_heads, head_dim, (float*)k_cache, (float*)v_cache, page_table, pt_width, tok_seq, positions,
+                  n_pages, append);
     else
         return hb_fail("rope_kv_append: unsupported dtypes qkv %d cache %d", qkv_dtype, cache_dtype);
     return hb_check_launch("rope_kv_append");
