@@ -195,10 +195,11 @@ extern "C" int hb_rope_table(const int* positions, const float* inv_freq, float*
 }
 
 // --------------------------------------------------------------------- rope + cache append
-// One block per token; its threads walk all (head, pair) combinations.  Query heads are
-// rotated in place, key heads are rotated into the cache row of the token's position, value
-// heads are copied to the cache.  Rotation pairs (i, i + rot/2); dims beyond `rot` pass
+// Blocks (token, group): a group is ROPE_GROUP query heads, rotated in place, or (the last
+// group of a token) all key and value heads: keys are rotated into the cache row of the
+// token's position, values are copied there.  Rotation pairs (i, i + rot/2); dims beyond `rot` pass
 // through (cpu_backend.c:87-100; cuda_backend.cu:212-249).
+#define ROPE_GROUP 8
 template <typename T, typename TC>
 __global__ void __launch_bounds__(256)
 rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot, int nh,
@@ -211,16 +212,20 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
     const int half = rot >> 1;
     T* row = qkv + (size_t)t * qkv_stride;
     const float2* cs_row = table + (size_t)t * half;
-    // query heads: rotate in place
-    for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
-        const int h = idx / half, i = idx - h * half;
-        T* x = row + (size_t)h * hd;
-        const float2 cs = cs_row[i];
-        const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
-        x[i] = from_f32<T>(x1 * cs.x - x2 * cs.y);
-        x[i + half] = from_f32<T>(x2 * cs.x + x1 * cs.y);
+    // blockIdx.y < gridDim.y - 1: a group of ROPE_GROUP query heads, rotated in place;
+    // the last block of a token handles the key and value heads
+    if (blockIdx.y + 1 < gridDim.y || !append) {
+        const int h0 = blockIdx.y * ROPE_GROUP, h1 = min(nh, h0 + ROPE_GROUP);
+        for (int idx = threadIdx.x; idx < (h1 - h0) * half; idx += blockDim.x) {
+            const int h = h0 + idx / half, i = idx % half;
+            T* x = row + (size_t)h * hd;
+            const float2 cs = cs_row[i];
+            const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
+            x[i] = from_f32<T>(x1 * cs.x - x2 * cs.y);
+            x[i + half] = from_f32<T>(x2 * cs.x + x1 * cs.y);
+        }
+        return;
     }
-    if (!append) return;
     const int pos = positions[t];
     const int page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
     if (page < 0 || page >= n_pages) return;   // the host reserved the pages; never write outside the cache
@@ -256,16 +261,18 @@ extern "C" int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride,
                rot, head_dim);
     HB_REQUIRE(rot == 0 || table != nullptr, "rope_kv_append: no rotary table");
     if (rot == 0 && !append) return 0;
-    const long long work = (long long)(n_heads + n_kv_heads) * (rot / 2) + (long long)n_kv_heads * head_dim;
+    const long long work = (long long)ROPE_GROUP * (rot / 2) + (long long)n_kv_heads * head_dim;
     const int threads = work >= 1024 ? 256 : work >= 256 ? 128 : 64;
+    const int groups = (n_heads + ROPE_GROUP - 1) / ROPE_GROUP + (append ? 1 : 0);
+    HB_REQUIRE(groups <= 65535, "rope_kv_append: too many heads");
     cudaStream_t s = (cudaStream_t)stream;
     const float2* tab = (const float2*)table;
     if (qkv_dtype == HB_BF16 && cache_dtype == HB_BF16)
-        hb_launch(rope_kv_append_kernel<bf16, bf16>, dim3(n_tokens), dim3(threads), 0, s, (bf16*)qkv, qkv_stride, tab, rot,
+        hb_launch(rope_kv_append_kernel<bf16, bf16>, dim3(n_tokens, groups), dim3(threads), 0, s, (bf16*)qkv, qkv_stride, tab, rot,
                   n_heads, n_kv_heads, head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table, pt_width, tok_seq, positions,
                   n_pages, append);
     else if (qkv_dtype == HB_F32 && cache_dtype == HB_F32)
-        hb_launch(rope_kv_append_kernel<float, float>, dim3(n_tokens), dim3(threads), 0, s, (float*)qkv, qkv_stride, tab, rot,
+        hb_launch(rope_kv_append_kernel<float, float>, dim3(n_tokens, groups), dim3(threads), 0, s, (float*)qkv, qkv_stride, tab, rot,
                   n_heads, n_kv_heads, head_dim, (float*)k_cache, (float*)v_cache, page_table, pt_width, tok_seq, positions,
                   n_pages, append);
     else

@@ -31,9 +31,35 @@ __device__ __forceinline__ void argmax_row(const float* __restrict__ row, int vo
                                            float* sval, int* sidx) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    if ((((uintptr_t)row) & 15) == 0) {
+        // 16-byte loads, four in flight per thread: one block has to pull a whole row
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const int n4 = vocab >> 2;
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * blockDim.x;
+                v[u] = i < n4 ? r4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int base = (i0 + u * blockDim.x) * 4;
+                const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    if (e[k] > best || (e[k] == best && base + k < bi)) { best = e[k]; bi = base + k; }
+            }
+        }
+        for (int i = (n4 << 2) + threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+        }
     }
     // a NaN never compares greater: a row of NaNs yields index 0x7fffffff, mapped to 0 below
 #pragma unroll
