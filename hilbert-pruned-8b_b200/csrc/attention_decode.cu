@@ -17,52 +17,22 @@
 #define AD_STAGES 3
 #define AD_LOG2E 1.4426950408889634f
 
-template <int HD>
-__global__ void __launch_bounds__(AD_THREADS)
-attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
-                   const int* __restrict__ page_table, int pt_width, const int* __restrict__ positions,
-                   float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, float scale_log2e,
-                   int window, int pages_per_split, int n_pages) {
-    pdl_trigger();
-    pdl_wait();
+// The work of one CTA on its range of pages [p_begin, p_end): scores, online softmax and
+// weighted values of the group's query heads (fragments `qf`, rows >= group size zero), each of
+// the 4 warps on a quarter of every page.  Leaves per-warp results in shared memory:
+// so[4][16][HD] unnormalised outputs, sm[4][16] maxima (log2 domain), sl[4][16] sums.
+// `after_prologue` runs once the first pages are requested and before any of them is used: the
+// place to build the query fragments (and to append a new key) while the loads are in flight.
+template <int HD, typename F>
+__device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], const bf16* kc, const bf16* vc,
+                                                  const int* __restrict__ pt, int n_pages, int nkv, int g, int lo,
+                                                  int len, int p_begin, int p_end, float scale_log2e, uint8_t* smem,
+                                                  F&& after_prologue) {
     constexpr int ROW_BYTES = HD * 2;
     constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;        // one page of K (or V) of one kv head
     constexpr int CHUNKS = ROW_BYTES / 16;
     constexpr int KSTEPS = HD / 16;
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z, S = gridDim.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int G = nh / nkv;
-    const int len = positions[b] + 1;
-    const int lo = (window > 0 && len - window > 0) ? len - window : 0;
-    const int p_begin = max(z * pages_per_split, lo / HB_PAGE_TOKENS);
-    const int p_end = min((z + 1) * pages_per_split, (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS);
-    const int* pt = page_table + (size_t)b * pt_width;
-
-    if (p_begin >= p_end) {                       // nothing to read: an empty partial
-        if (tid < G) {
-            float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
-            ml[0] = -INFINITY;
-            ml[1] = 0.0f;
-        }
-        return;
-    }
-
-    // query fragments: row r of the tile is head g*G + r (rows >= G are zero)
-    uint32_t qf[KSTEPS][4];
-    {
-        const int r0 = lane >> 2, c = (lane & 3) * 2;
-        const bf16* q0 = q + (size_t)b * q_stride + (size_t)(g * G + r0) * HD;
-        const bf16* q1 = q0 + (size_t)8 * HD;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ks++) {
-            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c) : 0u;
-            qf[ks][1] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c) : 0u;
-            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c + 8) : 0u;
-            qf[ks][3] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c + 8) : 0u;
-        }
-    }
-
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     auto load_page = [&](int stage, int page_idx) {
         if (page_idx < p_end) {
@@ -89,6 +59,7 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
 
 #pragma unroll
     for (int s = 0; s < AD_STAGES - 1; s++) load_page(s, p_begin + s);
+    after_prologue();
 
     for (int pi = p_begin; pi < p_end; pi++) {
         const int it = pi - p_begin;
@@ -188,6 +159,55 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
         }
     }
     __syncthreads();
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AD_THREADS)
+attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                   const int* __restrict__ page_table, int pt_width, const int* __restrict__ positions,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, float scale_log2e,
+                   int window, int pages_per_split, int n_pages) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int KSTEPS = HD / 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z, S = gridDim.x;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int G = nh / nkv;
+    const int len = positions[b] + 1;
+    const int lo = (window > 0 && len - window > 0) ? len - window : 0;
+    const int p_begin = max(z * pages_per_split, lo / HB_PAGE_TOKENS);
+    const int p_end = min((z + 1) * pages_per_split, (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS);
+    const int* pt = page_table + (size_t)b * pt_width;
+
+    if (p_begin >= p_end) {                       // nothing to read: an empty partial
+        if (tid < G) {
+            float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.0f;
+        }
+        return;
+    }
+
+    // query fragments: row r of the tile is head g*G + r (rows >= G are zero)
+    uint32_t qf[KSTEPS][4];
+    {
+        const int r0 = lane >> 2, c = (lane & 3) * 2;
+        const bf16* q0 = q + (size_t)b * q_stride + (size_t)(g * G + r0) * HD;
+        const bf16* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c) : 0u;
+            qf[ks][1] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c) : 0u;
+            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c + 8) : 0u;
+            qf[ks][3] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c + 8) : 0u;
+        }
+    }
+
+    decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [] {});
+    const float* so = reinterpret_cast<const float*>(smem);
+    const float* sm = so + 4 * 16 * HD;
+    const float* sl = sm + 4 * 16;
     for (int idx = tid; idx < G * HD; idx += AD_THREADS) {
         const int r = idx / HD, d = idx - r * HD;
         float M = -INFINITY;
@@ -208,6 +228,145 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
             part_ml[base * 2] = M;
             part_ml[base * 2 + 1] = L;
         }
+    }
+}
+
+// One rotated element of a head: x is the head's row before rotation, cs_row the token's
+// (cos, sin) pairs; pairs are (i, i + rot/2), elements beyond `rot` pass through
+// (cleanroom-transformer/src/cpu_backend.c:92-97).
+__device__ __forceinline__ float rotated(const bf16* __restrict__ x, int d, int rot, const float2* __restrict__ cs_row) {
+    const int half = rot >> 1;
+    if (d >= rot) return __bfloat162float(x[d]);
+    if (d < half) {
+        const float2 cs = cs_row[d];
+        return __bfloat162float(x[d]) * cs.x - __bfloat162float(x[d + half]) * cs.y;
+    }
+    const float2 cs = cs_row[d - half];
+    return __bfloat162float(x[d]) * cs.x + __bfloat162float(x[d - half]) * cs.y;
+}
+
+// The whole attention of a decode step in one launch: rotate the new token's queries and key,
+// append key and value to the cache, attend over the cache in splits, and let the last split
+// of a (sequence, kv head) to finish combine the partial results (a counter per pair, left at
+// zero).  qkv holds the projections BEFORE rotation; it is not written.  The split that owns
+// the page of the new position appends before it reads that page.
+template <int HD>
+__global__ void __launch_bounds__(AD_THREADS)
+attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot,
+                         bf16* kc, bf16* vc, const int* __restrict__ page_table, int pt_width,
+                         const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
+                         int* __restrict__ counters, bf16* __restrict__ out, long long out_stride, int nh, int nkv,
+                         float scale_log2e, int window, int pages_per_split, int n_pages, int append) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int KSTEPS = HD / 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int is_last;
+    const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z, S = gridDim.x;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int G = nh / nkv;
+    const int pos = positions[b], len = pos + 1;
+    const int lo = (window > 0 && len - window > 0) ? len - window : 0;
+    const int p_begin = max(z * pages_per_split, lo / HB_PAGE_TOKENS);
+    const int p_end = min((z + 1) * pages_per_split, (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS);
+    const int* pt = page_table + (size_t)b * pt_width;
+    const bf16* row = qkv + (size_t)b * qkv_stride;
+    const float2* cs_row = table + (size_t)b * (rot >> 1);
+
+    // The split that owns the page of the new position appends the rotated key and the value.
+    // With the page among the first ones requested it has to happen before the requests, else
+    // it runs while they are in flight.
+    const bool owner = append && z == (pos / HB_PAGE_TOKENS) / pages_per_split;
+    auto append_new = [&]() {
+        const int page = pt[pos / HB_PAGE_TOKENS];
+        if (page >= 0 && page < n_pages) {       // the host reserved the page; never write outside the cache
+            const bf16* kn = row + (size_t)(nh + g) * HD;
+            const bf16* vn = row + (size_t)(nh + nkv + g) * HD;
+            const size_t off = cache_offset(page, g, pos, nkv, HD);
+            for (int d = tid; d < HD; d += AD_THREADS) {
+                kc[off + d] = __float2bfloat16_rn(rotated(kn, d, rot, cs_row));
+                vc[off + d] = vn[d];
+            }
+        }
+        __threadfence();
+        __syncthreads();
+    };
+    const bool early_append = owner && (pos / HB_PAGE_TOKENS) < p_begin + AD_STAGES - 1;
+    if (owner && (early_append || p_begin >= p_end)) append_new();
+
+    if (p_begin < p_end) {
+        uint32_t qf[KSTEPS][4];
+        decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&]() {
+            if (owner && !early_append) append_new();
+            // query fragments, rotated: row r of the tile is head g*G + r (rows >= G are zero)
+            const int r0 = lane >> 2, c = (lane & 3) * 2;
+            const bf16* q0 = row + (size_t)(g * G + r0) * HD;
+            const bf16* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                const int d = ks * 16 + c;
+                qf[ks][0] = r0 < G ? pack_bf16(rotated(q0, d, rot, cs_row), rotated(q0, d + 1, rot, cs_row)) : 0u;
+                qf[ks][1] = r0 + 8 < G ? pack_bf16(rotated(q1, d, rot, cs_row), rotated(q1, d + 1, rot, cs_row)) : 0u;
+                qf[ks][2] = r0 < G ? pack_bf16(rotated(q0, d + 8, rot, cs_row), rotated(q0, d + 9, rot, cs_row)) : 0u;
+                qf[ks][3] = r0 + 8 < G ? pack_bf16(rotated(q1, d + 8, rot, cs_row), rotated(q1, d + 9, rot, cs_row)) : 0u;
+            }
+        });
+        const float* so = reinterpret_cast<const float*>(smem);
+        const float* sm = so + 4 * 16 * HD;
+        const float* sl = sm + 4 * 16;
+        for (int idx = tid; idx < G * HD; idx += AD_THREADS) {
+            const int r = idx / HD, d = idx - r * HD;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; w++) M = fmaxf(M, sm[w * 16 + r]);
+            float acc = 0.0f, L = 0.0f;
+            if (M != -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const float e = exp2f(sm[w * 16 + r] - M);
+                    acc += so[(size_t)(w * 16 + r) * HD + d] * e;
+                    L += sl[w * 16 + r] * e;
+                }
+            }
+            const size_t base = ((size_t)b * nh + g * G + r) * S + z;
+            part_o[base * HD + d] = acc;
+            if (d == 0) {
+                part_ml[base * 2] = M;
+                part_ml[base * 2 + 1] = L;
+            }
+        }
+    } else if (tid < G) {                        // nothing to read: an empty partial
+        float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.0f;
+    }
+
+    // the last split of this (sequence, kv head) to get here combines all of them
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(counters + (size_t)b * nkv + g, 1);
+        is_last = prev == S - 1;
+        if (is_last) counters[(size_t)b * nkv + g] = 0;     // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = tid; idx < G * HD; idx += AD_THREADS) {
+        const int r = idx / HD, d = idx - r * HD, head = g * G + r;
+        const size_t base = ((size_t)b * nh + head) * S;
+        float M = -INFINITY;
+        for (int zz = 0; zz < S; zz++) M = fmaxf(M, __ldcg(part_ml + (base + zz) * 2));
+        float L = 0.0f, acc = 0.0f;
+        for (int zz = 0; zz < S; zz++) {
+            const float mz = __ldcg(part_ml + (base + zz) * 2);
+            if (mz != -INFINITY) {
+                const float e = exp2f(mz - M);
+                L += __ldcg(part_ml + (base + zz) * 2 + 1) * e;
+                acc += __ldcg(part_o + (base + zz) * HD + d) * e;
+            }
+        }
+        out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
     }
 }
 
@@ -297,6 +456,60 @@ extern "C" int hb_attention_decode(const void* q, long long q_stride, const void
                                   batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
     return launch_decode<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride, batch,
                              n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+}
+
+template <int HD>
+static int launch_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
+                               const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
+                               void* out, long long out_stride, int batch, int nh, int nkv, float scale, int window,
+                               int splits, int pages_per_split, int n_pages, int append, cudaStream_t s) {
+    constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
+    constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
+    constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return hb_fail("attention_decode_fused: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)batch * nh * splits * HD;
+    hb_launch(attn_decode_fused_kernel<HD>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)qkv, stride,
+              (const float2*)table, rot, (bf16*)kc, (bf16*)vc, page_table, pt_width, positions, part_o, part_ml, counters,
+              (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, pages_per_split, n_pages, append);
+    return hb_check_launch("attention_decode_fused");
+}
+
+// The attention of a decode step in one launch.  qkv: [batch, stride] bfloat16 rows holding the
+// q, k and v projections of each sequence's new token BEFORE rotation (q heads first, then k
+// heads, then v heads); `table`: [batch, rot/2] (cos, sin) of the tokens' positions;
+// positions[b] is the new token's position.  With `append` the rotated key and the value are
+// written to the cache first.  `scratch` as for hb_attention_decode; `counters` holds
+// batch * n_kv_heads ints, zero before the first use (the kernel leaves them zero).
+extern "C" int hb_attention_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* k_cache,
+                                         void* v_cache, const int* page_table, int pt_width, const int* positions,
+                                         float* scratch, int* counters, void* out, long long out_stride, int batch,
+                                         int n_heads, int n_kv_heads, int head_dim, float scale, int window, int splits,
+                                         int max_pages, int n_pages, int append, void* stream) {
+    if (batch == 0) return 0;
+    HB_REQUIRE(hb_attention_decode_supported(n_heads, n_kv_heads, head_dim),
+               "attention_decode_fused: head size %d with %d heads over %d kv heads is not built (64 or 128, groups up to 16)",
+               head_dim, n_heads, n_kv_heads);
+    HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && scratch && counters, "attention_decode_fused: bad sizes");
+    HB_REQUIRE(batch <= 65535 && n_kv_heads <= 65535, "attention_decode_fused: batch or kv heads too large for one launch");
+    HB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0 && (rot == 0 || table), "attention_decode_fused: bad rotary size %d", rot);
+    HB_REQUIRE(stride % 2 == 0 && ((uintptr_t)qkv & 3) == 0, "attention_decode_fused: projections must be 4-byte aligned");
+    HB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_decode_fused: cache must be 16-byte aligned");
+    if (splits > max_pages) splits = max_pages;
+    const int pps = (max_pages + splits - 1) / splits;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_dim == 128)
+        return launch_decode_fused<128>(qkv, stride, table, rot, k_cache, v_cache, page_table, pt_width, positions, scratch,
+                                        counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits, pps,
+                                        n_pages, append, s);
+    return launch_decode_fused<64>(qkv, stride, table, rot, k_cache, v_cache, page_table, pt_width, positions, scratch,
+                                   counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages,
+                                   append, s);
 }
 
 // ------------------------------------------------------------------ no-allocation entry point

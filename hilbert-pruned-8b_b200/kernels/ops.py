@@ -36,6 +36,9 @@ _SIGNATURES = {
                              _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
     "hb_attention_decode": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                             _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_attention_decode_fused": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                  _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                  _c_ptr],
     "hb_attention_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                              _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr],
     "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -115,8 +118,14 @@ class Ops:
         self._splitk_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
         # split-K decode attention scratch: partial outputs with their maxima and sums
         self._decode_scratch = torch.empty(4 << 20, dtype=torch.float32, device=self.device)
+        self._decode_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
         self._retired = []              # outgrown scratch, kept alive for graphs that captured it
         self.use_fast_attention = True  # tests switch this off to compare with the general kernel
+        # One-launch decode attention (rotation + append + splits + combination).  Off: measured
+        # at batch 8 / 8192 tokens it is 5 us per layer SLOWER than the three kernels, because the
+        # small kernels between the big ones are where the next matrix product's CTAs get
+        # resident and request their first weight tiles.
+        self.fuse_decode_attention = False
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
@@ -276,6 +285,45 @@ class Ops:
         pages per split, at most 16 splits (measured: more splits cost more in the combine
         than they gain)."""
         return max(1, min(2 * self.sm_count // max(1, batch * kv_heads), -(-max_pages // 8), 16))
+
+    def can_fuse_decode_attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out) -> bool:
+        """Whether ``attention_decode_fused`` takes this step: one token per sequence,
+        bfloat16 everywhere, a head size and group the tensor-core kernel is built for."""
+        return bool(self.fuse_decode_attention and self.use_fast_attention and step.is_decode
+                    and qkv.dtype == torch.bfloat16
+                    and cache.k.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                    and cache.k.is_contiguous() and cache.v.is_contiguous()
+                    and step.num_tokens * kv_heads <= self._decode_counters.numel()
+                    and self.lib.hb_attention_decode_supported(heads, kv_heads, head_dim))
+
+    def attention_decode_fused(self, qkv, table, rot: int, heads: int, kv_heads: int, head_dim: int, cache, step, out,
+                               scale: float, window: Optional[int], append: bool, splits: Optional[int] = None) -> None:
+        """Rotation of the new tokens' queries and keys, cache append, split-K attention and the
+        combination of the splits in ONE launch (decode steps only).  ``qkv`` holds the
+        projections before rotation and is not written."""
+        self._dev(qkv, table, cache.k, cache.v, out)
+        T = qkv.shape[0]
+        pt = step.page_tables[cache.group]
+        if out.shape[0] != T or out.shape[1] != heads * head_dim:
+            raise KernelError("attention: output shape does not match")
+        if rot and (table is None or table.shape[0] != T or table.shape[1] != rot // 2):
+            raise KernelError("attention: rotary table does not match the tokens")
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim):
+            raise KernelError("attention: cache layer shape does not match the heads")
+        max_pages = (step.max_len + 63) // 64
+        n_splits = splits if splits is not None else self.decode_splits_for(T, kv_heads, max_pages)
+        n_splits = max(1, min(n_splits, max_pages))
+        need = self.lib.hb_attention_decode_scratch_floats(T, heads, head_dim, n_splits)
+        if need > self._decode_scratch.numel():
+            self._retired.append(self._decode_scratch)
+            self._decode_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+        self._call("hb_attention_decode_fused", qkv.data_ptr(), _rows(qkv, "attention projections"),
+                   table.data_ptr() if rot else None, rot, cache.k.data_ptr(), cache.v.data_ptr(), pt.data_ptr(),
+                   pt.shape[1], step.positions.data_ptr(), self._decode_scratch.data_ptr(),
+                   self._decode_counters.data_ptr(), out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,
+                   head_dim, float(scale), int(window) if window else 0, n_splits, max_pages, cache.k.shape[0],
+                   1 if append else 0, self._stream())
+        self.launches += 1
 
     def attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out, scale: float,
                   window: Optional[int], splits: Optional[int] = None) -> None:

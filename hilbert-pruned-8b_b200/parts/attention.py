@@ -71,7 +71,13 @@ class Attention(Mixer):
             ops.linear(h, self.w_qkv[: self.q_width], qkv[:, : self.q_width])
         table = self.position.table(step) if self.position is not None else None
         rot = self.position.rotary_dim if self.position is not None else 0
-        ops.rope_kv_append(qkv, table, rot, self.heads, self.kv_heads, self.head_dim, cache, step, append)
         attn = ws.buffer("attention.out", (cap, self.q_width), self.ctx.dtype)[:T]
-        ops.attention(qkv, self.heads, self.kv_heads, self.head_dim, cache, step, attn, self.scale, self.window)
+        if ops.can_fuse_decode_attention(qkv, self.heads, self.kv_heads, self.head_dim, cache, step, attn):
+            # one token per sequence: rotation, append, attention and the combination of its
+            # splits are one launch
+            ops.attention_decode_fused(qkv, table, rot, self.heads, self.kv_heads, self.head_dim, cache, step, attn,
+                                       self.scale, self.window, append)
+        else:
+            ops.rope_kv_append(qkv, table, rot, self.heads, self.kv_heads, self.head_dim, cache, step, append)
+            ops.attention(qkv, self.heads, self.kv_heads, self.head_dim, cache, step, attn, self.scale, self.window)
         ops.linear(attn, self.w_o, residual, accumulate=True)

@@ -108,3 +108,15 @@ def test_step_cut_into_chunks(model_folders, dtype):
     eng = _engine(model_folders[model], dtype, peak, max_step_tokens=32)
     got = tt.run_in_process(eng, steps)
     tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "chunked")
+
+
+@pytest.mark.parametrize("model", ["strong_c", "strong_d"])
+def test_one_launch_decode_attention_in_the_engine(model_folders, model):
+    """The optional one-launch decode attention gives the same logits as the three kernels."""
+    require_gpu()
+    reqs = _requests(model, [70, 33, 130], seed=650)
+    steps, peak = tt.trace_batches([{rid: (t, 5 + 20 * i) for i, (rid, t) in enumerate(reqs.items())}])
+    eng = _engine(model_folders[model], "bfloat16", peak)
+    eng.ctx.ops.fuse_decode_attention = True
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], "bfloat16"), reqs), "bfloat16", "fused decode attention")

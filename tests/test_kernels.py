@@ -343,6 +343,65 @@ def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
         assert _rel(out, gen.double()) < 2 ** -7
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot,window", [(8, 2, 128, 128, None), (3, 1, 64, 64, None), (16, 1, 64, 32, 100),
+                                                  (10, 5, 128, 128, 65)])
+def test_attention_decode_fused_equals_the_three_kernels(ops, nh, nkv, hd, rot, window):
+    """The one-launch decode attention (rotation, append, splits, combination) against the
+    separate rope/append, attention and combine kernels, twice in a row (counters return to
+    zero), with lengths at page edges and a first token."""
+    torch.manual_seed(14)
+    dtype = torch.bfloat16
+    scale = 1.0 / math.sqrt(hd)
+    positions = [130, 0, 63, 300, 64]
+    B = len(positions)
+    tables = torch.tensor([[7, 1, 4, -1, -1], [3, 8, -1, -1, -1], [0, 15, -1, -1, -1], [9, 10, 11, 12, 13],
+                           [2, 5, -1, -1, -1]], dtype=torch.int32, device=DEV)
+    base = _cache(16, nkv, hd, dtype)
+    base.k.normal_()
+    base.v.normal_()
+    step = _step(torch.arange(B, dtype=torch.int32, device=DEV), torch.tensor(positions, dtype=torch.int32, device=DEV), tables)
+    step.is_decode, step.host_new, step.num_seqs, step.num_tokens = True, [1] * B, B, B
+    step.max_len = max(positions) + 1
+    step.seq_start = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    step.seq_pos0 = step.positions
+    inv = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+    table = torch.empty(B, rot // 2, 2, device=DEV)
+    ops.rope_table(step.positions, inv, table)
+    for rep in range(2):
+        qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=DEV).to(dtype)
+        from hilbert_pruned_8b_b200.cache import LayerCache
+        c1 = LayerCache(base.k.clone(), base.v.clone(), 0, None)
+        c2 = LayerCache(base.k.clone(), base.v.clone(), 0, None)
+        q1 = qkv.clone()
+        ops.rope_kv_append(q1, table, rot, nh, nkv, hd, c1, step, True)
+        want = torch.empty(B, nh * hd, device=DEV, dtype=dtype)
+        ops.attention(q1, nh, nkv, hd, c1, step, want, scale, window)
+        for splits in (None, 1, 3):
+            c3 = LayerCache(c2.k.clone(), c2.v.clone(), 0, None)
+            got = torch.full_like(want, 9.0)
+            before = qkv.clone()
+            ops.fuse_decode_attention = True
+            try:
+                assert ops.can_fuse_decode_attention(qkv, nh, nkv, hd, c3, step, got)
+            finally:
+                ops.fuse_decode_attention = False
+            ops.attention_decode_fused(qkv, table, rot, nh, nkv, hd, c3, step, got, scale, window, True, splits=splits)
+            assert torch.equal(qkv, before)
+            assert torch.equal(c3.k, c1.k) and torch.equal(c3.v, c1.v), "appended keys or values differ"
+            assert _rel(got, want.double()) < 2 ** -8, f"splits={splits}"
+        assert int(ops._decode_counters.abs().sum()) == 0
+    # a layer that reads another layer's cache: no append, the new key is not there
+    c4 = LayerCache(base.k.clone(), base.v.clone(), 0, None)
+    got = torch.empty(B, nh * hd, device=DEV, dtype=dtype)
+    ops.attention_decode_fused(qkv, table, rot, nh, nkv, hd, c4, step, got, scale, window, False)
+    assert torch.equal(c4.k, base.k) and torch.equal(c4.v, base.v)
+    q1 = qkv.clone()
+    ops.rope_kv_append(q1, table, rot, nh, nkv, hd, c4, step, False)
+    want = torch.empty_like(got)
+    ops.attention(q1, nh, nkv, hd, c4, step, want, scale, window)
+    assert _rel(got, want.double()) < 2 ** -8
+
+
 def test_attention_finds_a_far_key(ops):
     """One key among hundreds matches the query: the output must be that key's value."""
     nh, nkv, hd, n = 4, 2, 32, 700
