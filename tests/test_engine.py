@@ -120,3 +120,16 @@ def test_one_launch_decode_attention_in_the_engine(model_folders, model):
     eng.ctx.ops.fuse_decode_attention = True
     got = tt.run_in_process(eng, steps)
     tt.compare(got, tt.plain_logits(_plain(model_folders[model], "bfloat16"), reqs), "bfloat16", "fused decode attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("model", ["strong_c", "strong_d"])
+def test_hundreds_of_keys_through_the_tensor_core_attention(model_folders, model, dtype):
+    """A 600-token prompt, then 40 tokens one by one, next to a short request: ten pages of keys
+    per sequence, prefill blocks that start inside pages, decode splits over many pages."""
+    require_gpu()
+    reqs = _requests(model, [640, 90], seed=660)
+    steps, peak = tt.trace_batches([{"r0": (reqs["r0"], 600), "r1": (reqs["r1"], 50)}])
+    eng = _engine(model_folders[model], dtype, peak, max_step_tokens=1024)
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], dtype), reqs), dtype, "hundreds of keys")

@@ -402,26 +402,31 @@ def test_attention_decode_fused_equals_the_three_kernels(ops, nh, nkv, hd, rot, 
     assert _rel(got, want.double()) < 2 ** -8
 
 
-def test_attention_finds_a_far_key(ops):
-    """One key among hundreds matches the query: the output must be that key's value."""
-    nh, nkv, hd, n = 4, 2, 32, 700
+@pytest.mark.parametrize("hd,dtype", [(32, torch.float32), (128, torch.bfloat16), (64, torch.bfloat16)])
+def test_attention_finds_a_far_key(ops, hd, dtype):
+    """One key among hundreds matches the query: the output must be that key's value (general
+    kernel for head size 32, the split-K decode kernel for 64 and 128)."""
+    nh, nkv, n = 4, 2, 700
     torch.manual_seed(10)
-    cache = _cache(12, nkv, hd, torch.float32)
+    cache = _cache(12, nkv, hd, dtype)
     tables = torch.arange(11, -1, -1, dtype=torch.int32, device=DEV).view(1, 12)
     k = torch.randn(n, nkv, hd) * 0.1
     v = torch.randn(n, nkv, hd)
     needle = 137
     k[needle, 1] = torch.ones(hd) * 3.0
+    v = v.to(dtype).float()
     for s in range(n):
-        cache.k[int(tables[0, s // 64]), :, s % 64] = k[s].to(DEV)
-        cache.v[int(tables[0, s // 64]), :, s % 64] = v[s].to(DEV)
-    qkv = torch.zeros(1, (nh + 2 * nkv) * hd, device=DEV)
+        cache.k[int(tables[0, s // 64]), :, s % 64] = k[s].to(dtype).to(DEV)
+        cache.v[int(tables[0, s // 64]), :, s % 64] = v[s].to(dtype).to(DEV)
+    qkv = torch.zeros(1, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
     qkv[0, 3 * hd:4 * hd] = 10.0                                   # head 3 reads kv head 1
-    out = torch.empty(1, nh * hd, device=DEV)
+    out = torch.empty(1, nh * hd, device=DEV, dtype=dtype)
     step = _step(torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV), tables)
+    step.is_decode, step.host_new, step.num_seqs, step.max_len, step.num_tokens = True, [1], 1, n, 1
     ops.attention(qkv, nh, nkv, hd, cache, step, out, 1.0 / math.sqrt(hd), None)
-    assert (out[0, 3 * hd:].cpu() - v[needle, 1]).abs().max() < 1e-4
-    assert (out[0, :hd].cpu() - v[:, 0].mean(0)).abs().max() < 1e-4   # a zero query averages the values
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert (out[0, 3 * hd:].float().cpu() - v[needle, 1]).abs().max() < tol
+    assert (out[0, :hd].float().cpu() - v[:, 0].mean(0)).abs().max() < tol   # a zero query averages the values
 
 
 # ------------------------------------------------------------------------------- sampling

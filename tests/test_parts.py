@@ -318,3 +318,38 @@ def test_run_order_names_a_layer_twice_and_shares_a_cache(model_folders):
     for make in (tt.trace_whole, lambda r: tt.trace_tail(r, 20), lambda r: tt.trace_batches([{"u": (r["u"], 9), "w": (r["w"], 64)}])):
         steps, _ = make(reqs)
         tt.compare(tt.run_in_process(eng, steps), ref, "float32", "planned")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("model,window", [("strong_c", 40), ("strong_b", 70), ("strong_d", 64)])
+def test_windowed_layers_give_pages_back_and_match_plain(model_folders, model, window, dtype):
+    """Every layer with a window: the cache group frees pages that no later token can see
+    (their page-table entries become -1) and the kernels mask the window's edge."""
+    require_gpu()
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.config import PartSpec
+    from hilbert_pruned_8b_b200.engine.step import Engine
+    from hilbert_pruned_8b_b200.weights import load_tensors
+    folder = model_folders[model]
+    spec = hb.load_config(folder).model_spec()
+    layers = [dataclasses.replace(ls, mixer=PartSpec("attention", {**ls.mixer.params, "window": window})) for ls in spec.layers]
+    spec = dataclasses.replace(spec, layers=layers)
+    eng = Engine(spec, dtype, max_tokens=64 * 12)
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    eng.model.bind(load_tensors(folder, eng.model.weight_table(), tdt, eng.device))
+    eng._make_cache()
+    vocab = spec.vocab_size
+    reqs = {"a": tt.random_tokens(330, vocab, 920), "b": tt.random_tokens(150, vocab, 921)}
+    plain = pl.PlainLlama(folder, round_to=torch.bfloat16 if dtype == "bfloat16" else None, window=window)
+    ref = tt.plain_logits(plain, reqs)
+    steps, _ = tt.trace_batches([{"a": (reqs["a"], 200), "b": (reqs["b"], 1)}])
+    got = tt.run_in_process(eng, steps)
+    tt.compare(got, ref, dtype, "windowed")
+    # while "a" was 330 tokens long it held only the pages its window reaches, not all six
+    seq = eng.open_sequence()
+    eng.step_chunked([__import__("hilbert_pruned_8b_b200").engine.StepEntry(seq, reqs["a"][:300], [])])
+    eng.step([__import__("hilbert_pruned_8b_b200").engine.StepEntry(seq, [reqs["a"][300]], [0])])
+    held = [p for p in seq.pages[0] if p is not None]
+    assert len(seq.pages[0]) == 5 and len(held) <= (window + 63) // 64 + 1
+    eng.close_sequence(seq)
+    assert min(eng.cache.pages_free()) == eng.cache.num_pages
