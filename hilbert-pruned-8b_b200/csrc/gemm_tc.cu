@@ -35,100 +35,8 @@
 //
 // Requirements (checked on the host, refused with a message otherwise): bfloat16 A and W,
 // 16-byte aligned bases, row strides that are multiples of 8 elements.  Any M, N and K.
-#include <cuda.h>
-
 #include "api.h"
-#include "common.cuh"
-
-#define TC_BM 128           // features per tile (MMA M)
-#define TC_BK 64            // K per stage: 64 bf16 = one 128-byte swizzle row
-#define TC_THREADS 192
-#define TC_WAIT_LIMIT (1u << 24)
-
-enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_SWIGLU_BF16 = 3 };
-
-// ------------------------------------------------------------------------------- PTX
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-// Bounded wait; returns false when it ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t addr, float* v) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
-// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
-    d |= (uint64_t)1 << 46;                 // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
+#include "tcgen05.cuh"
 
 template <int BN, int MODE>
 struct TcLayout {
@@ -139,23 +47,7 @@ struct TcLayout {
     static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
     static constexpr int NBUF = 2;                                     // accumulator buffers
     static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
-    static constexpr int XCHG_BYTES = SWIGLU ? (2 * 16 * 64 * 4 + 2 * 16 * 64 * 2) : 0;
-};
-
-struct TcParams {
-    void* out;
-    long long ldc;
-    int M, N, K;
-    int up_row0;          // SWIGLU: row of W where the up rows start
-    int tiles_m, tiles_n;
-    int kb_total;         // K blocks per tile
-    int stream_k;         // 0: whole tiles round-robin; 1: contiguous (tile, K block) ranges per CTA;
-                          // 2: every tile cut into `split` equal K ranges, one per CTA
-    int split;
-    int max_slots;        // partial tiles per output tile in scratch (stream-K)
-    float* partials;
-    int* counters;
-    int* error_flag;
+    static constexpr int XCHG_BYTES = SWIGLU ? TC_XCHG_BYTES : 0;
 };
 
 // The work items of one CTA, in order: (tile, first K block, end K block).
@@ -430,57 +322,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             for (int j = 0; j < 16; j++) v[j] += __ldcg(pz + (size_t)(c + j) * TC_BM + row);
                         }
                     }
-                    if (SWIGLU) {
-                        // rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same
-                        // features: pair them through shared memory, then store 16 bytes per thread
-                        float* xf = (float*)xchg + ((c >> 4) & 1) * (16 * 64);
-                        bf16* yb = (bf16*)(xchg + 2 * 16 * 64 * 4) + ((c >> 4) & 1) * (16 * 64);
-                        if (q >= 2) {
-#pragma unroll
-                            for (int j = 0; j < 16; j++) xf[j * 64 + row - 64] = v[j];
-                        }
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (q < 2) {
-#pragma unroll
-                            for (int j = 0; j < 16; j++) yb[j * 64 + row] = __float2bfloat16_rn(silu_f32(v[j]) * xf[j * 64 + row]);
-                        }
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        const int r = et >> 3, ch = et & 7;                 // token row of the chunk, 8-feature group
-                        const int m = m0 + c + r, n = n0 + ch * 8;
-                        if (m < p.M && n < p.N) {
-                            bf16* o = (bf16*)p.out + (size_t)m * p.ldc + n;
-                            if (n + 8 <= p.N) {
-                                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(yb + r * 64 + ch * 8);
-                            } else {
-                                for (int e = 0; e < p.N - n; e++) o[e] = yb[r * 64 + ch * 8 + e];
-                            }
-                        }
-                    } else {
-                        const int f = n0 + row;
-                        if (f < p.N) {
-                            if (MODE == TC_ADD_F32) {
-                                // all loads of the residual first, then the stores: written one by one
-                                // the compiler must keep each load behind the store before it
-                                float r[16];
-                                float* po = (float*)p.out + (size_t)(m0 + c) * p.ldc + f;
-#pragma unroll
-                                for (int j = 0; j < 16; j++) r[j] = (m0 + c + j < p.M) ? __ldcg(po + (size_t)j * p.ldc) : 0.0f;
-#pragma unroll
-                                for (int j = 0; j < 16; j++)
-                                    if (m0 + c + j < p.M) po[(size_t)j * p.ldc] = r[j] + v[j];
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 16; j++) {
-                                    const int m = m0 + c + j;
-                                    if (m < p.M) {
-                                        const size_t o = (size_t)m * p.ldc + f;
-                                        if (MODE == TC_STORE_BF16) ((bf16*)p.out)[o] = __float2bfloat16_rn(v[j]);
-                                        else ((float*)p.out)[o] = v[j];
-                                    }
-                                }
-                            }
-                        }
-                    }
+                    tc_emit_chunk<MODE>(p, m0, n0, c, v, xchg, q, row, et);
                 }
             }
             if (whole) {
@@ -519,7 +361,7 @@ static EncodeTiledFn get_encode() {
 
 // Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements): boxes of
 // box_rows x 64 elements, 128-byte swizzle, zeros outside.
-static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+int tc_make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return hb_fail("gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -655,8 +497,8 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
                    "gemm_tc: stream-K needs %lld scratch floats and %lld counters", pl.scratch_floats, pl.tiles);
     }
     CUtensorMap mw, ma;
-    if (make_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM)) return 1;
-    if (make_map(&ma, a, M, K, lda, pl.bn)) return 1;
+    if (tc_make_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM)) return 1;
+    if (tc_make_map(&ma, a, M, K, lda, pl.bn)) return 1;
     TcParams prm;
     prm.out = out;
     prm.ldc = ldc;

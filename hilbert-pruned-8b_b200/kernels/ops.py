@@ -32,6 +32,7 @@ _SIGNATURES = {
                         _c_int, _c_ptr],
     "hb_gemm_tc": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr],
+    "hb_gemm_tc2": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                              _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
     "hb_attention_decode": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
@@ -69,6 +70,8 @@ def load_library():
         lib.hb_gemm_tc_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int, _c_int]
         lib.hb_gemm_tc_scratch_floats.restype = _c_ll
         lib.hb_gemm_tc_tiles.argtypes, lib.hb_gemm_tc_tiles.restype = [_c_int, _c_int, _c_int], _c_ll
+        lib.hb_gemm_tc2_wanted.argtypes, lib.hb_gemm_tc2_wanted.restype = [_c_int, _c_int, _c_int], _c_int
+        lib.hb_gemm_tc2_resident_pairs.argtypes, lib.hb_gemm_tc2_resident_pairs.restype = [_c_int], _c_int
         for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported"):
             getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
@@ -111,6 +114,7 @@ class Ops:
             raise KernelError(f"the kernels are built for sm_100a; device {idx} is sm_{major.value}{minor.value}")
         self.launches = 0  # kernels launched through this object (a claim bench.py reports)
         self.use_tensor_cores = True   # tests switch this off to compare the two matrix-product kernels
+        self.use_pair_gemm = True      # many-token products on CTA pairs (cta_group::2)
         # device status word the tensor-core kernels set when one of their bounded waits ran out
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         # split-K scratch: float32 partial tiles and one counter per output tile (kept zero)
@@ -232,6 +236,13 @@ class Ops:
 
     def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None) -> None:
         M, K = a.shape
+        if schedule == "pairs" or (schedule is None and self.use_pair_gemm and self.lib.hb_gemm_tc2_wanted(M, N, K)):
+            # many tokens: CTA pairs (cta_group::2) on 256 x 256 tiles
+            self._call("hb_gemm_tc2", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), _rows(w, "linear weight"),
+                       w.shape[0], out.data_ptr(), _rows(out, "linear output"), M, N, K, mode, up_row0,
+                       self.error_flag.data_ptr(), self._stream())
+            self.launches += 1
+            return
         sched = self.SCHEDULES[schedule]
         need = self.lib.hb_gemm_tc_scratch_floats(M, N, K, mode, sched)
         tiles = self.lib.hb_gemm_tc_tiles(M, N, mode)

@@ -215,7 +215,33 @@ def test_gemm_tensor_core_stream_k_and_tiles(ops, M, N, K):
         assert torch.equal(out, again)          # the sum order is fixed
 
 
-@pytest.mark.parametrize("schedule", ["tiles", "stream_k"])
+@pytest.mark.parametrize("M,N,K", [(512, 256, 64), (300, 640, 256), (1000, 1100, 520), (2048, 1024, 1024), (1, 128, 64),
+                                   (257, 129, 72)])
+def test_gemm_tensor_core_cta_pairs(ops, M, N, K):
+    """The cta_group::2 kernel (256 x 256 tiles on pairs of CTAs) with every epilogue, at sizes
+    with partial tiles in every dimension, against the plain product and the single-CTA kernel."""
+    torch.manual_seed(15)
+    a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
+    ref = a.double() @ w.double().t()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), 7.0, device=DEV, dtype=out_dtype)
+        ops.linear(a, w, out, schedule="pairs")
+        ops.check_errors()
+        assert _rel(out, ref) < (2 ** -8 if out_dtype == torch.bfloat16 else 2e-6 * math.sqrt(K))
+    res = torch.randn(M, N, device=DEV)
+    acc = res.clone()
+    ops.linear(a, w, acc, accumulate=True, schedule="pairs")
+    ops.check_errors()
+    assert _rel(acc, ref + res.double()) < 2e-6 * math.sqrt(K)
+    one = torch.empty(M, N, device=DEV)
+    ops.linear(a, w, one, schedule="tiles")
+    two = torch.empty(M, N, device=DEV)
+    ops.linear(a, w, two, schedule="pairs")
+    assert _rel(two, one) < 1e-6 * math.sqrt(K)
+    assert ops.lib.hb_gemm_tc2_resident_pairs(0) >= 32
+
+
+@pytest.mark.parametrize("schedule", ["tiles", "stream_k", "pairs"])
 @pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 304), (8, 4096, 512), (300, 512, 1000)])
 def test_linear_swiglu(ops, M, K, I, schedule):
     from hilbert_pruned_8b_b200.engine.workspace import Workspace
