@@ -27,6 +27,9 @@
 #define T2_TOKENS 256          // tokens per pair tile (MMA N)
 #define T2_HALF 128            // tokens loaded by each CTA
 #define T2_STAGE_BYTES (TC_BM * TC_BK * 2 + T2_HALF * TC_BK * 2)     // 32 KB per CTA and stage
+// 6 stages of 32 KB; a 7th (measured) changes nothing, and asking L2 ahead for the weight tiles
+// of later K blocks (cp.async.bulk.prefetch) made the kernel slower
+#define T2_STAGES(MODE) 6
 
 template <int MODE, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
@@ -209,7 +212,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 template <int MODE>
 static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int pairs, cudaStream_t s) {
-    constexpr int STAGES = 6;
+    constexpr int STAGES = T2_STAGES(MODE);
     constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? TC_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(SMEM <= 227 * 1024, "tile pipeline does not fit shared memory");
     static bool attr_set = false;
@@ -227,7 +230,7 @@ static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& ma, const TcPara
 // leaves one without a partner): the persistent grid must not be larger.
 template <int MODE>
 static int query_pairs() {
-    constexpr int STAGES = 6;
+    constexpr int STAGES = T2_STAGES(MODE);
     constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? TC_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
     cudaFuncSetAttribute(gemm_tc2_kernel<MODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     cudaLaunchConfig_t cfg = {};
