@@ -42,6 +42,8 @@ _SIGNATURES = {
                                   _c_ptr],
     "hb_attention_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                              _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr],
+    "hb_attention_prefill_tc": [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int,
+                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
 }
@@ -72,7 +74,7 @@ def load_library():
         lib.hb_gemm_tc_tiles.argtypes, lib.hb_gemm_tc_tiles.restype = [_c_int, _c_int, _c_int], _c_ll
         lib.hb_gemm_tc2_wanted.argtypes, lib.hb_gemm_tc2_wanted.restype = [_c_int, _c_int, _c_int], _c_int
         lib.hb_gemm_tc2_resident_pairs.argtypes, lib.hb_gemm_tc2_resident_pairs.restype = [_c_int], _c_int
-        for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported"):
+        for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported", "hb_attention_prefill_tc_supported"):
             getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
         lib.hb_attention_decode_scratch_floats.restype = _c_ll
@@ -124,6 +126,7 @@ class Ops:
         self._decode_scratch = torch.empty(4 << 20, dtype=torch.float32, device=self.device)
         self._decode_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
         self._retired = []              # outgrown scratch, kept alive for graphs that captured it
+        self.use_tcgen05_attention = True   # head size 128 prefill on tcgen05 (else the mma.sync kernel)
         self.use_fast_attention = True  # tests switch this off to compare with the general kernel
         # One-launch decode attention (rotation + append + splits + combination).  Off: measured
         # at batch 8 / 8192 tokens it is 5 us per layer SLOWER than the three kernels, because the
@@ -363,6 +366,16 @@ class Ops:
                        self._decode_scratch.data_ptr(), out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,
                        head_dim, float(scale), win, n_splits, max_pages, cache.k.shape[0], self._stream())
             self.launches += 2
+            return
+        if (fast and self.use_tcgen05_attention and self.lib.hb_attention_prefill_tc_supported(heads, kv_heads, head_dim)
+                and qkv.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and _rows(qkv, "attention queries") % 8 == 0
+                and _rows(out, "attention output") % 8 == 0):
+            q_blocks = sum((n + 127) // 128 for n in step.host_new)
+            self._call("hb_attention_prefill_tc", qkv.data_ptr(), _rows(qkv, "attention queries"), T, cache.k.data_ptr(),
+                       cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(),
+                       out.data_ptr(), _rows(out, "attention output"), step.num_seqs, q_blocks, heads, kv_heads, head_dim,
+                       float(scale), win, cache.k.shape[0], self.error_flag.data_ptr(), self._stream())
+            self.launches += 1
             return
         if fast and self.lib.hb_attention_prefill_supported(heads, kv_heads, head_dim):
             q_blocks = sum((n + 63) // 64 for n in step.host_new)
