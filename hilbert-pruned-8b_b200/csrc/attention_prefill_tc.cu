@@ -4,13 +4,15 @@
 //
 // One CTA = 128 consecutive new tokens of one sequence x one query head.  The 128 query rows
 // are the 128 lanes of tensor memory.  Keys and values come in tiles of 128 keys (two pages).
-//   warp 0     TMA producer: the query tile once, then K and V tiles (two stages of 64 KB)
+//   warp 0     TMA producer: the query tile once, then K tiles and V tiles (three stages of
+//              32 KB each, freed separately: a K tile right after S_j, a V tile after O += P_j V_j)
 //   warp 1     owns tensor memory; one thread issues the MMAs:
 //                S_j = Q K_j^T      (operands in shared memory, K-major, 8 x K16)
 //                O  += P_j V_j      (P_j from tensor memory, V_j in shared memory as stored:
 //                                    keys are rows, an MN-major B operand)
-//   warps 2-5  softmax: thread r owns query row r: reads S_j from tensor memory, keeps the
-//              running maximum and sum in float32, writes P_j (bfloat16) over S_j
+//   warps 2-9  softmax: two threads per query row (64 key columns each): they read S_j from
+//              tensor memory, agree on the row's maximum through shared memory, keep the
+//              running maximum and sum in float32 and write P_j (bfloat16) over S_j
 // Two S buffers: the softmax of tile j runs while the tensor cores compute S_{j+1}.  The
 // output accumulator stays in tensor memory; it is rescaled only when a row's maximum grows by
 // more than 2^8 (probabilities are taken against a maximum that may be stale by less).
@@ -26,38 +28,37 @@
 #define FA_HD 128
 #define FA_HALF_BYTES (128 * 64 * 2)                 // 128 rows x 64 elements: one swizzle-wide sub-tile
 #define FA_TILE_BYTES (2 * FA_HALF_BYTES)            // 128 x 128 bf16
-#define FA_STAGES 2
+#define FA_STAGES 3
 #define FA_LOG2E 1.4426950408889634f
 #define FA_RESCALE_THRESHOLD 8.0f
+#define FA_THREADS 320                                // producer, MMA, 8 softmax warps
 
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, float* v) {
     uint32_t r[32];
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(addr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
-// the same without the wait: several loads in flight, then one tmem_wait_ld()
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, float* v) {
+// 64 consecutive columns of this thread's lane, loaded and waited for in ONE asm statement, so
+// that no use of the values can be scheduled before the wait
+__device__ __forceinline__ void tmem_ld64(uint32_t addr, float* v) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-        "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
-          "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]),
-          "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]),
-          "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
-        : "r"(addr)
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31]), "=f"(v[32]), "=f"(v[33]), "=f"(v[34]), "=f"(v[35]), "=f"(v[36]), "=f"(v[37]), "=f"(v[38]), "=f"(v[39]), "=f"(v[40]), "=f"(v[41]), "=f"(v[42]), "=f"(v[43]), "=f"(v[44]), "=f"(v[45]), "=f"(v[46]), "=f"(v[47]), "=f"(v[48]), "=f"(v[49]), "=f"(v[50]), "=f"(v[51]), "=f"(v[52]), "=f"(v[53]), "=f"(v[54]), "=f"(v[55]), "=f"(v[56]), "=f"(v[57]), "=f"(v[58]), "=f"(v[59]), "=f"(v[60]), "=f"(v[61]), "=f"(v[62]), "=f"(v[63])
+        : "r"(addr), "r"(addr + 32)
         : "memory");
 }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // 2^x on the special-function unit (float32, about 2 ulp); 2^-inf = 0
 __device__ __forceinline__ float exp2_approx(float x) {
     float y;
@@ -114,7 +115,7 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t l
     return d;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int pt_width,
                        const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, bf16* __restrict__ out,
@@ -122,13 +123,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        int* __restrict__ error_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    // [Q 32 KB][stage 0: K 32 KB, V 32 KB][stage 1: K, V][barriers]
+    // [Q 32 KB][K stages 3 x 32 KB][V stages 3 x 32 KB][barriers]
     uint64_t* bars = (uint64_t*)(smem + FA_TILE_BYTES + FA_STAGES * 2 * FA_TILE_BYTES);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 18);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* xrow = (float*)(tmem_slot + 4);                    // [2 halves][128 rows]: row maxima, at the end row sums
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t q_full = smem_u32(bars), kv_full0 = smem_u32(bars + 1), kv_empty0 = smem_u32(bars + 3);
-    const uint32_t s_full0 = smem_u32(bars + 5), p_full0 = smem_u32(bars + 7), pv_done = smem_u32(bars + 9);
+    const uint32_t k_smem = smem_base + FA_TILE_BYTES, v_smem = k_smem + FA_STAGES * FA_TILE_BYTES;
+    const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), k_empty0 = smem_u32(bars + 4);
+    const uint32_t v_full0 = smem_u32(bars + 7), v_empty0 = smem_u32(bars + 10);
+    const uint32_t s_full0 = smem_u32(bars + 13), p_full0 = smem_u32(bars + 15), pv_done = smem_u32(bars + 17);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y, g = head / (nh / nkv);
 
@@ -152,11 +156,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        for (int s = 0; s < FA_STAGES; s++) {
+            mbar_init(k_full0 + 8 * s, 1);
+            mbar_init(k_empty0 + 8 * s, 1);
+            mbar_init(v_full0 + 8 * s, 1);
+            mbar_init(v_empty0 + 8 * s, 1);
+        }
         for (int s = 0; s < 2; s++) {
-            mbar_init(kv_full0 + 8 * s, 1);
-            mbar_init(kv_empty0 + 8 * s, 1);
             mbar_init(s_full0 + 8 * s, 1);
-            mbar_init(p_full0 + 8 * s, 128);
+            mbar_init(p_full0 + 8 * s, 256);
         }
         mbar_init(pv_done, 1);
         *abort_flag = 0;
@@ -179,31 +187,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_expect_tx(q_full, FA_TILE_BYTES);
             tma_load_2d(smem_base, &map_q, q_full, head * FA_HD, t_begin + row_base);
             tma_load_2d(smem_base + FA_HALF_BYTES, &map_q, q_full, head * FA_HD + 64, t_begin + row_base);
-            int issued = 0;
-            for (int it = 0; it < n_it; it++) {
-                const int s = it & 1;
-                if (!mbar_wait(kv_empty0 + 8 * s, ((it >> 1) & 1) ^ 1)) {
-                    atomicExch(error_flag, 21);
-                    *abort_flag = 1;
-                    break;
-                }
-                const uint32_t kst = smem_base + FA_TILE_BYTES + s * 2 * FA_TILE_BYTES, vst = kst + FA_TILE_BYTES;
-                mbar_expect_tx(kv_full0 + 8 * s, 2 * FA_TILE_BYTES);
+            // K tiles run ahead of V tiles: a K stage is free as soon as its scores exist
+            auto load_tile = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int it) {
+                mbar_expect_tx(bar, FA_TILE_BYTES);
                 for (int pg = 0; pg < 2; pg++) {
                     const int pi = (jt0 + it) * 2 + pg;
                     int page = pi < pt_width ? pt[pi] : -1;
                     if (page < 0 || page >= n_pages) page = 0;      // masked keys; never read outside the cache
                     const int row = (page * nkv + g) * HB_PAGE_TOKENS;
-                    for (int half = 0; half < 2; half++) {
-                        const uint32_t off = half * FA_HALF_BYTES + pg * (FA_HALF_BYTES / 2);
-                        tma_load_2d(kst + off, &map_k, kv_full0 + 8 * s, half * 64, row);
-                        tma_load_2d(vst + off, &map_v, kv_full0 + 8 * s, half * 64, row);
-                    }
+                    for (int half = 0; half < 2; half++)
+                        tma_load_2d(dst + half * FA_HALF_BYTES + pg * (FA_HALF_BYTES / 2), map, bar, half * 64, row);
                 }
-                issued = it + 1;
+            };
+            int k_issued = 0, v_issued = 0;
+            bool alive = true;
+            for (int step = 0; step < n_it + 1 && alive; step++) {
+                const int ik = step, iv = step - 1;                 // the K of tile `step`, then the V of the tile before
+                if (ik < n_it) {
+                    const int s = ik % FA_STAGES;
+                    if (!mbar_wait(k_empty0 + 8 * s, ((ik / FA_STAGES) & 1) ^ 1)) {
+                        atomicExch(error_flag, 21);
+                        *abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    load_tile(k_smem + s * FA_TILE_BYTES, &map_k, k_full0 + 8 * s, ik);
+                    k_issued = ik + 1;
+                }
+                if (iv >= 0) {
+                    const int s = iv % FA_STAGES;
+                    if (!mbar_wait(v_empty0 + 8 * s, ((iv / FA_STAGES) & 1) ^ 1)) {
+                        atomicExch(error_flag, 22);
+                        *abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    load_tile(v_smem + s * FA_TILE_BYTES, &map_v, v_full0 + 8 * s, iv);
+                    v_issued = iv + 1;
+                }
             }
-            for (int it = max(0, issued - 2); it < issued; it++)
-                if (!mbar_wait(kv_full0 + 8 * (it & 1), (it >> 1) & 1)) atomicExch(error_flag, 22);
+            for (int it = max(0, k_issued - FA_STAGES); it < k_issued; it++)
+                if (!mbar_wait(k_full0 + 8 * (it % FA_STAGES), (it / FA_STAGES) & 1)) atomicExch(error_flag, 23);
+            for (int it = max(0, v_issued - FA_STAGES); it < v_issued; it++)
+                if (!mbar_wait(v_full0 + 8 * (it % FA_STAGES), (it / FA_STAGES) & 1)) atomicExch(error_flag, 23);
             if (!mbar_wait(q_full, 0)) atomicExch(error_flag, 23);
         }
     } else if (warp == 1) {
@@ -214,21 +240,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             bool alive = mbar_wait(q_full, 0);
             if (!alive) { atomicExch(error_flag, 24); *abort_flag = 1; }
             auto issue_qk = [&](int it) {
-                const int s = it & 1;
-                if (!mbar_wait(kv_full0 + 8 * s, (it >> 1) & 1)) {
+                const int s = it % FA_STAGES, sb = it & 1;
+                if (!mbar_wait(k_full0 + 8 * s, (it / FA_STAGES) & 1)) {
                     atomicExch(error_flag, 25);
                     *abort_flag = 1;
                     alive = false;
                     return;
                 }
                 tc_fence_after();
-                const uint32_t kst = smem_base + FA_TILE_BYTES + s * 2 * FA_TILE_BYTES;
+                const uint32_t kst = k_smem + s * FA_TILE_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < FA_HD / 16; kk++) {
                     const uint32_t off = (kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32;
-                    umma_bf16(tmem_base + s * 128, smem_desc_sw128(smem_base + off), smem_desc_sw128(kst + off), idesc_qk, kk ? 1u : 0u);
+                    umma_bf16(tmem_base + sb * 128, smem_desc_sw128(smem_base + off), smem_desc_sw128(kst + off), idesc_qk, kk ? 1u : 0u);
                 }
-                umma_commit(s_full0 + 8 * s);
+                umma_commit(k_empty0 + 8 * s);                // the K tile is used up
+                umma_commit(s_full0 + 8 * sb);
             };
             if (alive) issue_qk(0);
             for (int it = 0; it < n_it && alive; it++) {
@@ -240,53 +267,68 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     *abort_flag = 1;
                     break;
                 }
+                const int sv = it % FA_STAGES;
+                if (!mbar_wait(v_full0 + 8 * sv, (it / FA_STAGES) & 1)) {
+                    atomicExch(error_flag, 30);
+                    *abort_flag = 1;
+                    break;
+                }
                 tc_fence_after();
-                const uint32_t vst = smem_base + FA_TILE_BYTES + s * 2 * FA_TILE_BYTES + FA_TILE_BYTES;
+                const uint32_t vst = v_smem + sv * FA_TILE_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < FA_KEYS / 16; kk++)
                     umma_bf16_ts(tm_o, tmem_base + s * 128 + kk * 8, smem_desc_mn_sw128(vst + kk * 16 * 128, FA_HALF_BYTES, 1024),
                                  idesc_pv, (it | kk) ? 1u : 0u);
-                umma_commit(kv_empty0 + 8 * s);               // the stage's keys and values are used up
+                umma_commit(v_empty0 + 8 * sv);               // the V tile is used up
                 umma_commit(pv_done);
             }
         }
     } else if (n_it > 0) {
         // ---------------------------------------------------------------- softmax and output
         const int q = warp & 3, r = q * 32 + lane;            // query row of this thread = TMEM lane
+        const int hf = (warp - 2) >> 2;                       // which 64 key columns (and output columns) of the row
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         const int qpos = first_pos + r;
         const int lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
         const bool valid = row_base + r < n_new;
-        float m_run = -INFINITY, l = 0.0f;
+        float m_run = -INFINITY, l = 0.0f;                    // l: this thread's columns only
         bool ok = true;
         for (int it = 0; it < n_it; it++) {
             const int s = it & 1;
             if (!mbar_wait(s_full0 + 8 * s, (it >> 1) & 1)) {
                 atomicExch(error_flag, 27);
                 *abort_flag = 1;
+            }
+            tc_fence_after();
+            const uint32_t tm_s = tmem_base + s * 128 + lane_base;
+            const int kbase = (jt0 + it) * FA_KEYS + hf * 64;
+            // this thread's row sees keys lo..qpos; as columns of its half tile: [c_lo, c_hi]
+            const int c_lo = lo - kbase, c_hi = qpos - kbase;
+            // the scores in registers: one round trip to tensor memory
+            float sv[64];
+            tmem_ld64(tm_s + hf * 64, sv);
+            if (c_lo > 0 || c_hi < 63) {                       // the causal diagonal or the window's edge
+#pragma unroll
+                for (int e = 0; e < 64; e++)
+                    if (e < c_lo || e > c_hi) sv[e] = -INFINITY;
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int e = 0; e < 64; e += 4) {
+                mx4[0] = fmaxf(mx4[0], sv[e]);
+                mx4[1] = fmaxf(mx4[1], sv[e + 1]);
+                mx4[2] = fmaxf(mx4[2], sv[e + 2]);
+                mx4[3] = fmaxf(mx4[3], sv[e + 3]);
+            }
+            xrow[hf * 128 + r] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // all 256 softmax threads: every score is in registers now (P may overwrite S) and the
+            // other half's maximum is visible
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            if (*abort_flag) {                                 // read after the barrier: the same for all 256 threads
                 ok = false;
                 break;
             }
-            if (*abort_flag) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t tm_s = tmem_base + s * 128 + lane_base;
-            const int kbase = (jt0 + it) * FA_KEYS;
-            // this thread's row sees keys lo..qpos; as columns of the tile: [c_lo, c_hi]
-            const int c_lo = lo - kbase, c_hi = qpos - kbase;
-            // the whole row of scores in registers: one round trip to tensor memory
-            float sv[FA_KEYS];
-#pragma unroll
-            for (int c = 0; c < 4; c++) tmem_ld32_nowait(tm_s + c * 32, sv + c * 32);
-            tmem_wait_ld();
-            if (c_lo > 0 || c_hi < FA_KEYS - 1) {           // a tile on the causal diagonal or the window's edge
-#pragma unroll
-                for (int e = 0; e < FA_KEYS; e++)
-                    if (e < c_lo || e > c_hi) sv[e] = -INFINITY;
-            }
-            float mx = -INFINITY;
-#pragma unroll
-            for (int e = 0; e < FA_KEYS; e++) mx = fmaxf(mx, sv[e]);
-            const float m_tile = mx * scale_log2e;
+            const float m_tile = fmaxf(xrow[r], xrow[128 + r]) * scale_log2e;
             if (it == 0) {
                 m_run = m_tile;
             } else {
@@ -296,8 +338,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (!mbar_wait(pv_done, (it - 1) & 1)) {
                         atomicExch(error_flag, 28);
                         *abort_flag = 1;
-                        ok = false;
-                        break;
                     }
                     tc_fence_after();
                     const float m_new = fmaxf(m_run, m_tile);
@@ -305,50 +345,53 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     m_run = m_new;
                     l *= corr;
 #pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
+                    for (int c = 0; c < 2; c++) {
                         float v[32];
-                        tmem_ld32(tm_o + lane_base + c * 32, v);
+                        tmem_ld32(tm_o + lane_base + hf * 64 + c * 32, v);
 #pragma unroll
                         for (int e = 0; e < 32; e++) v[e] *= corr;
-                        tmem_st32(tm_o + lane_base + c * 32, v);
+                        tmem_st32(tm_o + lane_base + hf * 64 + c * 32, v);
                     }
                     tmem_wait_st();
                 }
             }
             const float neg_m = m_run == -INFINITY ? 0.0f : -m_run;
-            float sum = 0.0f;
+            float sum2[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
                     const float p0 = exp2_approx(fmaf(sv[c * 32 + e], scale_log2e, neg_m));
                     const float p1 = exp2_approx(fmaf(sv[c * 32 + e + 1], scale_log2e, neg_m));
-                    sum += p0 + p1;
+                    sum2[0] += p0;
+                    sum2[1] += p1;
                     pk[e >> 1] = pack_bf16_pair(p0, p1);
                 }
-                tmem_st16u(tm_s + c * 16, pk);            // P over S: every score is in registers already
+                tmem_st16u(tm_s + hf * 32 + c * 16, pk);      // P over S
             }
-            l += sum;
+            l += sum2[0] + sum2[1];
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(p_full0 + 8 * s);
         }
-        if (ok) {
-            if (!mbar_wait(pv_done, (n_it - 1) & 1)) {
-                atomicExch(error_flag, 29);
-                *abort_flag = 1;
-                ok = false;
-            }
+        if (ok && !mbar_wait(pv_done, (n_it - 1) & 1)) {
+            atomicExch(error_flag, 29);
+            *abort_flag = 1;
         }
-        if (ok) {
+        // the two halves of a row add their sums
+        asm volatile("bar.sync 2, 256;" ::: "memory");      // nobody still reads the maxima
+        xrow[hf * 128 + r] = l;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (!*abort_flag) {
             tc_fence_after();
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            bf16* dst = out + (size_t)(t_begin + row_base + r) * out_stride + (size_t)head * FA_HD;
+            const float lt = xrow[r] + xrow[128 + r];
+            const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
+            bf16* dst = out + (size_t)(t_begin + row_base + r) * out_stride + (size_t)head * FA_HD + hf * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
                 float v[32];
-                tmem_ld32(tm_o + lane_base + c * 32, v);
+                tmem_ld32(tm_o + lane_base + hf * 64 + c * 32, v);
                 if (valid) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
@@ -396,14 +439,15 @@ extern "C" int hb_attention_prefill_tc(const void* q, long long q_stride, long l
     if (tc_make_map(&mq, q, n_tokens, (long long)n_heads * head_dim, q_stride, FA_ROWS)) return 1;
     if (tc_make_map(&mk, k_cache, cache_rows, head_dim, head_dim, HB_PAGE_TOKENS)) return 1;
     if (tc_make_map(&mv, v_cache, cache_rows, head_dim, head_dim, HB_PAGE_TOKENS)) return 1;
-    constexpr int SMEM = FA_TILE_BYTES + FA_STAGES * 2 * FA_TILE_BYTES + 10 * 8 + 16 + 1024;
+    constexpr int SMEM = FA_TILE_BYTES + FA_STAGES * 2 * FA_TILE_BYTES + 18 * 8 + 16 + 2 * 128 * 4 + 1024;
+    static_assert(SMEM <= 227 * 1024, "attention tiles do not fit shared memory");
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
-    cudaError_t e = hb_launch(attn_prefill_tc_kernel, dim3(q_blocks, n_heads), dim3(TC_THREADS), SMEM, (cudaStream_t)stream, mq, mk, mv,
+    cudaError_t e = hb_launch(attn_prefill_tc_kernel, dim3(q_blocks, n_heads), dim3(FA_THREADS), SMEM, (cudaStream_t)stream, mq, mk, mv,
                               page_table, pt_width, seq_start, seq_pos0, (bf16*)out, out_stride, n_seqs, n_heads, n_kv_heads,
                               scale * FA_LOG2E, window, n_pages, error_flag);
     if (e != cudaSuccess) return hb_fail("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
