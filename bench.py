@@ -1,6 +1,8 @@
 """Decode and prefill throughput of the Llama-3.1-8B-shaped model with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+    python bench.py --workload 3b|1b      # a line of its own: unequal prompts, then decoding
+    python bench.py --timeline --layers 3 --skip-points    # per-kernel times inside the decode graph
 
 Prints ONE JSON line.  A step is one decode step of a batch of 8 sequences whose caches hold
 about 8192 tokens each; ``value`` is decoded tokens per second from CUDA events around the
@@ -31,6 +33,16 @@ MODEL_8B = dict(
     rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
     tie_word_embeddings=False, max_position_embeddings=131072)
+# BASELINE.json configs[3] and configs[4]: generation workloads at the 3B and 1B shapes
+# (--workload 3b | 1b): (model, batch, prompt lengths uniform in [lo, hi], decode steps)
+LLAMA3_32 = dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                 original_max_position_embeddings=8192)
+MODEL_3B = dict(MODEL_8B, hidden_size=3072, num_hidden_layers=28, intermediate_size=8192, num_attention_heads=24,
+                rope_scaling=LLAMA3_32, tie_word_embeddings=True)
+MODEL_1B = dict(MODEL_8B, hidden_size=2048, num_hidden_layers=16, intermediate_size=8192, head_dim=64,
+                rope_scaling=LLAMA3_32, tie_word_embeddings=True)
+WORKLOADS = {"3b": (MODEL_3B, "llama-3.2-3b-shaped", 16, 64, 1024, 128),
+             "1b": (MODEL_1B, "llama-3.2-1b-shaped", 64, 16, 512, 256)}
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -233,6 +245,125 @@ def prefill_flops(cfg, layers, tokens):
     return layers * (per_layer + attn) + 2 * H * V
 
 
+def generation_workload(name, repeats, warmup):
+    """A batch of unequal prompts through the Python entry point (host tokens in and out):
+    all prompts in one step, then a fixed number of decode steps (no stop tokens).  One JSON
+    line of its own; the default line (8B shape) is not affected."""
+    import torch
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.api import LLM
+    cfg_dict, label, batch, lo, hi, new_tokens = WORKLOADS[name]
+    cfg = hb.LlamaConfig.from_dict(cfg_dict)
+    g = torch.Generator().manual_seed(11)
+    lengths = torch.randint(lo, hi + 1, (batch,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lengths]
+    max_tokens = sum((n + new_tokens + 63) // 64 * 64 for n in lengths)
+    llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, device=0, max_batch=batch,
+                     max_step_tokens=max(PREFILL_TOKENS, hi))
+    llm.generator._sync = torch.cuda.synchronize     # so that the phase times split at the right place
+    runs = []
+    clocks = ClockSampler()
+    for i in range(warmup + repeats):
+        if i == warmup:
+            clocks.start()
+        st = llm.generator.stats = type(llm.generator.stats)()
+        launches0 = llm.engine.ctx.ops.launches
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = llm.generate(prompts, max_new_tokens=new_tokens, temperature=0.0, stop_token_ids=[])
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert all(len(r.tokens) == new_tokens for r in out)
+        runs.append((dt, st.prefill_seconds, st.decode_seconds, st.decode_steps, llm.engine.ctx.ops.launches - launches0))
+    clock_info = clocks.stop()
+    dt, pre_s, dec_s, dec_steps, launches = sorted(runs[warmup:])[len(runs[warmup:]) // 2]
+    dec_tokens = batch * (new_tokens - 1)            # the first token of each comes from the prompt step
+    pk, pk_src = peaks()
+    mean_len = [n + new_tokens // 2 for n in lengths]
+    step_bytes = llm.engine.decode_step_bytes(mean_len)
+    ms = dec_s / max(1, dec_steps) * 1e3
+    line = {
+        "metric": f"decode tok/s, batch {batch}, prompts uniform in [{lo}, {hi}], {new_tokens} new tokens ({label}, random weights)",
+        "value": round(dec_tokens / dec_s, 1), "unit": "tokens/s", "n_gpus": 1, "steps": dec_steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights, random token ids", "impl": "ours",
+        "config": {"model": label, "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": batch,
+                   "prompt_tokens": sum(lengths), "new_tokens": new_tokens, "parallelism": "single-gpu",
+                   "timing": "host clock around the generation loop's phases, device synchronised", "peaks": pk_src},
+        "e2e": {"value": round(batch * new_tokens / dt, 1), "unit": "generated tokens/s, prompts included in the time",
+                "seconds": round(dt, 4)},
+        "gpu_launches": launches,
+        "prefill": {"value": round(sum(lengths) / pre_s, 1), "tokens": sum(lengths), "ms": round(pre_s * 1e3, 3),
+                    "frac": round(sum(prefill_flops_varlen(cfg_dict, lengths)) / pre_s / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(step_bytes / (ms * 1e-3) / 1e9, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+        "clocks": clock_info,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def prefill_flops_varlen(cfg, lengths):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    L = cfg["num_hidden_layers"]
+    return [L * (2 * n * (H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I) + 2 * n * n * hd * nh) + 2 * H * V
+            for n in lengths]
+
+
+def timeline_table(llm, batch, context, steps=8):
+    """Per-kernel times of decode steps inside the replayed graph (timeline build of the
+    kernel library): for every kernel the time from the moment it found its predecessors
+    finished to the moment its successor did, overlap between neighbours included, and how
+    long before that moment its first block was already resident."""
+    import torch
+    from hilbert_pruned_8b_b200.engine.batch import StepEntry
+    eng = llm.engine
+    ops = eng.ctx.ops
+    seqs = open_filled(llm, batch, context - steps - 8)
+
+    def one(k):
+        lg = eng.step([StepEntry(s, [(7 * k + b) % 1000], [0]) for b, s in enumerate(seqs)])
+        llm.sampler.greedy(lg)
+
+    ops.call_log = []
+    one(0)                                   # the first step runs eagerly: its calls name the kernels
+    names = []
+    for n in ops.call_log:
+        if n == "hb_attention_decode":
+            names += ["attention_decode", "attention_decode_combine"]
+        elif n not in ("hb_device_info", "hb_timeline_set"):
+            names.append(n[3:])
+    ops.call_log = None
+    for k in range(1, 5):
+        one(k)
+    torch.cuda.synchronize()
+    ops.timeline_begin(1 << 20)
+    for k in range(steps):
+        one(5 + k)
+    marks = [m for m in ops.timeline_end() if m[0] > 10 ** 9]      # kernel marks (events carry small codes)
+    per = len(marks) // steps
+    if per != len(names):
+        names = [f"kernel {i}" for i in range(per)]
+    rows, total = [], 0.0
+    for i in range(per):
+        dur = [marks[s * per + i + 1][1] - marks[s * per + i][1] for s in range(1, steps - 1)]
+        lead = [marks[s * per + i][1] - marks[s * per + i][0] for s in range(1, steps - 1)]
+        d, l = statistics.median(dur) / 1e3, statistics.median(lead) / 1e3
+        total += d
+        rows.append((i, names[i], d, l))
+    print(f"decode step, batch {batch}, context {context}, {llm.config.num_hidden_layers} layers: "
+          f"{per} kernels, {total:.1f} us (sum of medians over {steps - 2} replayed steps)")
+    print("   #  kernel                          us    resident before its predecessors finished (us)")
+    for i, n, d, l in rows:
+        print(f"{i:4d}  {n:28s} {d:8.2f} {l:10.2f}")
+    for s in seqs:
+        eng.close_sequence(s)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -242,7 +373,14 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", choices=("8b", "3b", "1b"), default="8b",
+                    help="8b: the default line; 3b, 1b: the generation workloads at those shapes (--steps = repeats)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the per-kernel times of a decode step inside the replayed graph (builds the "
+                         "timeline variant of the kernel library) instead of the JSON line")
     a = ap.parse_args()
+    if a.timeline:
+        os.environ["HILBERT_B200_TIMELINE"] = "1"      # before the kernel library is looked for
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the installed reference package (semif-score) only scores answer options of text rows "
@@ -254,6 +392,8 @@ def main() -> int:
         print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported by this single-GPU library")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.workload != "8b":
+        return generation_workload(a.workload, repeats=min(a.steps, 3), warmup=1)
 
     import torch
     import hilbert_pruned_8b_b200 as hb
@@ -274,6 +414,8 @@ def main() -> int:
     torch.cuda.synchronize()
     build_s = time.time() - t_build
 
+    if a.timeline:
+        return timeline_table(llm, a.batch, CONTEXT)
     prefill_ms = time_prefill(llm, PREFILL_TOKENS)
     pf = prefill_flops(cfg_dict, layers, PREFILL_TOKENS)
     ms, launches, step_bytes, clocks = time_decode(llm, a.batch, a.steps, a.warmup, CONTEXT, ClockSampler())

@@ -24,6 +24,8 @@ int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride, const floa
                       int n_heads, int n_kv_heads, int head_dim, void* k_cache, void* v_cache, int cache_dtype,
                       const int* page_table, int pt_width, const int* tok_seq, const int* positions,
                       int n_tokens, int append, int n_pages, void* stream);
+// Time marks of a timeline build (see common.cuh); other builds refuse.
+int hb_timeline_set(void* marks, void* count, int capacity, int events);
 int hb_gemm_general(const void* a, int a_dtype, long long lda, const void* w, int w_dtype, long long ldw,
                     void* out, int out_dtype, long long ldc, int M, int N, int K, int accumulate, void* stream);
 int hb_gemm_tc_token_tile(int M);

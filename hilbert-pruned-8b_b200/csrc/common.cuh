@@ -28,7 +28,101 @@ typedef __nv_bfloat16 bf16;
 // that kernel may have written (for most kernels: first thing) and pdl_trigger() to let the
 // kernel after it be scheduled early in turn.  What runs before pdl_wait() may only read
 // memory that no kernel of a step writes (weights) and set up on-chip state.
+#ifndef HB_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define TL_INIT()
+#define TL_EVENT(code)
+#define TL_FLUSH()
+#else
+// Timeline build (-DHB_TIMELINE): thread 0 of block 0 of every kernel notes the global timer
+// when it reaches pdl_wait() (the block is resident and set up) and when the wait returns
+// (everything before the kernel in the stream has finished).  The difference between two
+// kernels' second marks is the time the first one took inside a replayed graph, overlap
+// included.  Each translation unit has its own pointer to the one mark buffer.
+static __device__ unsigned long long* g_tl_marks = nullptr;   // [capacity][2]
+static __device__ unsigned int* g_tl_count = nullptr;
+static __device__ unsigned int g_tl_capacity = 0;
+static __device__ int g_tl_events = 0;                        // in-kernel events on (they cost a few microseconds per kernel)
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void pdl_wait() {
+    const bool mark = (threadIdx.x | threadIdx.y | blockIdx.x | blockIdx.y | blockIdx.z) == 0 && g_tl_marks != nullptr;
+    unsigned long long t0 = 0ull;
+    unsigned int i = 0xffffffffu;
+    if (mark) {
+        t0 = tl_now();
+        i = atomicAdd(g_tl_count, 1u);          // the slot is taken while waiting anyway
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (mark && i < g_tl_capacity) {
+        g_tl_marks[2 * (size_t)i] = t0;
+        g_tl_marks[2 * (size_t)i + 1] = tl_now();
+    }
+}
+// Tagged events inside a kernel: kept in shared memory (a global atomic per event would cost
+// the thread a round trip) and copied out by TL_FLUSH at the block's end.  An event is the
+// pair (code * 1000 + block, time).
+#define TL_EVENTS_PER_BLOCK 128
+static __shared__ unsigned long long tl_sh_events[2 * TL_EVENTS_PER_BLOCK];
+static __shared__ unsigned int tl_sh_count;
+static __shared__ unsigned long long tl_sh_ref[2];      // global timer and SM clock at TL_INIT
+static __shared__ int tl_sh_on;                         // the block's copy of g_tl_events
+__device__ __forceinline__ void tl_init() {
+    tl_sh_count = 0;
+    tl_sh_on = g_tl_events;
+    if (!tl_sh_on) return;
+    tl_sh_ref[0] = tl_now();
+    tl_sh_ref[1] = (unsigned long long)clock64();
+}
+// the SM's cycle counter is cheap to read; the global timer costs a fraction of a microsecond
+__device__ __forceinline__ void tl_event(int code) {
+    if (!tl_sh_on) return;
+    const unsigned long long c = (unsigned long long)clock64();
+    const unsigned int i = atomicAdd(&tl_sh_count, 1u);
+    if (i < TL_EVENTS_PER_BLOCK) {
+        tl_sh_events[2 * i] = (unsigned long long)(code * 1000 + (int)blockIdx.x);
+        tl_sh_events[2 * i + 1] = c;
+    }
+}
+__device__ __forceinline__ void tl_flush() {           // the thread that ran tl_init, after a block-wide barrier
+    if (!tl_sh_on || g_tl_marks == nullptr) return;
+    const unsigned long long g1 = tl_now(), c1 = (unsigned long long)clock64();
+    const double ns_per_cycle = (double)(g1 - tl_sh_ref[0]) / (double)(c1 - tl_sh_ref[1]);
+    const unsigned int n = min(tl_sh_count, (unsigned int)TL_EVENTS_PER_BLOCK);
+    const unsigned int base = atomicAdd(g_tl_count, n);
+    for (unsigned int i = 0; i < n && base + i < g_tl_capacity; i++) {
+        g_tl_marks[2 * (size_t)(base + i)] = tl_sh_events[2 * i];
+        g_tl_marks[2 * (size_t)(base + i) + 1] =
+            tl_sh_ref[0] + (unsigned long long)((double)(tl_sh_events[2 * i + 1] - tl_sh_ref[1]) * ns_per_cycle);
+    }
+}
+#ifdef HB_TIMELINE_EVENTS          // a build of its own: the events lengthen the kernels that have them
+#define TL_INIT() tl_init()
+#define TL_EVENT(code) tl_event(code)
+#define TL_FLUSH() tl_flush()
+#else
+#define TL_INIT()
+#define TL_EVENT(code)
+#define TL_FLUSH()
+#endif
+typedef void (*HbTimelineSetter)(unsigned long long*, unsigned int*, unsigned int, int);
+void hb_timeline_register(HbTimelineSetter fn);
+static void tl_set_this_unit(unsigned long long* marks, unsigned int* count, unsigned int capacity, int events) {
+    cudaMemcpyToSymbol(g_tl_events, &events, sizeof events);
+    cudaMemcpyToSymbol(g_tl_marks, &marks, sizeof marks);
+    cudaMemcpyToSymbol(g_tl_count, &count, sizeof count);
+    cudaMemcpyToSymbol(g_tl_capacity, &capacity, sizeof capacity);
+}
+namespace {
+struct TlRegistrar {
+    TlRegistrar() { hb_timeline_register(tl_set_this_unit); }
+};
+static TlRegistrar g_tl_registrar;
+}  // namespace
+#endif
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool hb_pdl_enabled();

@@ -55,16 +55,17 @@ struct TcSchedule {
     int tiles, kbt, stream_k, split, per;
     int cur, end, step;       // stream-K: unit cursor and range end; tiles: tile cursor and stride
     long long base;
-    int rem, grid;
+    int rem, grid, cta;
     __device__ __forceinline__ void init(const TcParams& p) {
         tiles = p.tiles_m * p.tiles_n;
         kbt = p.kb_total;
         stream_k = p.stream_k;
         split = p.split;
         grid = gridDim.x;
+        cta = blockIdx.x;
         if (stream_k == 2) {
             per = (kbt + split - 1) / split;
-            const int t = blockIdx.x / split, part = blockIdx.x - t * split;
+            const int t = cta / split, part = cta - t * split;
             cur = t * kbt + part * per;                       // as a unit range of the flat space
             end = t * kbt + min(kbt, (part + 1) * per);
             if (t >= tiles) end = cur;
@@ -72,11 +73,11 @@ struct TcSchedule {
             const long long units = (long long)tiles * kbt;
             base = units / grid;
             rem = (int)(units % grid);
-            const long long b = blockIdx.x;
+            const long long b = cta;
             cur = (int)(b * base + (b < rem ? b : rem));
             end = cur + (int)base + (b < rem ? 1 : 0);
         } else {
-            cur = blockIdx.x;
+            cur = cta;
             step = grid;
             end = tiles;
         }
@@ -105,17 +106,21 @@ struct TcSchedule {
     __device__ __forceinline__ void contributors(int tile, int& n, int& slot) const {
         if (stream_k == 2) {
             n = (kbt + per - 1) / per;
-            slot = blockIdx.x - tile * split;
+            slot = cta - tile * split;
         } else {
             const long long u0 = (long long)tile * kbt;
             const int c_lo = cta_of(u0);
             n = cta_of(u0 + kbt - 1) - c_lo + 1;
-            slot = blockIdx.x - c_lo;
+            slot = cta - c_lo;
         }
     }
 };
 
 // ------------------------------------------------------------------------------- kernel
+// TL_EVENT(code) marks exist in timeline builds only (common.cuh): 1 predecessors finished
+// (producer), 2 first stage full (MMA thread), 3 last MMA of a work item committed, 4 accumulator
+// full (epilogue), 5 partial tile written and fenced, 6 tile counter known, 7 tile emitted,
+// 8 block end.
 template <int BN, int MODE, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
@@ -134,6 +139,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
     const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
 
+    TcSchedule sched;
+    sched.init(p);
+    int tile, kb0, kb1;
+    auto load_w = [&](int s, int t, int kb) {
+        const int n0 = (t / p.tiles_m) * L::FEAT, k = kb * TC_BK;
+        const uint32_t stage = smem_base + s * L::STAGE_BYTES;
+        if (SWIGLU) {
+            tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
+            tma_load_2d(stage + L::W_BYTES / 2, &map_w, full0 + 8 * s, k, p.up_row0 + n0);
+        } else {
+            tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
+        }
+    };
+    auto load_a = [&](int s, int t, int kb) {
+        tma_load_2d(smem_base + s * L::STAGE_BYTES + L::W_BYTES, &map_a, full0 + 8 * s, kb * TC_BK, (t % p.tiles_m) * BN);
+    };
+
+    int early = 0;              // K blocks whose weight tiles thread 0 requests right away
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
@@ -145,8 +168,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         *abort_flag = 0;
         *last_flag = 0;
+        TL_INIT();
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // The weights are written by no kernel of a step: the first stages' weight tiles are
+        // requested at once, before the block has its tensor memory and before the kernel in
+        // front, whose output is only the activation operand, has finished.
+        TcSchedule peek = sched;
+        if (peek.next(tile, kb0, kb1)) {
+            early = min(kb1 - kb0, STAGES);
+            for (int j = 0; j < early; j++) {
+                mbar_expect_tx(full0 + 8 * j, L::STAGE_BYTES);
+                load_w(j, tile, kb0 + j);
+            }
+        }
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), L::TMEM_COLS);
     tc_fence_before();
@@ -155,43 +190,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     pdl_trigger();
 
-    TcSchedule sched;
-    sched.init(p);
-    int tile, kb0, kb1;
-
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            auto load_w = [&](int s, int t, int kb) {
-                const int n0 = (t / p.tiles_m) * L::FEAT, k = kb * TC_BK;
-                const uint32_t stage = smem_base + s * L::STAGE_BYTES;
-                if (SWIGLU) {
-                    tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
-                    tma_load_2d(stage + L::W_BYTES / 2, &map_w, full0 + 8 * s, k, p.up_row0 + n0);
-                } else {
-                    tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
-                }
-            };
-            auto load_a = [&](int s, int t, int kb) {
-                tma_load_2d(smem_base + s * L::STAGE_BYTES + L::W_BYTES, &map_a, full0 + 8 * s, kb * TC_BK,
-                            (t % p.tiles_m) * BN);
-            };
-            // The weights are written by no kernel of a step: the first stages' weight tiles are
-            // requested before waiting for the kernel in front, whose output is only the
-            // activation operand.
-            int early = 0;
-            {
-                TcSchedule peek = sched;
-                if (peek.next(tile, kb0, kb1)) {
-                    early = min(kb1 - kb0, STAGES);
-                    for (int j = 0; j < early; j++) {
-                        mbar_expect_tx(full0 + 8 * j, L::STAGE_BYTES);
-                        load_w(j, tile, kb0 + j);
-                    }
-                }
-                pdl_wait();
-                for (int j = 0; j < early; j++) load_a(j, tile, kb0 + j);
-            }
+            pdl_wait();
+            TL_EVENT(1);
+            for (int j = 0; j < early; j++) load_a(j, tile, kb0 + j);
             int g = 0;                    // K blocks issued so far (all work items)
             bool alive = true;
             while (alive && sched.next(tile, kb0, kb1)) {
@@ -244,6 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         break;
                     }
                     tc_fence_after();
+                    if (item == 0 && kb == kb0) TL_EVENT(2);
                     const uint32_t w_lo = desc_lo0 + s * STAGE_STEP;
 #pragma unroll
                     for (int kk = 0; kk < TC_BK / 16; kk++) {
@@ -255,6 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 umma_commit(accf0 + 8 * buf);          // arrives when the item's MMAs have finished
+                TL_EVENT(3);
                 item++;
             }
         }
@@ -274,6 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             if (*abort_flag) break;
             tc_fence_after();
+            if (et == 0) TL_EVENT(4);
             const uint32_t lane_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
             const int m0 = (tile % p.tiles_m) * BN, n0 = (tile / p.tiles_m) * L::FEAT;
             const bool whole = kb0 == 0 && kb1 == p.kb_total;
@@ -295,6 +302,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 mbar_arrive(acce0 + 8 * buf);                  // the accumulator buffer is free again
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) TL_EVENT(5);
                 if (et == 0) {
                     const int prev = atomicAdd(p.counters + tile, 1);
                     const int last = (prev == contributors - 1) ? 1 : 0;
@@ -304,8 +312,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 finish = *last_flag != 0;
                 __threadfence();
+                if (et == 0) TL_EVENT(6);
             }
-            if (finish) {
+            if (finish && !whole && BN <= 64) {
+                // Sum of the partial tiles in K order with 16-byte loads: every load of one
+                // contributor is in flight at once, so the sum costs one L2 round trip per
+                // contributor (two are overlapped) instead of one per 16 tokens of each.
+                const float4* src4 = reinterpret_cast<const float4*>(p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM)) + et;
+                constexpr int NV = BN <= 64 ? BN / 4 : 1;
+                float4 acc[NV];
+#pragma unroll
+                for (int i = 0; i < NV; i++) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                const int tw = et >> 5;
+#pragma unroll 2
+                for (int z = 0; z < contributors; z++) {
+                    const float4* pz = src4 + (size_t)z * (BN * TC_BM / 4);
+                    float4 t[NV];
+#pragma unroll
+                    for (int i = 0; i < NV; i++)
+                        t[i] = (m0 + i * 4 + tw < p.M) ? __ldcg(pz + i * TC_BM) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int i = 0; i < NV; i++) {
+                        acc[i].x += t[i].x;
+                        acc[i].y += t[i].y;
+                        acc[i].z += t[i].z;
+                        acc[i].w += t[i].w;
+                    }
+                }
+                tc_emit_flat<MODE, BN <= 64 ? BN : 4>(p, m0, n0, acc, et);
+            } else if (finish) {
                 const float* src = p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM);
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
@@ -329,11 +364,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tc_fence_before();
                 mbar_arrive(acce0 + 8 * buf);
             }
+            if (et == 0 && finish) TL_EVENT(7);
             item++;
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) {
+        TL_EVENT(8);
+        TL_FLUSH();
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, L::TMEM_COLS);

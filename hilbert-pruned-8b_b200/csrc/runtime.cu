@@ -37,6 +37,30 @@ bool hb_pdl_enabled() {
 
 extern "C" const char* hb_last_error(void) { return g_error; }
 
+// Timeline marks (see common.cuh).  `marks` holds capacity pairs of 64-bit times, `count` one
+// 32-bit counter; both are device memory of the caller.  A library built without
+// -DHB_TIMELINE refuses.  `events` non-zero also records the events inside kernels that have
+// some.  Passing null pointers switches the marks off again.
+#ifdef HB_TIMELINE
+static HbTimelineSetter g_tl_setters[64];
+static int g_tl_setter_count = 0;
+void hb_timeline_register(HbTimelineSetter fn) {
+    if (g_tl_setter_count < 64) g_tl_setters[g_tl_setter_count++] = fn;
+}
+#endif
+extern "C" int hb_timeline_set(void* marks, void* count, int capacity, int events) {
+#ifdef HB_TIMELINE
+    for (int i = 0; i < g_tl_setter_count; i++)
+        g_tl_setters[i]((unsigned long long*)marks, (unsigned int*)count, (unsigned int)capacity, events);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return hb_fail("timeline: %s", cudaGetErrorString(e));
+    return 0;
+#else
+    (void)marks, (void)count, (void)capacity, (void)events;
+    return hb_fail("timeline: this library was built without -DHB_TIMELINE (set HILBERT_B200_TIMELINE=1 before the first use)");
+#endif
+}
+
 extern "C" int hb_device_info(int device, int* sm_major, int* sm_minor, int* sm_count) {
     cudaDeviceProp p;
     cudaError_t e = cudaGetDeviceProperties(&p, device);

@@ -230,6 +230,62 @@ __device__ __forceinline__ void tc_emit_chunk(const TcParams& p, int m0, int n0,
     }
 }
 
+// Epilogue of a summed partial tile held in the scratch layout [token][row]: thread et
+// (0..127) holds, for i = 0..BN/4-1, the four rows (et & 31) * 4 .. + 3 of token
+// i * 4 + (et >> 5).  The same results as tc_emit_chunk, with 16-byte accesses.
+template <int MODE, int BN>
+__device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, const float4 (&acc)[BN / 4], int et) {
+    const int lane = et & 31, tw = et >> 5;
+#pragma unroll
+    for (int i = 0; i < BN / 4; i++) {
+        const int m = m0 + i * 4 + tw;                      // uniform in a warp
+        if (m >= p.M) continue;
+        const float v[4] = {acc[i].x, acc[i].y, acc[i].z, acc[i].w};
+        if (MODE == TC_SWIGLU_BF16) {
+            // lanes 0..15 hold gate rows 4 * lane .. + 3, lanes 16..31 the up rows of the same features
+            float u[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) u[e] = __shfl_down_sync(0xffffffffu, v[e], 16);
+            const int n = n0 + lane * 4;
+            if (lane < 16 && n < p.N) {
+                bf16 y[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) y[e] = __float2bfloat16_rn(silu_f32(v[e]) * u[e]);
+                bf16* o = (bf16*)p.out + (size_t)m * p.ldc + n;
+                if (n + 4 <= p.N) {
+                    *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(y);
+                } else {
+                    for (int e = 0; e < p.N - n; e++) o[e] = y[e];
+                }
+            }
+        } else {
+            const int n = n0 + lane * 4;
+            if (n >= p.N) continue;
+            const size_t off = (size_t)m * p.ldc + n;
+            if (MODE == TC_STORE_BF16) {
+                bf16* o = (bf16*)p.out + off;
+                bf16 y[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) y[e] = __float2bfloat16_rn(v[e]);
+                if (n + 4 <= p.N && (((uintptr_t)o) & 7) == 0) {
+                    *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(y);
+                } else {
+                    for (int e = 0; e < 4 && n + e < p.N; e++) o[e] = y[e];
+                }
+            } else {
+                float* o = (float*)p.out + off;
+                if (n + 4 <= p.N && (((uintptr_t)o) & 15) == 0) {
+                    float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (MODE == TC_ADD_F32) r = __ldcg(reinterpret_cast<const float4*>(o));
+                    *reinterpret_cast<float4*>(o) = make_float4(r.x + v[0], r.y + v[1], r.z + v[2], r.w + v[3]);
+                } else {
+                    for (int e = 0; e < 4 && n + e < p.N; e++) o[e] = (MODE == TC_ADD_F32 ? o[e] : 0.0f) + v[e];
+                }
+            }
+        }
+    }
+}
+
 // Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements): boxes of
 // box_rows x 64 elements, 128-byte swizzle, zeros outside.
 int tc_make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows);

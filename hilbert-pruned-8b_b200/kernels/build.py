@@ -25,6 +25,16 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 
 
+# HILBERT_B200_TIMELINE=1 builds a second library (own folder) whose kernels note the time at
+# which each of them started and found its predecessors finished (kernels/ops.py:
+# Ops.timeline_begin); =2 a third one that also records events inside the kernels that have
+# some, which lengthens those kernels by a few microseconds.
+TIMELINE = os.environ.get("HILBERT_B200_TIMELINE", "0")
+TIMELINE = int(TIMELINE) if TIMELINE.isdigit() else 0
+if TIMELINE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DHB_TIMELINE"] + (["-DHB_TIMELINE_EVENTS"] if TIMELINE > 1 else [])
+
+
 class BuildError(RuntimeError):
     pass
 
@@ -74,8 +84,9 @@ def build_dirs() -> List[str]:
     dirs = []
     if os.environ.get("HILBERT_B200_BUILD_DIR"):
         dirs.append(os.environ["HILBERT_B200_BUILD_DIR"])
-    dirs.append(os.path.join(CSRC, "_build"))
-    dirs.append(os.path.join(tempfile.gettempdir(), f"hilbert_b200_build_{os.getuid()}"))
+    tag = "_timeline" + (str(TIMELINE) if TIMELINE > 1 else "") if TIMELINE else ""
+    dirs.append(os.path.join(CSRC, "_build" + tag))
+    dirs.append(os.path.join(tempfile.gettempdir(), f"hilbert_b200_build{tag}_{os.getuid()}"))
     return dirs
 
 

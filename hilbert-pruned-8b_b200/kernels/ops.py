@@ -22,6 +22,7 @@ _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_floa
 
 _SIGNATURES = {
     "hb_device_info": [_c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
+    "hb_timeline_set": [_c_ptr, _c_ptr, _c_int, _c_int],
     "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
     "hb_rmsnorm": [_c_ptr, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_silu_mul": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
@@ -107,6 +108,7 @@ class Ops:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device is available; the library has no CPU path")
         self.lib = load_library()
+        self.call_log = None  # a list: the name of every library call is appended (diagnostics)
         major, minor, sms = _c_int(), _c_int(), _c_int()
         idx = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._call("hb_device_info", idx, ctypes.byref(major), ctypes.byref(minor), ctypes.byref(sms))
@@ -139,6 +141,32 @@ class Ops:
         rc = getattr(self.lib, name)(*args)
         if rc != 0:
             raise KernelError(self.lib.hb_last_error().decode("utf-8", "replace"))
+        if self.call_log is not None:
+            self.call_log.append(name)
+
+    # ------------------------------------------------------------------ timeline
+    def timeline_begin(self, capacity: int = 1 << 16, events: bool = False) -> None:
+        """Switches the kernels' time marks on (library built with HILBERT_B200_TIMELINE=1 only):
+        from now on every kernel notes when its first block reached its dependency wait and
+        when that wait returned.  ``events`` also records the events inside the kernels that have
+        some (the few-token matrix product); they cost those kernels a few microseconds."""
+        self._tl_marks = torch.zeros(capacity, 2, dtype=torch.int64, device=self.device)
+        self._tl_count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        self._call("hb_timeline_set", self._tl_marks.data_ptr(), self._tl_count.data_ptr(), capacity,
+                   1 if events else 0)
+
+    def timeline_end(self):
+        """Switches the marks off; returns the marks ordered by their second field.  A kernel's
+        mark is (resident_ns, predecessors_done_ns) of its first block; an event inside a kernel
+        (the matrix product has some) is (code * 1000 + block, time_ns) with a first field
+        below 10**9."""
+        torch.cuda.synchronize(self.device)
+        self._call("hb_timeline_set", None, None, 0, 0)
+        n = min(int(self._tl_count.item()), self._tl_marks.shape[0])
+        marks = self._tl_marks[:n].tolist()
+        self._tl_marks = self._tl_count = None
+        return sorted(((a, b) for a, b in marks), key=lambda m: m[1])
 
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream
