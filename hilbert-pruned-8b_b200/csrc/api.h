@@ -33,11 +33,11 @@ long long hb_gemm_tc_scratch_floats(int M, int N, int K, int mode, int schedule)
 long long hb_gemm_tc_tiles(int M, int N, int mode);
 int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,
                int M, int N, int K, int mode, int up_row0, int schedule, float* partials, long long partials_capacity,
-               int* tile_counters, long long counters_capacity, int* error_flag, void* stream);
+               int* tile_counters, long long counters_capacity, int* error_flag, int packed, void* stream);
 int hb_gemm_tc2_wanted(int M, int N, int K);
 int hb_gemm_tc2_resident_pairs(int mode);
 int hb_gemm_tc2(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,
-                int M, int N, int K, int mode, int up_row0, int* error_flag, void* stream);
+                int M, int N, int K, int mode, int up_row0, int* error_flag, int packed, void* stream);
 int hb_attention_general(const void* q, int q_dtype, long long q_stride, const void* k_cache, const void* v_cache,
                          int cache_dtype, const int* page_table, int pt_width, const int* tok_seq,
                          const int* positions, void* out, int out_dtype, long long out_stride, int n_tokens,

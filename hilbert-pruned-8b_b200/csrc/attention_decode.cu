@@ -16,6 +16,7 @@
 #define AD_THREADS 128
 #define AD_STAGES 3
 #define AD_LOG2E 1.4426950408889634f
+#define AD_MAX_SPLITS 16         // the one-launch kernel keeps (maximum, sum) of every split of a group in shared memory
 
 // The work of one CTA on its range of pages [p_begin, p_end): scores, online softmax and
 // weighted values of the group's query heads (fragments `qf`, rows >= group size zero), each of
@@ -262,6 +263,9 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
     constexpr int KSTEPS = HD / 16;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
+    __shared__ __align__(16) bf16 q_rot[16 * HD];          // the group's rotated queries, rows >= G zero
+    __shared__ float w_split[16 * AD_MAX_SPLITS];          // maxima, then combination weights [row][split]
+    __shared__ float l_split[16 * AD_MAX_SPLITS];          // sums [row][split]
     const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z, S = gridDim.x;
     const int tid = threadIdx.x, lane = tid & 31;
     const int G = nh / nkv;
@@ -298,17 +302,21 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
         uint32_t qf[KSTEPS][4];
         decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&]() {
             if (owner && !early_append) append_new();
-            // query fragments, rotated: row r of the tile is head g*G + r (rows >= G are zero)
+            // the group's queries, rotated once by the whole block; row r of the tile is head
+            // g*G + r (rows >= G are zero), fragments come from shared memory
+            for (int idx = tid; idx < 16 * HD; idx += AD_THREADS) {
+                const int r = idx / HD, d = idx - r * HD;
+                q_rot[idx] = r < G ? __float2bfloat16_rn(rotated(row + (size_t)(g * G + r) * HD, d, rot, cs_row))
+                                   : __float2bfloat16_rn(0.0f);
+            }
+            __syncthreads();
             const int r0 = lane >> 2, c = (lane & 3) * 2;
-            const bf16* q0 = row + (size_t)(g * G + r0) * HD;
-            const bf16* q1 = q0 + (size_t)8 * HD;
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ks++) {
-                const int d = ks * 16 + c;
-                qf[ks][0] = r0 < G ? pack_bf16(rotated(q0, d, rot, cs_row), rotated(q0, d + 1, rot, cs_row)) : 0u;
-                qf[ks][1] = r0 + 8 < G ? pack_bf16(rotated(q1, d, rot, cs_row), rotated(q1, d + 1, rot, cs_row)) : 0u;
-                qf[ks][2] = r0 < G ? pack_bf16(rotated(q0, d + 8, rot, cs_row), rotated(q0, d + 9, rot, cs_row)) : 0u;
-                qf[ks][3] = r0 + 8 < G ? pack_bf16(rotated(q1, d + 8, rot, cs_row), rotated(q1, d + 9, rot, cs_row)) : 0u;
+                qf[ks][0] = *reinterpret_cast<const uint32_t*>(q_rot + r0 * HD + ks * 16 + c);
+                qf[ks][1] = *reinterpret_cast<const uint32_t*>(q_rot + (r0 + 8) * HD + ks * 16 + c);
+                qf[ks][2] = *reinterpret_cast<const uint32_t*>(q_rot + r0 * HD + ks * 16 + c + 8);
+                qf[ks][3] = *reinterpret_cast<const uint32_t*>(q_rot + (r0 + 8) * HD + ks * 16 + c + 8);
             }
         });
         const float* so = reinterpret_cast<const float*>(smem);
@@ -352,21 +360,39 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // weights of the splits, one (row, split) pair per thread: all maxima and sums are
+    // requested at once, then all partial outputs, so the tail costs two round trips
+    for (int i = tid; i < G * S; i += AD_THREADS) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + ((size_t)b * nh + g * G) * S + i);
+        w_split[i] = ml.x;
+        l_split[i] = ml.y;
+    }
+    __syncthreads();
+    if (tid < G) {
+        float M = -INFINITY;
+        for (int zz = 0; zz < S; zz++) M = fmaxf(M, w_split[tid * S + zz]);
+        float L = 0.0f;
+        for (int zz = 0; zz < S; zz++) {
+            const float mz = w_split[tid * S + zz];
+            const float e = mz != -INFINITY ? exp2f(mz - M) : 0.0f;
+            L += l_split[tid * S + zz] * e;
+            w_split[tid * S + zz] = e;
+        }
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+        for (int zz = 0; zz < S; zz++) w_split[tid * S + zz] *= inv;
+    }
+    __syncthreads();
     for (int idx = tid; idx < G * HD; idx += AD_THREADS) {
         const int r = idx / HD, d = idx - r * HD, head = g * G + r;
-        const size_t base = ((size_t)b * nh + head) * S;
-        float M = -INFINITY;
-        for (int zz = 0; zz < S; zz++) M = fmaxf(M, __ldcg(part_ml + (base + zz) * 2));
-        float L = 0.0f, acc = 0.0f;
+        const float* po = part_o + ((size_t)b * nh + head) * S * HD + d;
+        float acc = 0.0f;
+#pragma unroll 4
         for (int zz = 0; zz < S; zz++) {
-            const float mz = __ldcg(part_ml + (base + zz) * 2);
-            if (mz != -INFINITY) {
-                const float e = exp2f(mz - M);
-                L += __ldcg(part_ml + (base + zz) * 2 + 1) * e;
-                acc += __ldcg(part_o + (base + zz) * HD + d) * e;
-            }
+            const float w = w_split[r * S + zz];
+            const float v = __ldcg(po + (size_t)zz * HD);
+            if (w != 0.0f) acc += v * w;
         }
-        out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+        out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -496,6 +522,7 @@ extern "C" int hb_attention_decode_fused(const void* qkv, long long stride, cons
                "attention_decode_fused: head size %d with %d heads over %d kv heads is not built (64 or 128, groups up to 16)",
                head_dim, n_heads, n_kv_heads);
     HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && scratch && counters, "attention_decode_fused: bad sizes");
+    HB_REQUIRE(splits <= AD_MAX_SPLITS, "attention_decode_fused: at most %d splits, got %d", AD_MAX_SPLITS, splits);
     HB_REQUIRE(batch <= 65535 && n_kv_heads <= 65535, "attention_decode_fused: batch or kv heads too large for one launch");
     HB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0 && (rot == 0 || table), "attention_decode_fused: bad rotary size %d", rot);
     HB_REQUIRE(stride % 2 == 0 && ((uintptr_t)qkv & 3) == 0, "attention_decode_fused: projections must be 4-byte aligned");

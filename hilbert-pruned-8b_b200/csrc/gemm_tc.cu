@@ -143,13 +143,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     sched.init(p);
     int tile, kb0, kb1;
     auto load_w = [&](int s, int t, int kb) {
-        const int n0 = (t / p.tiles_m) * L::FEAT, k = kb * TC_BK;
+        const int n0 = (t / p.tiles_m) * L::FEAT;
         const uint32_t stage = smem_base + s * L::STAGE_BYTES;
+        int x, y;
+        tc_w_coords(p, n0, kb, x, y);
+        tma_load_2d(stage, &map_w, full0 + 8 * s, x, y);
         if (SWIGLU) {
-            tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
-            tma_load_2d(stage + L::W_BYTES / 2, &map_w, full0 + 8 * s, k, p.up_row0 + n0);
-        } else {
-            tma_load_2d(stage, &map_w, full0 + 8 * s, k, n0);
+            tc_w_coords(p, p.up_row0 + n0, kb, x, y);
+            tma_load_2d(stage + L::W_BYTES / 2, &map_w, full0 + 8 * s, x, y);
         }
     };
     auto load_a = [&](int s, int t, int kb) {
@@ -158,6 +159,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     int early = 0;              // K blocks whose weight tiles thread 0 requests right away
     if (threadIdx.x == 0) {
+        tma_prefetch_map(&map_w);
+        tma_prefetch_map(&map_a);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
@@ -286,6 +289,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const bool whole = kb0 == 0 && kb1 == p.kb_total;
             bool finish = whole;
             int contributors = 1;
+            // TC_ADD_F32 with a split tile: the output's old values are requested now, by every
+            // contributor, so that the one that turns out to be last need not wait for them
+            // (nobody writes the tile before all contributors have counted themselves in)
+            constexpr int NV = BN <= 64 ? BN / 4 : 1;
+            constexpr bool RES_AHEAD = MODE == TC_ADD_F32 && BN <= 32;
+            float4 res[NV];
+            const bool have_res = RES_AHEAD && !whole && (p.ldc & 3) == 0 && (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
+            if (RES_AHEAD && have_res) {
+                const int n = n0 + (et & 31) * 4;
+#pragma unroll
+                for (int i = 0; i < NV; i++) {
+                    const int m = m0 + i * 4 + (et >> 5);
+                    res[i] = (m < p.M && n < p.N) ? __ldcg(reinterpret_cast<const float4*>((const float*)p.out + (size_t)m * p.ldc + n))
+                                                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+            }
             if (!whole) {
                 // partial tile to scratch: [tile][slot][token][row], float32
                 int slot;
@@ -319,7 +338,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 // contributor is in flight at once, so the sum costs one L2 round trip per
                 // contributor (two are overlapped) instead of one per 16 tokens of each.
                 const float4* src4 = reinterpret_cast<const float4*>(p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM)) + et;
-                constexpr int NV = BN <= 64 ? BN / 4 : 1;
                 float4 acc[NV];
 #pragma unroll
                 for (int i = 0; i < NV; i++) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -339,7 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         acc[i].w += t[i].w;
                     }
                 }
-                tc_emit_flat<MODE, BN <= 64 ? BN : 4>(p, m0, n0, acc, et);
+                tc_emit_flat<MODE, BN <= 64 ? BN : 4>(p, m0, n0, acc, et, res, have_res);
             } else if (finish) {
                 const float* src = p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM);
 #pragma unroll 1
@@ -413,6 +431,14 @@ int tc_make_map(CUtensorMap* map, const void* base, long long rows, long long co
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return hb_fail("gemm_tc: tensor map encode failed with code %d (rows %lld cols %lld ld %lld)", (int)r, rows, cols, ld);
     return 0;
+}
+
+// The map of a weight matrix: row-major [rows, K] with row stride ld, or packed tiles, which
+// read as a matrix of 64-column rows (ceil(rows / 128) * ceil(K / 64) * 128 of them).
+int tc_make_weight_map(CUtensorMap* map, const void* w, long long rows, long long K, long long ld, int box_rows, int packed) {
+    if (!packed) return tc_make_map(map, w, rows, K, ld, box_rows);
+    const long long bands = (rows + TC_BM - 1) / TC_BM, kbs = (K + TC_BK - 1) / TC_BK;
+    return tc_make_map(map, w, bands * kbs * TC_BM, TC_BK, TC_BK, box_rows);
 }
 
 static int sm_count() {
@@ -516,17 +542,20 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& ma, con
 // mode: 0 store bf16, 1 store f32, 2 add into f32, 3 silu(gate) * up -> bf16 (W holds the gate
 // rows [0, N) and the up rows [up_row0, up_row0 + N)).  `partials` and `tile_counters` are the
 // scratch described above (capacities in floats and ints); `error_flag` is a device int the
-// kernel sets when a wait ran out.
+// kernel sets when a wait ran out.  `packed`: W is stored as contiguous 128 x 64 tiles (see
+// tc_w_coords; w_rows is then the number of rows before padding and ldw is not used).
 extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,
                           long long ldc, int M, int N, int K, int mode, int up_row0, int schedule, float* partials,
                           long long partials_capacity, int* tile_counters, long long counters_capacity, int* error_flag,
-                          void* stream) {
+                          int packed, void* stream) {
     if (M == 0 || N == 0) return 0;
     HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     HB_REQUIRE(mode >= 0 && mode <= 3, "gemm_tc: unknown epilogue %d", mode);
     HB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
-    HB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc: row strides %lld and %lld must be multiples of 8 elements", lda, ldw);
-    HB_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_tc: a row stride is smaller than its row");
+    HB_REQUIRE(lda % 8 == 0 && (packed || ldw % 8 == 0), "gemm_tc: row strides %lld and %lld must be multiples of 8 elements", lda, ldw);
+    HB_REQUIRE(lda >= K && (packed || ldw >= K) && ldc >= N, "gemm_tc: a row stride is smaller than its row");
+    HB_REQUIRE(!packed || N <= w_rows, "gemm_tc: %d output features from a packed matrix of %lld rows", N, w_rows);
+    HB_REQUIRE(!packed || mode != TC_SWIGLU_BF16 || up_row0 % 64 == 0, "gemm_tc: packed up rows must start at a multiple of 64");
     HB_REQUIRE(error_flag != nullptr, "gemm_tc: no error flag");
     HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 + N <= w_rows, "gemm_tc: up rows lie outside the weight matrix");
     HB_REQUIRE(mode != TC_SWIGLU_BF16 || (ldc % 8 == 0 && ((uintptr_t)out & 15) == 0),
@@ -537,7 +566,7 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
                    "gemm_tc: stream-K needs %lld scratch floats and %lld counters", pl.scratch_floats, pl.tiles);
     }
     CUtensorMap mw, ma;
-    if (tc_make_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM)) return 1;
+    if (tc_make_weight_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM, packed)) return 1;
     if (tc_make_map(&ma, a, M, K, lda, pl.bn)) return 1;
     TcParams prm;
     prm.out = out;
@@ -555,6 +584,7 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
     prm.partials = partials;
     prm.counters = tile_counters;
     prm.error_flag = error_flag;
+    prm.packed = packed ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     switch (mode) {
         case TC_STORE_BF16: return dispatch_bn<TC_STORE_BF16>(pl.bn, mw, ma, prm, pl.grid, s);

@@ -81,13 +81,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             auto load_w = [&](int s, int t, int kb) {
-                const int n0 = (t / p.tiles_m) * (2 * FEAT) + (int)rank * FEAT, k = kb * TC_BK;
+                const int n0 = (t / p.tiles_m) * (2 * FEAT) + (int)rank * FEAT;
                 const uint32_t stage = smem_base + s * T2_STAGE_BYTES;
+                int x, y;
+                tc_w_coords(p, n0, kb, x, y);
+                tma_load_2d_pair(stage, &map_w, lead_full0 + 8 * s, x, y);
                 if (SWIGLU) {
-                    tma_load_2d_pair(stage, &map_w, lead_full0 + 8 * s, k, n0);
-                    tma_load_2d_pair(stage + W_BYTES / 2, &map_w, lead_full0 + 8 * s, k, p.up_row0 + n0);
-                } else {
-                    tma_load_2d_pair(stage, &map_w, lead_full0 + 8 * s, k, n0);
+                    tc_w_coords(p, p.up_row0 + n0, kb, x, y);
+                    tma_load_2d_pair(stage + W_BYTES / 2, &map_w, lead_full0 + 8 * s, x, y);
                 }
             };
             auto load_a = [&](int s, int t, int kb) {
@@ -266,13 +267,15 @@ extern "C" int hb_gemm_tc2_wanted(int M, int N, int K) { return M >= 512 && N >=
 
 // Arguments as hb_gemm_tc (no scratch: whole tiles only).
 extern "C" int hb_gemm_tc2(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,
-                           long long ldc, int M, int N, int K, int mode, int up_row0, int* error_flag, void* stream) {
+                           long long ldc, int M, int N, int K, int mode, int up_row0, int* error_flag, int packed, void* stream) {
     if (M == 0 || N == 0) return 0;
     HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc2: bad sizes M=%d N=%d K=%d", M, N, K);
     HB_REQUIRE(mode >= 0 && mode <= 3, "gemm_tc2: unknown epilogue %d", mode);
     HB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc2: operands must be 16-byte aligned");
-    HB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc2: row strides %lld and %lld must be multiples of 8 elements", lda, ldw);
-    HB_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_tc2: a row stride is smaller than its row");
+    HB_REQUIRE(lda % 8 == 0 && (packed || ldw % 8 == 0), "gemm_tc2: row strides %lld and %lld must be multiples of 8 elements", lda, ldw);
+    HB_REQUIRE(lda >= K && (packed || ldw >= K) && ldc >= N, "gemm_tc2: a row stride is smaller than its row");
+    HB_REQUIRE(!packed || N <= w_rows, "gemm_tc2: %d output features from a packed matrix of %lld rows", N, w_rows);
+    HB_REQUIRE(!packed || mode != TC_SWIGLU_BF16 || up_row0 % 64 == 0, "gemm_tc2: packed up rows must start at a multiple of 64");
     HB_REQUIRE(error_flag != nullptr, "gemm_tc2: no error flag");
     HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 + N <= w_rows, "gemm_tc2: up rows lie outside the weight matrix");
     HB_REQUIRE(mode != TC_SWIGLU_BF16 || (ldc % 8 == 0 && ((uintptr_t)out & 15) == 0),
@@ -294,12 +297,13 @@ extern "C" int hb_gemm_tc2(const void* a, long long lda, const void* w, long lon
     prm.partials = nullptr;
     prm.counters = nullptr;
     prm.error_flag = error_flag;
+    prm.packed = packed ? 1 : 0;
     const long long tiles = (long long)prm.tiles_m * prm.tiles_n;
     int pairs = resident_pairs(mode);
     if (pairs < 1) return hb_fail("gemm_tc2: no CTA pair can be resident on this device");
     if (tiles < pairs) pairs = (int)tiles;
     CUtensorMap mw, ma;
-    if (tc_make_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM)) return 1;
+    if (tc_make_weight_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM, packed)) return 1;
     if (tc_make_map(&ma, a, M, K, lda, T2_HALF)) return 1;
     cudaStream_t s = (cudaStream_t)stream;
     switch (mode) {

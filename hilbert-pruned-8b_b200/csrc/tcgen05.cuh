@@ -48,6 +48,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+// fetches a tensor map (a kernel parameter) into the descriptor cache ahead of its first use
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 // asks L2 to fetch a tile that a later tma_load will want
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
@@ -167,7 +171,23 @@ struct TcParams {
     float* partials;
     int* counters;
     int* error_flag;
+    int packed;           // W is stored as tiles [row / 128][K block][128 rows][64 columns] (see tc_w_coords)
 };
+
+// TMA coordinates of the box of weight rows that starts at `row`, K block kb.  Row-major W:
+// column kb * 64 of row `row`.  Packed W: every 128-row x 64-column tile is one contiguous
+// 16 KB piece and the K blocks of a 128-row band follow one another, so a CTA that walks
+// along K reads one sequential range; seen as a matrix of 64-column rows the tile starts at
+// row ((row / 128) * K blocks + kb) * 128.  A box must not straddle two bands.
+__device__ __forceinline__ void tc_w_coords(const TcParams& p, int row, int kb, int& x, int& y) {
+    if (p.packed) {
+        x = 0;
+        y = ((row >> 7) * p.kb_total + kb) * TC_BM + (row & (TC_BM - 1));
+    } else {
+        x = kb * TC_BK;
+        y = row;
+    }
+}
 
 #define TC_XCHG_BYTES (2 * 16 * 64 * 4 + 2 * 16 * 64 * 2)
 
@@ -233,8 +253,11 @@ __device__ __forceinline__ void tc_emit_chunk(const TcParams& p, int m0, int n0,
 // Epilogue of a summed partial tile held in the scratch layout [token][row]: thread et
 // (0..127) holds, for i = 0..BN/4-1, the four rows (et & 31) * 4 .. + 3 of token
 // i * 4 + (et >> 5).  The same results as tc_emit_chunk, with 16-byte accesses.
+// `res`: for TC_ADD_F32, the values of the output read ahead of time (have_res; they are then
+// not read again).
 template <int MODE, int BN>
-__device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, const float4 (&acc)[BN / 4], int et) {
+__device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, const float4 (&acc)[BN / 4], int et,
+                                             const float4 (&res)[BN / 4], bool have_res) {
     const int lane = et & 31, tw = et >> 5;
 #pragma unroll
     for (int i = 0; i < BN / 4; i++) {
@@ -276,7 +299,7 @@ __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, 
                 float* o = (float*)p.out + off;
                 if (n + 4 <= p.N && (((uintptr_t)o) & 15) == 0) {
                     float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    if (MODE == TC_ADD_F32) r = __ldcg(reinterpret_cast<const float4*>(o));
+                    if (MODE == TC_ADD_F32) r = have_res ? res[i] : __ldcg(reinterpret_cast<const float4*>(o));
                     *reinterpret_cast<float4*>(o) = make_float4(r.x + v[0], r.y + v[1], r.z + v[2], r.w + v[3]);
                 } else {
                     for (int e = 0; e < 4 && n + e < p.N; e++) o[e] = (MODE == TC_ADD_F32 ? o[e] : 0.0f) + v[e];
@@ -289,3 +312,4 @@ __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, 
 // Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements): boxes of
 // box_rows x 64 elements, 128-byte swizzle, zeros outside.
 int tc_make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows);
+int tc_make_weight_map(CUtensorMap* map, const void* w, long long rows, long long K, long long ld, int box_rows, int packed);

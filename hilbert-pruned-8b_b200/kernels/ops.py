@@ -12,6 +12,7 @@ names the size; no op returns a wrong result for an odd size.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -32,8 +33,9 @@ _SIGNATURES = {
     "hb_gemm_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
                         _c_int, _c_ptr],
     "hb_gemm_tc": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr],
-    "hb_gemm_tc2": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                   _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr],
+    "hb_gemm_tc2": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int,
+                    _c_ptr],
     "hb_attention_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                              _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
     "hb_attention_decode": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
@@ -98,6 +100,58 @@ def _rows(t: torch.Tensor, what: str) -> int:
     return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
 
 
+class PackedWeight:
+    """A bfloat16 weight matrix ``[rows, cols]`` stored for the tensor-core products: every
+    128-row x 64-column tile is one contiguous 16 KB piece, and the tiles of a 128-row band
+    follow one another along the columns (``data`` has the shape ``[bands, column blocks, 128,
+    64]``, zero beyond ``rows`` and ``cols``).  A CTA that walks along the columns of a band
+    then reads one sequential range of memory instead of 128 rows a whole matrix row apart."""
+
+    def __init__(self, data: torch.Tensor, rows: int, cols: int):
+        self.data, self.rows, self.cols = data, int(rows), int(cols)
+
+    @classmethod
+    def pack(cls, w: torch.Tensor) -> "PackedWeight":
+        rows, cols = w.shape
+        bands, blocks = -(-rows // 128), -(-cols // 64)
+        if rows % 128 or cols % 64:
+            full = torch.zeros(bands * 128, blocks * 64, dtype=w.dtype, device=w.device)
+            full[:rows, :cols] = w
+            w = full
+        return cls(w.view(bands, 128, blocks, 64).permute(0, 2, 1, 3).contiguous(), rows, cols)
+
+    def unpacked(self) -> torch.Tensor:
+        bands, blocks = self.data.shape[0], self.data.shape[1]
+        return self.data.permute(0, 2, 1, 3).reshape(bands * 128, blocks * 64)[: self.rows, : self.cols].contiguous()
+
+    def first_rows(self, n: int) -> "PackedWeight":
+        """The matrix of the first ``n`` rows (shares the storage)."""
+        if not 0 < n <= self.rows:
+            raise KernelError(f"first_rows: {n} of {self.rows} rows")
+        return PackedWeight(self.data, n, self.cols)
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    @property
+    def dtype(self):
+        return self.data.dtype
+
+    @property
+    def device(self):
+        return self.data.device
+
+    def numel(self) -> int:
+        return self.rows * self.cols
+
+    def element_size(self) -> int:
+        return self.data.element_size()
+
+    def data_ptr(self) -> int:
+        return self.data.data_ptr()
+
+
 class Ops:
     """The kernels bound to one device."""
 
@@ -119,6 +173,8 @@ class Ops:
         self.launches = 0  # kernels launched through this object (a claim bench.py reports)
         self.use_tensor_cores = True   # tests switch this off to compare the two matrix-product kernels
         self.use_pair_gemm = True      # many-token products on CTA pairs (cta_group::2)
+        # weights as contiguous tiles (PackedWeight); HILBERT_B200_PACK=0 keeps them row-major
+        self.use_packed_weights = os.environ.get("HILBERT_B200_PACK", "1") != "0"
         # device status word the tensor-core kernels set when one of their bounded waits ran out
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         # split-K scratch: float32 partial tiles and one counter per output tile (kept zero)
@@ -258,20 +314,31 @@ class Ops:
             raise KernelError(f"a tensor-core kernel gave up a bounded wait (code {code}); its results are invalid")
 
     # ------------------------------------------------------------------ matrix products
+    def pack_weight(self, w: torch.Tensor, swiglu: bool = False):
+        """``w`` as a PackedWeight when the tensor-core products can read it that way (bfloat16
+        on this device, rows of a multiple of 8 elements; a [gate; up] matrix needs halves of a
+        multiple of 64 rows), else ``w`` itself."""
+        if (not self.use_packed_weights or not isinstance(w, torch.Tensor) or w.dtype != torch.bfloat16 or w.dim() != 2
+                or w.device != self.device or w.shape[1] % 8 or (swiglu and (w.shape[0] // 2) % 64)):
+            return w
+        return PackedWeight.pack(w)
+
     def _tensor_core_operands(self, a, w) -> bool:
-        return (self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-                and _rows(a, "linear input") % 8 == 0 and _rows(w, "linear weight") % 8 == 0)
+        if not (self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and _rows(a, "linear input") % 8 == 0):
+            return False
+        return isinstance(w, PackedWeight) or _rows(w, "linear weight") % 8 == 0
 
     SCHEDULES = {None: 0, "auto": 0, "tiles": 1, "stream_k": 2}
 
     def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None) -> None:
         M, K = a.shape
+        packed = 1 if isinstance(w, PackedWeight) else 0
+        ldw = 64 if packed else _rows(w, "linear weight")
         if schedule == "pairs" or (schedule is None and self.use_pair_gemm and self.lib.hb_gemm_tc2_wanted(M, N, K)):
             # many tokens: CTA pairs (cta_group::2) on 256 x 256 tiles
-            self._call("hb_gemm_tc2", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), _rows(w, "linear weight"),
-                       w.shape[0], out.data_ptr(), _rows(out, "linear output"), M, N, K, mode, up_row0,
-                       self.error_flag.data_ptr(), self._stream())
+            self._call("hb_gemm_tc2", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), ldw, w.shape[0], out.data_ptr(),
+                       _rows(out, "linear output"), M, N, K, mode, up_row0, self.error_flag.data_ptr(), packed, self._stream())
             self.launches += 1
             return
         sched = self.SCHEDULES[schedule]
@@ -283,10 +350,10 @@ class Ops:
         if tiles > self._splitk_counters.numel():
             self._retired.append(self._splitk_counters)
             self._splitk_counters = torch.zeros(tiles, dtype=torch.int32, device=self.device)
-        self._call("hb_gemm_tc", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), _rows(w, "linear weight"),
+        self._call("hb_gemm_tc", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), ldw,
                    w.shape[0], out.data_ptr(), _rows(out, "linear output"), M, N, K, mode, up_row0, sched,
                    self._splitk_partials.data_ptr(), self._splitk_partials.numel(), self._splitk_counters.data_ptr(),
-                   self._splitk_counters.numel(), self.error_flag.data_ptr(), self._stream())
+                   self._splitk_counters.numel(), self.error_flag.data_ptr(), packed, self._stream())
         self.launches += 1
 
     def linear(self, a, w, out, accumulate: bool = False, schedule=None) -> None:
@@ -301,6 +368,8 @@ class Ops:
             mode = 2 if accumulate else (1 if out.dtype == torch.float32 else 0)
             self._gemm_tc(a, w, out, mode, N, 0, schedule)
             return
+        if isinstance(w, PackedWeight):
+            w = w.unpacked()           # not a product path: only operands the tensor-core kernels refuse get here
         self._call("hb_gemm_general", a.data_ptr(), _code(a), _rows(a, "linear input"), w.data_ptr(), _code(w),
                    _rows(w, "linear weight"), out.data_ptr(), _code(out), _rows(out, "linear output"), M, N, K,
                    1 if accumulate else 0, self._stream())
@@ -316,6 +385,8 @@ class Ops:
                 and _rows(act, "swiglu output") % 8 == 0):
             self._gemm_tc(h, w_gate_up, act, 3, inter, up_row0=inter, schedule=schedule)
             return
+        if isinstance(w_gate_up, PackedWeight):
+            w_gate_up = w_gate_up.unpacked()
         gu = workspace.buffer("swiglu.gate_up", (cap, 2 * inter), torch.float32 if act.dtype == torch.float32
                               else torch.bfloat16)[:T]
         self.linear(h, w_gate_up, gu)

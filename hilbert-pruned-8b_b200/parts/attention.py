@@ -50,8 +50,9 @@ class Attention(Mixer):
         q, k, v = tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]
         if not (q.dtype == k.dtype == v.dtype):
             raise ValueError("attention: q, k and v projections are stored in different dtypes")
-        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        pack = self.ctx.ops.pack_weight
+        self.w_qkv = pack(torch.cat([q, k, v], dim=0).contiguous())
+        self.w_o = pack(tensors["o_proj.weight"].contiguous())
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o))
@@ -68,7 +69,8 @@ class Attention(Mixer):
             ops.linear(h, self.w_qkv, qkv)
         else:
             # a layer that reads another layer's cache needs its queries only
-            ops.linear(h, self.w_qkv[: self.q_width], qkv[:, : self.q_width])
+            w_q = self.w_qkv.first_rows(self.q_width) if hasattr(self.w_qkv, "first_rows") else self.w_qkv[: self.q_width]
+            ops.linear(h, w_q, qkv[:, : self.q_width])
         table = self.position.table(step) if self.position is not None else None
         rot = self.position.rotary_dim if self.position is not None else 0
         attn = ws.buffer("attention.out", (cap, self.q_width), self.ctx.dtype)[:T]

@@ -46,10 +46,11 @@ class LMHead(Part):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         if not self.tied:
-            self.weight = tensors["weight"].contiguous()
+            self.weight = self.ctx.ops.pack_weight(tensors["weight"].contiguous())
 
     def tie(self, embedding_weight: torch.Tensor) -> None:
-        self.weight = embedding_weight
+        # the table is gathered from by rows; the head reads its own copy, stored as tiles
+        self.weight = self.ctx.ops.pack_weight(embedding_weight)
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -33,8 +33,9 @@ class SwiGLU(FeedForward):
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         if g.dtype != u.dtype:
             raise ValueError("swiglu: gate and up projections are stored in different dtypes")
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        pack = self.ctx.ops.pack_weight
+        self.w_gate_up = pack(torch.cat([g, u], dim=0).contiguous(), swiglu=True)
+        self.w_down = pack(tensors["down_proj.weight"].contiguous())
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))

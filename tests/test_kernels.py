@@ -241,6 +241,56 @@ def test_gemm_tensor_core_cta_pairs(ops, M, N, K):
     assert ops.lib.hb_gemm_tc2_resident_pairs(0) >= 32
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 512, 1024), (5, 100, 416), (64, 300, 2048), (16, 1000, 72), (600, 640, 520)])
+def test_gemm_tensor_core_packed_weights(ops, M, N, K):
+    """A weight stored as contiguous 128 x 64 tiles gives bit for bit the results of the
+    row-major one, in every work split and epilogue; a row prefix of it too; packing is exact."""
+    from hilbert_pruned_8b_b200.kernels.ops import PackedWeight
+    torch.manual_seed(31)
+    a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
+    pw = PackedWeight.pack(w)
+    assert pw.shape == (N, K) and torch.equal(pw.unpacked(), w)
+    res = torch.randn(M, N, device=DEV)
+    for schedule in ("stream_k", "tiles", "pairs"):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            one, two = torch.empty(M, N, device=DEV, dtype=out_dtype), torch.empty(M, N, device=DEV, dtype=out_dtype)
+            ops.linear(a, w, one, schedule=schedule)
+            ops.linear(a, pw, two, schedule=schedule)
+            ops.check_errors()
+            assert torch.equal(one, two), (schedule, out_dtype)
+        acc1, acc2 = res.clone(), res.clone()
+        ops.linear(a, w, acc1, accumulate=True, schedule=schedule)
+        ops.linear(a, pw, acc2, accumulate=True, schedule=schedule)
+        assert torch.equal(acc1, acc2), schedule
+    n = N - 37
+    one, two = torch.empty(M, n, device=DEV), torch.empty(M, n, device=DEV)
+    ops.linear(a, w[:n], one)
+    ops.linear(a, pw.first_rows(n), two)
+    assert torch.equal(one, two)
+    ref = a.double() @ w.double().t()
+    out = torch.empty(M, N, device=DEV)
+    ops.linear(a, pw, out)
+    assert _rel(out, ref) < 2e-6 * math.sqrt(K)
+
+
+@pytest.mark.parametrize("M,K,I", [(3, 160, 448), (130, 256, 320), (8, 4096, 512), (700, 512, 1024)])
+def test_linear_swiglu_packed_weights(ops, M, K, I):
+    from hilbert_pruned_8b_b200.engine.workspace import Workspace
+    torch.manual_seed(32)
+    h = _bf(torch.randn(M, K, device=DEV))
+    w = _bf(torch.randn(2 * I, K, device=DEV) / math.sqrt(K))
+    pw = ops.pack_weight(w, swiglu=True)
+    assert not isinstance(pw, torch.Tensor)
+    assert isinstance(ops.pack_weight(_bf(torch.randn(2 * 100, K, device=DEV)), swiglu=True), torch.Tensor)   # halves of 100 rows: not packed
+    ws = Workspace(torch.device(DEV))
+    for schedule in ("tiles", "stream_k", "pairs"):
+        one, two = torch.empty(M, I, device=DEV, dtype=torch.bfloat16), torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+        ops.linear_swiglu(h, w, one, ws, M, schedule=schedule)
+        ops.linear_swiglu(h, pw, two, ws, M, schedule=schedule)
+        ops.check_errors()
+        assert torch.equal(one, two), schedule
+
+
 @pytest.mark.parametrize("schedule", ["tiles", "stream_k", "pairs"])
 @pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 304), (8, 4096, 512), (300, 512, 1000)])
 def test_linear_swiglu(ops, M, K, I, schedule):
