@@ -238,12 +238,11 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
 __device__ __forceinline__ float rotated(const bf16* __restrict__ x, int d, int rot, const float2* __restrict__ cs_row) {
     const int half = rot >> 1;
     if (d >= rot) return __bfloat162float(x[d]);
-    if (d < half) {
-        const float2 cs = cs_row[d];
-        return __bfloat162float(x[d]) * cs.x - __bfloat162float(x[d + half]) * cs.y;
-    }
-    const float2 cs = cs_row[d - half];
-    return __bfloat162float(x[d]) * cs.x + __bfloat162float(x[d - half]) * cs.y;
+    const int i = d < half ? d : d - half;
+    const float2 cs = cs_row[i];
+    float y1, y2;
+    rope_pair(__bfloat162float(x[i]), __bfloat162float(x[i + half]), cs.x, cs.y, y1, y2);
+    return d < half ? y1 : y2;
 }
 
 // The whole attention of a decode step in one launch: rotate the new token's queries and key,

@@ -193,6 +193,14 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// One rotated pair (cleanroom-transformer/src/cpu_backend.c:92-97): products rounded to
+// float32 one by one, then added, with no fused multiply-add, so that every kernel that
+// rotates gives the same bits.
+__device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, float& y1, float& y2) {
+    y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+    y2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+}
+
 // silu(z) = z / (1 + exp(-z))  (cleanroom-transformer/src/ops_common.h:56)
 __device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
 

@@ -220,9 +220,10 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
             const int h = h0 + idx / half, i = idx % half;
             T* x = row + (size_t)h * hd;
             const float2 cs = cs_row[i];
-            const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
-            x[i] = from_f32<T>(x1 * cs.x - x2 * cs.y);
-            x[i + half] = from_f32<T>(x2 * cs.x + x1 * cs.y);
+            float y1, y2;
+            rope_pair(to_f32(x[i]), to_f32(x[i + half]), cs.x, cs.y, y1, y2);
+            x[i] = from_f32<T>(y1);
+            x[i + half] = from_f32<T>(y2);
         }
         return;
     }
@@ -236,9 +237,10 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
         const T* x = krow + (size_t)g * hd;
         TC* dst = k_cache + cache_offset(page, g, pos, nkv, hd);
         const float2 cs = cs_row[i];
-        const float x1 = to_f32(x[i]), x2 = to_f32(x[i + half]);
-        dst[i] = from_f32<TC>(x1 * cs.x - x2 * cs.y);
-        dst[i + half] = from_f32<TC>(x2 * cs.x + x1 * cs.y);
+        float y1, y2;
+        rope_pair(to_f32(x[i]), to_f32(x[i + half]), cs.x, cs.y, y1, y2);
+        dst[i] = from_f32<TC>(y1);
+        dst[i + half] = from_f32<TC>(y2);
     }
     const int tail = hd - rot;
     for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
@@ -248,6 +250,76 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
         const int g = idx / hd, i = idx - g * hd;
         v_cache[cache_offset(page, g, pos, nkv, hd) + i] = from_f32<TC>(to_f32(vrow[idx]));
+    }
+}
+
+// The same for many bfloat16 tokens: one block per token, 16-byte accesses (8 elements of the
+// first half of a head and the matching 8 of the second half per task).  Needs rot % 16 == 0,
+// hd % 8 == 0 and 16-byte aligned rows.
+__device__ __forceinline__ void rope8(const uint4 lo, const uint4 hi, const float2* __restrict__ cs, uint4& out_lo, uint4& out_hi) {
+    const bf16* a = reinterpret_cast<const bf16*>(&lo);
+    const bf16* b = reinterpret_cast<const bf16*>(&hi);
+    bf16* ya = reinterpret_cast<bf16*>(&out_lo);
+    bf16* yb = reinterpret_cast<bf16*>(&out_hi);
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        float y1, y2;
+        rope_pair(__bfloat162float(a[e]), __bfloat162float(b[e]), cs[e].x, cs[e].y, y1, y2);
+        ya[e] = __float2bfloat16_rn(y1);
+        yb[e] = __float2bfloat16_rn(y2);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+rope_kv_append_vec_kernel(bf16* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot, int nh,
+                          int nkv, int hd, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                          const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
+                          const int* __restrict__ positions, int n_pages, int append) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = rot >> 1, hv = half >> 3;                 // 8-element pieces per half head
+    bf16* row = qkv + (size_t)t * qkv_stride;
+    const float2* cs_row = table + (size_t)t * half;
+    int page = -1, pos = 0;
+    if (append) {
+        pos = positions[t];
+        page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
+        if (page < 0 || page >= n_pages) page = -1;            // the host reserved the pages; never write outside the cache
+    }
+    const int q_tasks = nh * hv;
+    const int k_tasks = page >= 0 ? nkv * hv : 0;
+    const int kt_tasks = page >= 0 ? nkv * ((hd - rot) >> 3) : 0;
+    const int v_tasks = page >= 0 ? nkv * (hd >> 3) : 0;
+    const int total = q_tasks + k_tasks + kt_tasks + v_tasks;
+    const bf16* krow = row + (size_t)nh * hd;
+    const bf16* vrow = krow + (size_t)nkv * hd;
+    for (int task = threadIdx.x; task < total; task += blockDim.x) {
+        if (task < q_tasks + k_tasks) {
+            const bool is_q = task < q_tasks;
+            const int u = is_q ? task : task - q_tasks;
+            const int h = u / hv, i = (u - h * hv) << 3;
+            const bf16* x = (is_q ? row : krow) + (size_t)h * hd;
+            bf16* dst = is_q ? row + (size_t)h * hd : k_cache + cache_offset(page, h, pos, nkv, hd);
+            float2 cs[8];
+            const float4* c4 = reinterpret_cast<const float4*>(cs_row + i);
+#pragma unroll
+            for (int e = 0; e < 4; e++) reinterpret_cast<float4*>(cs)[e] = c4[e];
+            uint4 o_lo, o_hi;
+            rope8(*reinterpret_cast<const uint4*>(x + i), *reinterpret_cast<const uint4*>(x + i + half), cs, o_lo, o_hi);
+            *reinterpret_cast<uint4*>(dst + i) = o_lo;
+            *reinterpret_cast<uint4*>(dst + i + half) = o_hi;
+        } else if (task < q_tasks + k_tasks + kt_tasks) {
+            const int u = task - q_tasks - k_tasks, per = (hd - rot) >> 3;
+            const int g = u / per, i = rot + ((u - g * per) << 3);
+            *reinterpret_cast<uint4*>(k_cache + cache_offset(page, g, pos, nkv, hd) + i) =
+                *reinterpret_cast<const uint4*>(krow + (size_t)g * hd + i);
+        } else {
+            const int u = task - q_tasks - k_tasks - kt_tasks, per = hd >> 3;
+            const int g = u / per, i = (u - g * per) << 3;
+            *reinterpret_cast<uint4*>(v_cache + cache_offset(page, g, pos, nkv, hd) + i) =
+                *reinterpret_cast<const uint4*>(vrow + (size_t)g * hd + i);
+        }
     }
 }
 
@@ -267,6 +339,16 @@ extern "C" int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride,
     HB_REQUIRE(groups <= 65535, "rope_kv_append: too many heads");
     cudaStream_t s = (cudaStream_t)stream;
     const float2* tab = (const float2*)table;
+    // many bfloat16 tokens: one block per token with 16-byte accesses (few tokens keep the
+    // many small blocks, which finish sooner)
+    if (qkv_dtype == HB_BF16 && cache_dtype == HB_BF16 && n_tokens >= 64 && rot > 0 && rot % 16 == 0 && head_dim % 8 == 0 &&
+        qkv_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)table & 15) == 0 &&
+        ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0) {
+        hb_launch(rope_kv_append_vec_kernel, dim3(n_tokens), dim3(256), 0, s, (bf16*)qkv, qkv_stride, tab, rot, n_heads,
+                  n_kv_heads, head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table, pt_width, tok_seq, positions, n_pages,
+                  append);
+        return hb_check_launch("rope_kv_append");
+    }
     if (qkv_dtype == HB_BF16 && cache_dtype == HB_BF16)
         hb_launch(rope_kv_append_kernel<bf16, bf16>, dim3(n_tokens, groups), dim3(threads), 0, s, (bf16*)qkv, qkv_stride, tab, rot,
                   n_heads, n_kv_heads, head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table, pt_width, tok_seq, positions,

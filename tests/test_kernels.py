@@ -88,6 +88,34 @@ def _cache(n_pages, nkv, hd, dtype):
     return LayerCache(k, torch.zeros_like(k), 0, None)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot,append", [(6, 3, 48, 48, True), (5, 1, 80, 32, True), (32, 8, 128, 128, True),
+                                                  (3, 1, 64, 64, False)])
+def test_rope_kv_append_many_tokens(ops, nh, nkv, hd, rot, append):
+    """64 tokens and more take the one-block-per-token kernel with 16-byte accesses: the same
+    bits as the few-token kernel (run here on slices of under 64 tokens)."""
+    torch.manual_seed(33)
+    lens = [70, 3, 130]                                     # three sequences, the first and last cross pages
+    T = sum(lens)
+    positions = torch.tensor([p for n in lens for p in range(n)], dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([i for i, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    tables = torch.tensor([[5, 2, -1], [0, -1, -1], [1, 6, 3]], dtype=torch.int32, device=DEV)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, device=DEV).to(torch.bfloat16)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+    table = torch.empty(T, rot // 2, 2, device=DEV)
+    ops.rope_table(positions, inv, table)
+    fast, cache_fast = qkv.clone(), _cache(7, nkv, hd, torch.bfloat16)
+    ops.rope_kv_append(fast, table, rot, nh, nkv, hd, cache_fast, _step(tok_seq, positions, tables), append)
+    slow, cache_slow = qkv.clone(), _cache(7, nkv, hd, torch.bfloat16)
+    for a in range(0, T, 50):
+        b = min(T, a + 50)
+        ops.rope_kv_append(slow[a:b], table[a:b], rot, nh, nkv, hd, cache_slow, _step(tok_seq[a:b], positions[a:b], tables), append)
+    assert torch.equal(fast, slow)
+    assert torch.equal(cache_fast.k, cache_slow.k) and torch.equal(cache_fast.v, cache_slow.v)
+    assert (cache_fast.k.abs().sum() > 0) == append
+    assert cache_fast.k[4].abs().sum() == 0                 # a page of nobody stays clean
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(6, 3, 48, 48), (5, 1, 80, 40), (8, 8, 16, 16)])
 def test_rope_kv_append(ops, dtype, nh, nkv, hd, rot):
