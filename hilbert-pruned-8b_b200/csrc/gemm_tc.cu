@@ -35,6 +35,8 @@
 //
 // Requirements (checked on the host, refused with a message otherwise): bfloat16 A and W,
 // 16-byte aligned bases, row strides that are multiples of 8 elements.  Any M, N and K.
+#include <stdlib.h>
+
 #include "api.h"
 #include "tcgen05.cuh"
 
@@ -48,7 +50,9 @@ struct TcLayout {
     static constexpr int NBUF = 2;                                     // accumulator buffers
     static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
     static constexpr int XCHG_BYTES = SWIGLU ? TC_XCHG_BYTES : 0;
+    static constexpr int PART_BYTES = BN * TC_BM * 4;                  // one partial tile, float32 [token][row]
 };
+#define TC_MAX_CLUSTER 8        // portable cluster size: the most K ranges a tile is cut into in cluster mode
 
 // The work items of one CTA, in order: (tile, first K block, end K block).
 struct TcSchedule {
@@ -56,6 +60,7 @@ struct TcSchedule {
     int cur, end, step;       // stream-K: unit cursor and range end; tiles: tile cursor and stride
     long long base;
     int rem, grid, cta;
+    int whole_left, whole_next;   // mode 3: whole tiles still to come and the next one
     __device__ __forceinline__ void init(const TcParams& p) {
         tiles = p.tiles_m * p.tiles_n;
         kbt = p.kb_total;
@@ -70,7 +75,13 @@ struct TcSchedule {
             end = t * kbt + min(kbt, (part + 1) * per);
             if (t >= tiles) end = cur;
         } else if (stream_k) {
-            const long long units = (long long)tiles * kbt;
+            // mode 3: the first tiles % grid tiles are cut like mode 1, then every CTA takes
+            // tiles / grid whole tiles, so that the kernel ends with plain epilogues and the
+            // sums of the cut tiles happen while the whole tiles stream
+            whole_left = stream_k == 3 ? tiles / grid : 0;
+            const int cut_tiles = tiles - whole_left * grid;
+            whole_next = cut_tiles + cta;
+            const long long units = (long long)cut_tiles * kbt;
             base = units / grid;
             rem = (int)(units % grid);
             const long long b = cta;
@@ -83,6 +94,15 @@ struct TcSchedule {
         }
     }
     __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1) {
+        if (stream_k == 3 && cur >= end) {
+            if (whole_left <= 0) return false;
+            tile = whole_next;
+            kb0 = 0;
+            kb1 = kbt;
+            whole_next += grid;
+            whole_left--;
+            return true;
+        }
         if (cur >= end) return false;
         if (stream_k) {
             tile = cur / kbt;
@@ -121,7 +141,12 @@ struct TcSchedule {
 // (producer), 2 first stage full (MMA thread), 3 last MMA of a work item committed, 4 accumulator
 // full (epilogue), 5 partial tile written and fenced, 6 tile counter known, 7 tile emitted,
 // 8 block end.
-template <int BN, int MODE, int STAGES>
+//
+// CLUSTER (few tokens, every tile cut into `split` <= 8 equal K ranges): the CTAs of a tile are
+// one thread-block cluster.  Each writes its partial tile into the shared memory of the
+// cluster's first CTA (st.shared::cluster), one cluster barrier later that CTA sums the partial
+// tiles in K order and runs the epilogue: no scratch in global memory, no fence, no counter.
+template <int BN, int MODE, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
     using L = TcLayout<BN, MODE>;
@@ -129,7 +154,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* xchg = smem + STAGES * L::STAGE_BYTES;
-    uint64_t* bars = (uint64_t*)(xchg + L::XCHG_BYTES);        // full[S], empty[S], acc_full[2], acc_empty[2]
+    uint8_t* xpart = xchg + L::XCHG_BYTES;                     // CLUSTER: partial tiles [part][token][row] (first CTA's copy is used)
+    uint64_t* bars = (uint64_t*)(xpart + (CLUSTER ? TC_MAX_CLUSTER * L::PART_BYTES : 0));   // full[S], empty[S], acc_full[2], acc_empty[2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* last_flag = (int*)(tmem_slot + 2);
@@ -192,6 +218,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_trigger();
+
+    // CLUSTER: what the first CTA's epilogue threads carry across the cluster barrier
+    constexpr int CL_NV = BN <= 64 ? BN / 4 : 1;
+    float4 cl_res[CL_NV];
+    int cl_m0 = 0, cl_n0 = 0;
+    bool cl_have_res = false, cl_done = false;
+    const int et = (warp - 2) * 32 + lane;         // 0..127 among the epilogue threads (warps 2..5)
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -271,7 +304,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;                    // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;             // weight row of the tile = TMEM lane
-        const int et = (warp - 2) * 32 + lane;     // 0..127 among the epilogue threads
         pdl_wait();                                // the output, the scratch and the counters belong to earlier kernels until now
         int item = 0;
         while (sched.next(tile, kb0, kb1)) {
@@ -304,6 +336,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     res[i] = (m < p.M && n < p.N) ? __ldcg(reinterpret_cast<const float4*>((const float*)p.out + (size_t)m * p.ldc + n))
                                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 }
+            }
+            if (CLUSTER) {
+                // partial tile into the first CTA's shared memory, slot = this CTA's K range
+                cl_m0 = m0;
+                cl_n0 = n0;
+                cl_have_res = have_res;
+#pragma unroll
+                for (int i = 0; i < NV; i++) cl_res[i] = res[i];
+                const uint32_t dst = mapa_shared(smem_u32(xpart) + (blockIdx.x % p.split) * L::PART_BYTES, 0);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    tmem_ld16(lane_addr + c, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) st_cluster_f32(dst + ((c + j) * TC_BM + row) * 4, v[j]);
+                }
+                tc_fence_before();
+                mbar_arrive(acce0 + 8 * buf);
+                cl_done = true;
+                item++;
+                continue;
             }
             if (!whole) {
                 // partial tile to scratch: [tile][slot][token][row], float32
@@ -386,6 +439,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             item++;
         }
     }
+    if (CLUSTER) {
+        // Every thread of every CTA of the cluster gets here exactly once (the loops above are
+        // left by `break`, never by `return`).  After the barrier the partial tiles of all K
+        // ranges lie in the first CTA's shared memory.
+        cluster_sync_all();
+        if (warp >= 2 && blockIdx.x % p.split == 0 && cl_done && !*abort_flag) {
+            const int parts = (p.kb_total + ((p.kb_total + p.split - 1) / p.split) - 1) / ((p.kb_total + p.split - 1) / p.split);
+            float4 acc[CL_NV];
+#pragma unroll
+            for (int i = 0; i < CL_NV; i++) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int z = 0; z < parts; z++) {
+                const float4* pz = reinterpret_cast<const float4*>(xpart + z * L::PART_BYTES) + et;
+#pragma unroll
+                for (int i = 0; i < CL_NV; i++) {
+                    const float4 t = pz[i * TC_BM];
+                    acc[i].x += t.x;
+                    acc[i].y += t.y;
+                    acc[i].z += t.z;
+                    acc[i].w += t.w;
+                }
+            }
+            tc_emit_flat<MODE, BN <= 64 ? BN : 4>(p, cl_m0, cl_n0, acc, et, cl_res, cl_have_res);
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -454,8 +531,17 @@ static int sm_count() {
 
 extern "C" int hb_gemm_tc_token_tile(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
+static bool clusters_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("HILBERT_B200_CLUSTER");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
 // The work split of a product: tiles, grid, stream-K or not, scratch.  schedule: 0 automatic,
-// 1 whole tiles round-robin, 2 stream-K.
+// 1 whole tiles round-robin, 2 stream-K, 3 cut tiles first and whole tiles after.
 struct TcPlan {
     int bn, feat, tiles_m, tiles_n, kb_total, grid, stream_k, max_slots, split;
     long long scratch_floats, tiles;
@@ -473,7 +559,17 @@ static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
     const long long units = pl.tiles * pl.kb_total;
     pl.stream_k = schedule == 2 || (schedule == 0 && pl.tiles_m == 1 && pl.bn <= 64);
     pl.split = 1;
-    if (pl.stream_k) {
+    if (schedule == 3 || (schedule == 0 && pl.stream_k && pl.tiles >= sms)) {
+        // As many tiles as SMs or more: tiles % SMs tiles are cut over all CTAs first, then
+        // every CTA takes tiles / SMs whole tiles: the sums of the cut tiles overlap the whole
+        // tiles and the kernel ends with plain epilogues.
+        pl.stream_k = 3;
+        pl.grid = (int)(units < sms ? units : sms);
+        const long long cut_tiles = pl.tiles % pl.grid, base = cut_tiles * pl.kb_total / pl.grid;
+        pl.max_slots = base > 0 ? (int)(pl.kb_total / base) + 2 : pl.kb_total;
+        if (pl.max_slots > pl.grid) pl.max_slots = pl.grid;
+        pl.scratch_floats = cut_tiles * pl.max_slots * (long long)pl.bn * TC_BM;
+    } else if (pl.stream_k) {
         // Few tiles: either every SM takes one contiguous range of the whole (tile, K block)
         // space, or each tile is cut into floor(SMs / tiles) equal K ranges (one work item per
         // CTA, fewer partial tiles).  Costs in K blocks; a work item costs about six K blocks
@@ -482,7 +578,9 @@ static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
         g = g < 1 ? 1 : g > sms ? sms : g;
         if (schedule == 0 && pl.tiles < sms) {
             const long long split = sms / pl.tiles;
-            const long long aligned_cost = (pl.kb_total + split - 1) / split + 6;
+            // (four where the K ranges of a tile can be a cluster, which sums in shared memory)
+            const int fixed = (pl.bn == 16 && split >= 2 && split <= TC_MAX_CLUSTER && clusters_enabled()) ? 4 : 6;
+            const long long aligned_cost = (pl.kb_total + split - 1) / split + fixed;
             const long long stream_cost = units / g + 12;
             if (aligned_cost <= stream_cost && pl.kb_total / split >= 4) {
                 pl.stream_k = 2;
@@ -511,30 +609,76 @@ extern "C" long long hb_gemm_tc_scratch_floats(int M, int N, int K, int mode, in
 }
 extern "C" long long hb_gemm_tc_tiles(int M, int N, int mode) { return make_plan(M, N, 64, mode, 1).tiles; }
 
-template <int BN, int MODE, int STAGES>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
+template <int BN, int MODE, int STAGES, bool CLUSTER>
+struct TcLaunch {
     using L = TcLayout<BN, MODE>;
-    constexpr int SMEM = STAGES * L::STAGE_BYTES + L::XCHG_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+    static constexpr int SMEM = STAGES * L::STAGE_BYTES + L::XCHG_BYTES + (CLUSTER ? TC_MAX_CLUSTER * L::PART_BYTES : 0) +
+                                (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(SMEM <= 227 * 1024, "tile pipeline does not fit shared memory");
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return hb_fail("gemm_tc: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
-        attr_set = true;
+    static int prepare() {
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            if (e != cudaSuccess) return hb_fail("gemm_tc: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+            attr_set = true;
+        }
+        return 0;
     }
-    cudaError_t e = hb_launch(gemm_tc_kernel<BN, MODE, STAGES>, dim3(grid), dim3(TC_THREADS), SMEM, s, mw, ma, prm);
-    if (e != cudaSuccess) return hb_fail("gemm_tc: launch failed: %s", cudaGetErrorString(e));
-    return hb_check_launch("gemm_tc");
+    static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
+        if (prepare()) return 1;
+        cudaError_t e = CLUSTER ? hb_launch_clusters(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, dim3(grid), dim3(TC_THREADS), SMEM, s,
+                                                     (unsigned)prm.split, mw, ma, prm)
+                                : hb_launch(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, dim3(grid), dim3(TC_THREADS), SMEM, s, mw, ma, prm);
+        if (e != cudaSuccess) return hb_fail("gemm_tc: launch failed: %s", cudaGetErrorString(e));
+        return hb_check_launch("gemm_tc");
+    }
+    // how many clusters of `size` CTAs can be resident at once (0: the query failed)
+    static int resident_clusters(int size) {
+        if (prepare()) return 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(size * 1024);
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = SMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = size;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        return n;
+    }
+};
+
+// The cluster variant of the 16-token kernel: fewer stages, room for the partial tiles.
+template <int MODE>
+using TcClusterLaunch = TcLaunch<16, MODE, MODE == TC_SWIGLU_BF16 ? 7 : 8, true>;
+
+template <int MODE>
+static bool clusters_fit(int size, long long tiles) {
+    static int cached[TC_MAX_CLUSTER + 1] = {0};      // 0: not asked yet, -1: none
+    if (size < 2 || size > TC_MAX_CLUSTER) return false;
+    if (cached[size] == 0) {
+        const int n = TcClusterLaunch<MODE>::resident_clusters(size);
+        cached[size] = n > 0 ? n : -1;
+    }
+    return cached[size] >= tiles;
 }
 
 template <int MODE>
-static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
+static int dispatch_bn(int bn, bool cluster, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
+    if (cluster) return TcClusterLaunch<MODE>::launch(mw, ma, prm, grid, s);
     switch (bn) {
-        case 16: return launch_tc<16, MODE, 11>(mw, ma, prm, grid, s);
-        case 32: return launch_tc<32, MODE, 10>(mw, ma, prm, grid, s);
-        case 64: return launch_tc<64, MODE, 8>(mw, ma, prm, grid, s);
-        case 128: return launch_tc<128, MODE, 6>(mw, ma, prm, grid, s);
-        case 256: return launch_tc<256, MODE, 4>(mw, ma, prm, grid, s);
+        case 16: return TcLaunch<16, MODE, 11, false>::launch(mw, ma, prm, grid, s);
+        case 32: return TcLaunch<32, MODE, 10, false>::launch(mw, ma, prm, grid, s);
+        case 64: return TcLaunch<64, MODE, 8, false>::launch(mw, ma, prm, grid, s);
+        case 128: return TcLaunch<128, MODE, 6, false>::launch(mw, ma, prm, grid, s);
+        case 256: return TcLaunch<256, MODE, 4, false>::launch(mw, ma, prm, grid, s);
     }
     return hb_fail("gemm_tc: token tile %d is not built", bn);
 }
@@ -585,11 +729,23 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
     prm.counters = tile_counters;
     prm.error_flag = error_flag;
     prm.packed = packed ? 1 : 0;
+    // every tile cut into 2..8 equal K ranges, 16 tokens: the ranges' CTAs as one cluster, if
+    // all clusters can be resident at once (HILBERT_B200_CLUSTER=0: never)
+    bool cluster = pl.stream_k == 2 && pl.bn == 16 && pl.split >= 2 && pl.split <= TC_MAX_CLUSTER && clusters_enabled();
+    if (cluster) {
+        switch (mode) {
+            case TC_STORE_BF16: cluster = clusters_fit<TC_STORE_BF16>(pl.split, pl.tiles); break;
+            case TC_STORE_F32: cluster = clusters_fit<TC_STORE_F32>(pl.split, pl.tiles); break;
+            case TC_ADD_F32: cluster = clusters_fit<TC_ADD_F32>(pl.split, pl.tiles); break;
+            default: cluster = clusters_fit<TC_SWIGLU_BF16>(pl.split, pl.tiles); break;
+        }
+    }
+    prm.cluster = cluster ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     switch (mode) {
-        case TC_STORE_BF16: return dispatch_bn<TC_STORE_BF16>(pl.bn, mw, ma, prm, pl.grid, s);
-        case TC_STORE_F32: return dispatch_bn<TC_STORE_F32>(pl.bn, mw, ma, prm, pl.grid, s);
-        case TC_ADD_F32: return dispatch_bn<TC_ADD_F32>(pl.bn, mw, ma, prm, pl.grid, s);
-        default: return dispatch_bn<TC_SWIGLU_BF16>(pl.bn, mw, ma, prm, pl.grid, s);
+        case TC_STORE_BF16: return dispatch_bn<TC_STORE_BF16>(pl.bn, cluster, mw, ma, prm, pl.grid, s);
+        case TC_STORE_F32: return dispatch_bn<TC_STORE_F32>(pl.bn, cluster, mw, ma, prm, pl.grid, s);
+        case TC_ADD_F32: return dispatch_bn<TC_ADD_F32>(pl.bn, cluster, mw, ma, prm, pl.grid, s);
+        default: return dispatch_bn<TC_SWIGLU_BF16>(pl.bn, cluster, mw, ma, prm, pl.grid, s);
     }
 }

@@ -121,6 +121,9 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -165,12 +168,14 @@ struct TcParams {
     int tiles_m, tiles_n;
     int kb_total;         // K blocks per tile
     int stream_k;         // 0: whole tiles round-robin; 1: contiguous (tile, K block) ranges per CTA;
-                          // 2: every tile cut into `split` equal K ranges, one per CTA
+                          // 2: every tile cut into `split` equal K ranges, one per CTA;
+                          // 3: the first tiles % grid tiles cut as in 1, then tiles / grid whole tiles per CTA
     int split;
     int max_slots;        // partial tiles per output tile in scratch (stream-K)
     float* partials;
     int* counters;
     int* error_flag;
+    int cluster;          // stream_k == 2 only: the `split` CTAs of a tile are one cluster and sum through shared memory
     int packed;           // W is stored as tiles [row / 128][K block][128 rows][64 columns] (see tc_w_coords)
 };
 

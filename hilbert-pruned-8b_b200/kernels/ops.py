@@ -329,7 +329,7 @@ class Ops:
             return False
         return isinstance(w, PackedWeight) or _rows(w, "linear weight") % 8 == 0
 
-    SCHEDULES = {None: 0, "auto": 0, "tiles": 1, "stream_k": 2}
+    SCHEDULES = {None: 0, "auto": 0, "tiles": 1, "stream_k": 2, "cut_first": 3}
 
     def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None) -> None:
         M, K = a.shape

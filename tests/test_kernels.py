@@ -220,15 +220,16 @@ def test_gemm_tensor_core_against_plain_and_general(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(8, 512, 1024), (1, 384, 4096), (64, 256, 2048), (5, 100, 416), (40, 4096, 512),
-                                   (16, 20000, 256), (200, 384, 1024)])
+                                   (16, 20000, 256), (200, 384, 1024), (8, 28672, 512), (3, 19000, 64)])
 def test_gemm_tensor_core_stream_k_and_tiles(ops, M, N, K):
-    """Both work splits of the tensor-core kernel: stream-K (partial tiles in scratch, summed
-    in K order by the last contributor) and whole tiles round-robin (several per CTA)."""
+    """The work splits of the tensor-core kernel: stream-K (partial tiles in scratch, summed
+    in K order by the last contributor), whole tiles round-robin (several per CTA), and cut
+    tiles first with whole tiles after (what many tiles of few tokens get)."""
     torch.manual_seed(7)
     a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
     ref = a.double() @ w.double().t()
     res = torch.randn(M, N, device=DEV)
-    for schedule in ("stream_k", "tiles"):
+    for schedule in ("stream_k", "tiles", "cut_first"):
         for rep in range(2):                    # twice: the tile counters must come back to zero
             acc = res.clone()
             ops.linear(a, w, acc, accumulate=True, schedule=schedule)
@@ -267,6 +268,40 @@ def test_gemm_tensor_core_cta_pairs(ops, M, N, K):
     ops.linear(a, w, two, schedule="pairs")
     assert _rel(two, one) < 1e-6 * math.sqrt(K)
     assert ops.lib.hb_gemm_tc2_resident_pairs(0) >= 32
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (3, 3072, 3072), (16, 6144, 4096), (8, 2560, 2048), (8, 2304, 2112),
+                                   (1, 4000, 1536)])
+def test_gemm_tensor_core_cluster_split(ops, M, N, K):
+    """Few tokens and 19 to 74 tiles: every tile is cut into 2 to 8 K ranges whose CTAs form a
+    cluster and sum their partial tiles through the first CTA's shared memory (the last size
+    leaves one CTA of each cluster without work).  Every epilogue, twice (same bits)."""
+    torch.manual_seed(34)
+    a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
+    ref = a.double() @ w.double().t()
+    res = torch.randn(M, N, device=DEV)
+    acc = res.clone()
+    ops.linear(a, w, acc, accumulate=True)
+    ops.check_errors()
+    assert _rel(acc, ref + res.double()) < 2e-6 * math.sqrt(K)
+    acc2 = res.clone()
+    ops.linear(a, ops.pack_weight(w), acc2, accumulate=True)
+    assert torch.equal(acc, acc2)
+    for dtype, tol in ((torch.bfloat16, 2 ** -8), (torch.float32, 2e-6 * math.sqrt(K))):
+        out, again = torch.empty(M, N, device=DEV, dtype=dtype), torch.empty(M, N, device=DEV, dtype=dtype)
+        ops.linear(a, w, out)
+        ops.linear(a, w, again)
+        ops.check_errors()
+        assert _rel(out, ref) < tol and torch.equal(out, again)
+    if N % 128 == 0:
+        from hilbert_pruned_8b_b200.engine.workspace import Workspace
+        I = N // 2
+        act = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+        ws_ = _bf(w / math.sqrt(K))
+        ops.linear_swiglu(a, ws_, act, Workspace(torch.device(DEV)), M)
+        ops.check_errors()
+        g, u = a.double() @ ws_[:I].double().t(), a.double() @ ws_[I:].double().t()
+        assert _rel(act, g / (1 + torch.exp(-g)) * u) < 2 ** -7
 
 
 @pytest.mark.parametrize("M,N,K", [(8, 512, 1024), (5, 100, 416), (64, 300, 2048), (16, 1000, 72), (600, 640, 520)])
@@ -319,7 +354,7 @@ def test_linear_swiglu_packed_weights(ops, M, K, I):
         assert torch.equal(one, two), schedule
 
 
-@pytest.mark.parametrize("schedule", ["tiles", "stream_k", "pairs"])
+@pytest.mark.parametrize("schedule", ["tiles", "stream_k", "pairs", "cut_first"])
 @pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 304), (8, 4096, 512), (300, 512, 1000)])
 def test_linear_swiglu(ops, M, K, I, schedule):
     from hilbert_pruned_8b_b200.engine.workspace import Workspace
