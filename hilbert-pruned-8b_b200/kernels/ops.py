@@ -186,10 +186,10 @@ class Ops:
         self._retired = []              # outgrown scratch, kept alive for graphs that captured it
         self.use_tcgen05_attention = True   # head size 128 prefill on tcgen05 (else the mma.sync kernel)
         self.use_fast_attention = True  # tests switch this off to compare with the general kernel
-        # One-launch decode attention (rotation + append + splits + combination).  Off: measured
-        # at batch 8 / 8192 tokens it is 5 us per layer SLOWER than the three kernels, because the
-        # small kernels between the big ones are where the next matrix product's CTAs get
-        # resident and request their first weight tiles.
+        # One-launch decode attention (rotation + append + splits + combination).  Off: inside a
+        # replayed graph at batch 8 / 8192 tokens it takes 50.3 us where the three kernels take
+        # 4.0 + 43.5 + 4.2 us (its own round trips are as long as theirs), and at batch 64 it is
+        # 1 % slower.
         self.fuse_decode_attention = False
 
     # ------------------------------------------------------------------ plumbing
