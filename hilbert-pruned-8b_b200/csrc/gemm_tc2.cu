@@ -28,7 +28,10 @@
 #define T2_HALF 128            // tokens loaded by each CTA
 #define T2_STAGE_BYTES (TC_BM * TC_BK * 2 + T2_HALF * TC_BK * 2)     // 32 KB per CTA and stage
 // 6 stages of 32 KB; a 7th (measured) changes nothing, and asking L2 ahead for the weight tiles
-// of later K blocks (cp.async.bulk.prefetch) made the kernel slower
+// of later K blocks (cp.async.bulk.prefetch) made the kernel slower.  Cutting the tiles of the
+// last, partly filled wave over all pairs (float32 partial tiles of 128 KB per CTA in scratch,
+// summed by the last contributor) was measured too: the sums cost more than the idle pairs
+// (o projection at 2048 tokens: 99 us against 73 us), so tiles stay whole.
 #define T2_STAGES(MODE) 6
 
 template <int MODE, int STAGES>
