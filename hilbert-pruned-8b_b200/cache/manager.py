@@ -52,6 +52,7 @@ class Sequence:
     # per group: physical page of each logical page (None: given back, outside the window)
     pages: List[List[Optional[int]]] = field(default_factory=list)
     open: bool = True
+    pages_version: int = 0      # counts the changes of `pages`: who keeps a copy compares this
 
 
 class CacheGroup:
@@ -90,6 +91,7 @@ class CacheManager:
             by_need.setdefault(cache_needs[entry], []).append(entry)
         self.groups: List[CacheGroup] = [
             CacheGroup(need, entries, self.num_pages, device, dtype, allocate) for need, entries in by_need.items()]
+        self._windowed = any(g.need.window is not None for g in self.groups)
         self._group_of_entry: Dict[int, int] = {}
         for gi, g in enumerate(self.groups):
             for e in g.entries:
@@ -144,9 +146,12 @@ class CacheManager:
             if new_len < seq.length:
                 raise ValueError("cache: reserve cannot shrink a sequence (use truncate)")
         # pages a window lets go of are given back first: they may be what the step needs
-        for seq, _ in seqs_and_lengths:
-            self._release_outside_window(seq, seq.length)
+        if self._windowed:
+            for seq, _ in seqs_and_lengths:
+                self._release_outside_window(seq, seq.length)
         need = self._pages_needed(seqs_and_lengths)
+        if not any(need):
+            return
         for gi, g in enumerate(self.groups):
             if need[gi] > g.pool.num_free:
                 raise CacheFull(
@@ -157,6 +162,7 @@ class CacheManager:
                 extra = pages_for(new_len) - len(seq.pages[gi])
                 if extra > 0:
                     seq.pages[gi].extend(g.pool.alloc(extra))
+                    seq.pages_version += 1
 
     def _release_outside_window(self, seq: Sequence, first_new_position: int) -> None:
         for gi, g in enumerate(self.groups):
@@ -172,6 +178,7 @@ class CacheManager:
                 g.pool.free(gone)
                 for i in range(min(dead, len(pages))):
                     pages[i] = None
+                seq.pages_version += 1
 
     def commit(self, seq: Sequence, new_len: int) -> None:
         seq.length = new_len
@@ -191,6 +198,7 @@ class CacheManager:
             tail = seq.pages[gi][keep:]
             g.pool.free([p for p in tail if p is not None])
             del seq.pages[gi][keep:]
+        seq.pages_version += 1
         seq.length = length
 
     # ------------------------------------------------------------------ views

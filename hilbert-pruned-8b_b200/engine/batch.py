@@ -129,3 +129,97 @@ def build_step(entries: List[StepEntry], cache: CacheManager, workspace, device,
         page_tables=[seg(f"pt{gi}", B * w).view(B, w) for gi, w in enumerate(widths)],
         max_new=max(new), max_len=max(lens), is_decode=all(n == 1 for n in new),
         host_new=new, host_len=lens, host_state_slots=[e.seq.state_slot for e in entries])
+
+
+class DecodeMeta:
+    """The metadata of decode steps (one token per sequence, its logits wanted) of a fixed
+    batch size and page-table width, kept from step to step: the same layout and device
+    addresses as ``build_step`` gives with that ``table_width`` and ``meta_name``, but a step
+    only writes what changed since the last one (tokens, positions, lengths, and the page-table
+    row of a sequence whose pages changed).  The host side is a small ring of pinned buffers:
+    a buffer is written again only after the copy that read it has finished."""
+
+    RING = 4
+
+    def __init__(self, batch: int, width: int, cache: CacheManager, workspace, device, meta_name: str):
+        B = self.B = batch
+        self.width = width
+        self.n_groups = len(cache.groups)
+        off: Dict[str, int] = {}
+        cur = 0
+        for name, n in (("tokens", B), ("positions", B), ("tok_seq", B), ("seq_start", B + 1), ("seq_pos0", B),
+                        ("seq_len", B), ("state_slots", B), ("want", B)):
+            off[name] = cur
+            cur = _round4(cur + n)
+        for gi in range(self.n_groups):
+            off[f"pt{gi}"] = cur
+            cur = _round4(cur + B * width)
+        self.off, self.total = off, cur
+        pin = torch.device(device).type == "cuda"
+        self.hosts = [torch.zeros(cur, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        self.arrays = [h.numpy() for h in self.hosts]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * self.RING
+        self.seqs: List[Optional[list]] = [None] * self.RING          # the sequences a buffer was written for
+        self.versions: List[Optional[list]] = [None] * self.RING      # their pages_version then
+        self.turn = 0
+        cap = 1 << max(10, (cur - 1).bit_length())
+        dev = self.dev = workspace.buffer(meta_name, (cap,), torch.int32)[:cur]
+
+        def seg(name: str, n: int) -> torch.Tensor:
+            return dev[off[name]: off[name] + n]
+
+        self.batch = StepBatch(
+            num_tokens=B, num_seqs=B, num_wanted=B, tokens=seg("tokens", B), positions=seg("positions", B),
+            tok_seq=seg("tok_seq", B), seq_start=seg("seq_start", B + 1), seq_pos0=seg("seq_pos0", B),
+            seq_len=seg("seq_len", B), state_slots=seg("state_slots", B), want_rows=seg("want", B),
+            page_tables=[seg(f"pt{gi}", B * width).view(B, width) for gi in range(self.n_groups)],
+            max_new=1, max_len=width * PAGE_TOKENS, is_decode=True, host_new=[1] * B, host_len=[0] * B)
+
+    def _row(self, a, gi: int, b: int, pages) -> None:
+        w = self.width
+        lo = self.off[f"pt{gi}"] + b * w
+        a[lo: lo + w] = -1
+        pages = pages[:w]
+        a[lo: lo + len(pages)] = [(-1 if p is None else p) for p in pages]
+
+    def fill(self, entries: List[StepEntry]) -> StepBatch:
+        B, off = self.B, self.off
+        r = self.turn
+        self.turn = (r + 1) % self.RING
+        if self.events[r] is not None:
+            self.events[r].synchronize()              # the copy that read this buffer has finished
+        a = self.arrays[r]
+        seqs = [e.seq for e in entries]
+        versions = [s.pages_version for s in seqs]
+        old = self.seqs[r]
+        if old is None or len(old) != B or any(x is not y for x, y in zip(old, seqs)):
+            a[off["tok_seq"]: off["tok_seq"] + B] = np.arange(B)
+            a[off["seq_start"]: off["seq_start"] + B + 1] = np.arange(B + 1)
+            a[off["want"]: off["want"] + B] = np.arange(B)
+            a[off["state_slots"]: off["state_slots"] + B] = [s.state_slot for s in seqs]
+            for gi in range(self.n_groups):
+                for b, s in enumerate(seqs):
+                    self._row(a, gi, b, s.pages[gi])
+        else:
+            was = self.versions[r]
+            for b in range(B):
+                if versions[b] != was[b]:
+                    for gi in range(self.n_groups):
+                        self._row(a, gi, b, seqs[b].pages[gi])
+        self.seqs[r], self.versions[r] = seqs, versions
+        pos0 = [s.length for s in seqs]
+        a[off["tokens"]: off["tokens"] + B] = [e.tokens[0] for e in entries]
+        a[off["positions"]: off["positions"] + B] = pos0
+        a[off["seq_pos0"]: off["seq_pos0"] + B] = pos0
+        lens = [p + 1 for p in pos0]
+        a[off["seq_len"]: off["seq_len"] + B] = lens
+        self.dev.copy_(self.hosts[r], non_blocking=True)
+        if self.dev.is_cuda:
+            ev = self.events[r] or torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.dev.device))
+            self.events[r] = ev
+        batch = self.batch
+        batch.shared = {}                  # what parts keep per step (the rotary table) is of the last step
+        batch.host_len = lens
+        batch.host_state_slots = [s.state_slot for s in seqs]
+        return batch

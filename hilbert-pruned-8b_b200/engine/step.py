@@ -19,7 +19,7 @@ from ..cache.manager import CacheManager, Sequence
 from ..config.registry import load_config
 from ..parts.base import BuildContext
 from ..weights.loader import choose_prefix, folder_names, load_tensors
-from .batch import StepBatch, StepEntry, build_step
+from .batch import DecodeMeta, StepBatch, StepEntry, build_step
 from .model import DecoderModel
 from .workspace import Workspace
 
@@ -57,6 +57,7 @@ class Engine:
         # (batch size, page-table width): a step is then one small copy and one graph launch
         self.use_graphs = True
         self._graphs: Dict[tuple, object] = {}
+        self._decode_meta: Dict[tuple, DecodeMeta] = {}
         self.graph_replays = 0
         self.stop_token_ids = list(spec.stop_token_ids)
         self.vocab_size = spec.vocab_size
@@ -108,6 +109,7 @@ class Engine:
             raise ValueError("step: no sequences")
         total = 0
         seen = set()
+        capacity = self.cache.tokens_capacity()
         for e in entries:
             n = len(e.tokens)
             if n == 0:
@@ -117,8 +119,8 @@ class Engine:
             seen.add(id(e.seq))
             if not e.seq.open:
                 raise ValueError(f"step: sequence {e.seq.seq_id} is closed")
-            if e.seq.length + n > self.cache.tokens_capacity():
-                raise ValueError(f"step: {e.seq.length + n} tokens exceed context {self.cache.tokens_capacity()}")
+            if e.seq.length + n > capacity:
+                raise ValueError(f"step: {e.seq.length + n} tokens exceed context {capacity}")
             for t in e.tokens:
                 if not 0 <= int(t) < self.vocab_size:
                     raise ValueError(f"step: token {int(t)} out of range")
@@ -149,9 +151,11 @@ class Engine:
         need = max(pages_for(e.seq.length + 1) for e in entries)
         width = 1 << (need - 1).bit_length()
         key = (B, width)
-        batch = build_step(entries, self.cache, self.workspace, self.device, table_width=width,
-                           meta_name=f"step.meta.decode.{B}.{width}")
-        batch.max_len = width * 64          # kernel launch shapes depend on the bucket only
+        meta = self._decode_meta.get(key)
+        if meta is None:
+            meta = self._decode_meta[key] = DecodeMeta(B, width, self.cache, self.workspace, self.device,
+                                                       f"step.meta.decode.{B}.{width}")
+        batch = meta.fill(entries)          # max_len is the bucket's: kernel launch shapes depend on it only
         batch.tag = f".decode.{B}"
         state = self._graphs.get(key)
         if state is None:

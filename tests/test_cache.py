@@ -139,3 +139,41 @@ def test_random_traffic_never_loses_a_page():
         m.close(s)
     assert m.pages_free() == [40, 40] and m.slots.num_held == 0
     assert pages_for(1) == 1 and pages_for(64) == 1 and pages_for(65) == 2
+
+
+def test_decode_metadata_kept_from_step_to_step_equals_a_fresh_build():
+    """DecodeMeta writes only what changed since the last step (tokens, positions, lengths,
+    page-table rows of sequences whose pages changed); the device array must equal what
+    build_step writes from scratch, step after step: pages added, pages a window gave back,
+    a sequence replaced by another, more steps than the ring of host buffers is long."""
+    from hilbert_pruned_8b_b200.engine.batch import DecodeMeta, StepEntry, build_step
+    from hilbert_pruned_8b_b200.engine.workspace import Workspace
+    m = _manager(max_tokens=4096, window=70)
+    ws_a, ws_b = Workspace(CPU), Workspace(CPU)
+    rnd = random.Random(5)
+    seqs = [m.open() for _ in range(3)]
+    for s, n in zip(seqs, (3, 60, 130)):                 # prompts
+        m.reserve([(s, n)])
+        m.commit(s, n)
+    width = 8
+    meta = DecodeMeta(3, width, m, ws_a, CPU, "meta")
+    for step in range(150):
+        if step == 40:                                   # one sequence ends, another takes its place
+            m.close(seqs[1])
+            seqs[1] = m.open()
+            m.reserve([(seqs[1], 5)])
+            m.commit(seqs[1], 5)
+        entries = [StepEntry(s, [rnd.randrange(1000)], [0]) for s in seqs]
+        m.reserve([(e.seq, e.seq.length + 1) for e in entries])
+        kept = meta.fill(entries)
+        fresh = build_step(entries, m, ws_b, CPU, table_width=width, meta_name="fresh")
+        for name in ("tokens", "positions", "tok_seq", "seq_start", "seq_pos0", "seq_len", "state_slots", "want_rows"):
+            assert torch.equal(getattr(kept, name), getattr(fresh, name)), (step, name)
+        for a, b in zip(kept.page_tables, fresh.page_tables):
+            assert torch.equal(a, b), step
+        assert kept.host_len == fresh.host_len and kept.is_decode and fresh.is_decode
+        assert kept.shared == {}
+        kept.shared["x"] = 1                             # what a part leaves there must not survive the step
+        for e in entries:
+            m.commit(e.seq, e.seq.length + 1)
+    assert any(p is None for p in seqs[2].pages[m.group_of(2)])      # the window did give pages back
