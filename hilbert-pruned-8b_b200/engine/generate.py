@@ -152,20 +152,106 @@ class Generator:
         """The decode phase: one token per live sequence per step until none is live.  ``live``
         maps a result index to a state with ``req``, ``rid``, ``stop``, ``seq`` (whose cache
         holds everything but the token in ``next``) and ``out``.  Every step copies the batch's
-        tokens to the device and the sampled tokens back."""
+        metadata to the device and the sampled tokens back.
+
+        With an engine that takes a step's tokens from the device (``takes_device_tokens``) the
+        loop runs one step ahead: step k+1 is launched on the tokens step k left on the device
+        before the host has read them, so the host's work hides behind the device's.  What
+        the host does not know yet is whether a sequence stopped on a stop token at step k;
+        such a sequence has then run one step for nothing, its result is not affected.  A step
+        is only launched ahead when the same sequences take part as in the step before
+        (nobody ends on its budget or at the context's end)."""
         eng = self.engine
         step_no = first_step
-        while live:
+        ahead = bool(getattr(eng, "takes_device_tokens", False))
+        flying = None          # a step whose sampled tokens the host has not read yet
+        while live or flying is not None:
             t0 = time.perf_counter()
-            order = list(live)
-            entries = [StepEntry(live[i]["seq"], [live[i]["next"]], [0]) for i in order]
-            logits = eng.step(entries)
-            toks = self._sample(logits, [live[i] for i in order], step_no)
+            if flying is not None and self._same_batch_goes_on(flying, live):
+                order = flying["order"]
+                entries = [StepEntry(live[i]["seq"], [0], [0]) for i in order]
+                logits = eng.step(entries, device_tokens=flying["tokens"])
+                nxt = self._launch_sampling(logits, order, live, step_no)
+                self._land(flying, live, results)
+                flying = nxt
+            else:
+                if flying is not None:
+                    self._land(flying, live, results)
+                    flying = None
+                if not live:
+                    self.stats.decode_seconds += time.perf_counter() - t0
+                    break
+                order = list(live)
+                entries = [StepEntry(live[i]["seq"], [live[i]["next"]], [0]) for i in order]
+                logits = eng.step(entries)
+                flying = self._launch_sampling(logits, order, live, step_no)
+                if not ahead or not flying["on_device"]:
+                    self._land(flying, live, results)
+                    flying = None
             self.stats.decode_steps += 1
-            self.stats.decode_tokens += len(order)
-            self._take(order, toks, live, results)
             self.stats.decode_seconds += time.perf_counter() - t0
             step_no += 1
+
+    def _launch_sampling(self, logits, order, live, step_no: int) -> dict:
+        """Samples a step's tokens and starts their copy to the host; the record of a step whose
+        tokens have not been read."""
+        states = [live[i] for i in order]
+        toks = self.sampler.sample(logits, [s["req"].sampling.temperature for s in states],
+                                   [s["req"].sampling.seed for s in states], [s["rid"] for s in states],
+                                   [step_no] * len(states))
+        # the sequences' lengths as of this step: a later step may have grown them when this is read
+        rec = {"order": order, "tokens": toks, "on_device": False, "host": None, "event": None,
+               "lengths": {i: live[i]["seq"].length for i in order}}
+        if hasattr(toks, "is_cuda"):                   # a tensor: the next step can take it as it is
+            import torch
+            if toks.is_cuda:
+                host = self._host_tokens(len(order))
+                host.copy_(toks, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(toks.device))
+                rec.update(on_device=True, host=host, event=ev)
+            else:
+                rec.update(on_device=True, host=toks.clone())
+        return rec
+
+    def _host_tokens(self, n: int):
+        """One of two pinned buffers in turn (a step in flight and the one before it)."""
+        import torch
+        bufs = getattr(self, "_token_buffers", None)
+        if bufs is None or bufs[0].numel() < n:
+            bufs = self._token_buffers = [torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            self._token_turn = 0
+        self._token_turn ^= 1
+        return bufs[self._token_turn][:n]
+
+    def _same_batch_goes_on(self, flying: dict, live: Dict[int, dict]) -> bool:
+        """Whether the step after ``flying`` can be launched before ``flying``'s tokens are read:
+        every sequence of it is still live and will be, whatever token it got, unless that is
+        a stop token."""
+        order = flying["order"]
+        if len(order) != len(live):
+            return False
+        context = self._context()
+        for i in order:
+            st = live.get(i)
+            if st is None:
+                return False
+            if len(st["out"]) + 1 >= st["req"].max_new_tokens or st["seq"].length + 1 > context:
+                return False
+        return True
+
+    def _land(self, flying: dict, live: Dict[int, dict], results) -> None:
+        """Reads a step's tokens and books them (sequences that ended meanwhile are skipped)."""
+        toks = flying["tokens"]
+        if flying["on_device"]:
+            if flying["event"] is not None:
+                flying["event"].synchronize()
+            toks = flying["host"].tolist()
+        else:
+            toks = [int(t) for t in (toks.tolist() if hasattr(toks, "tolist") else toks)]
+        pairs = [(i, t) for i, t in zip(flying["order"], toks) if i in live]
+        self.stats.decode_tokens += len(pairs)
+        self._take([i for i, _ in pairs], [t for _, t in pairs], live, results, flying["lengths"])
 
     def _sample(self, logits, states, step_no: int) -> List[int]:
         toks = self.sampler.sample(logits, [s["req"].sampling.temperature for s in states],
@@ -173,14 +259,15 @@ class Generator:
                                    [step_no] * len(states))
         return [int(t) for t in (toks.tolist() if hasattr(toks, "tolist") else toks)]
 
-    def _take(self, order, toks, live, results) -> None:
-        """Books each sequence's new token and retires the sequences that end with it."""
+    def _take(self, order, toks, live, results, lengths=None) -> None:
+        """Books each sequence's new token and retires the sequences that end with it.
+        ``lengths``: the sequences' lengths when the tokens were sampled (default: now)."""
         for i, tok in zip(order, toks):
             st = live[i]
             st["out"].append(tok)
             st["next"] = tok
-            why = finish_reason(tok, len(st["out"]), st["req"].max_new_tokens, st["seq"].length, self._context(),
-                                st["stop"])
+            length = lengths[i] if lengths is not None else st["seq"].length
+            why = finish_reason(tok, len(st["out"]), st["req"].max_new_tokens, length, self._context(), st["stop"])
             if why is not None:
                 results[i] = GenerationResult(st["rid"], st["out"], why, len(st["req"].prompt))
                 self.engine.close_sequence(st["seq"])

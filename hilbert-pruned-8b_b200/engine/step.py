@@ -128,22 +128,31 @@ class Engine:
         if total > self.max_step_tokens:
             raise ValueError(f"step: {total} tokens exceed the step capacity {self.max_step_tokens}")
 
-    def step(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+    takes_device_tokens = True      # step(entries, device_tokens=...) exists
+
+    def step(self, entries: List[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries' tokens; returns ``[wanted, vocab]`` float32 logits on the device,
         in the order of the entries and of each entry's ``want`` (None if nothing is wanted).
-        The tensor is engine scratch: it is overwritten by the next step."""
+        The tensor is engine scratch: it is overwritten by the next step.  ``device_tokens``
+        (int32 on the device, one per entry, each entry then brings one placeholder token)
+        gives the tokens without the host knowing them: what a sampler just wrote."""
         self.check_entries(entries)
+        if device_tokens is not None and (device_tokens.dtype != torch.int32 or device_tokens.numel() != len(entries)
+                                          or any(len(e.tokens) != 1 for e in entries)):
+            raise ValueError("step: device tokens need one int32 token per entry and one placeholder token each")
         self.cache.reserve([(e.seq, e.seq.length + len(e.tokens)) for e in entries])
         if self.use_graphs and self.model.graph_safe and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits, batch = self._decode_step(entries)
+            logits, batch = self._decode_step(entries, device_tokens)
         else:
             batch = build_step(entries, self.cache, self.workspace, self.device)
+            if device_tokens is not None:
+                batch.tokens.copy_(device_tokens)
             logits = self.model.forward(batch, self.cache)
         for e, new_len in zip(entries, batch.host_len):
             self.cache.commit(e.seq, new_len)
         return logits
 
-    def _decode_step(self, entries: List[StepEntry]):
+    def _decode_step(self, entries: List[StepEntry], device_tokens: Optional[torch.Tensor] = None):
         """A decode step through a captured graph.  The first step of a shape runs eagerly
         (it also allocates every buffer), the second captures, later ones replay."""
         from ..cache.manager import pages_for
@@ -156,6 +165,8 @@ class Engine:
             meta = self._decode_meta[key] = DecodeMeta(B, width, self.cache, self.workspace, self.device,
                                                        f"step.meta.decode.{B}.{width}")
         batch = meta.fill(entries)          # max_len is the bucket's: kernel launch shapes depend on it only
+        if device_tokens is not None:
+            batch.tokens.copy_(device_tokens)       # after the metadata copy, before the graph that reads it
         batch.tag = f".decode.{B}"
         state = self._graphs.get(key)
         if state is None:

@@ -46,6 +46,24 @@ class FakeEngine:
         return torch.stack(rows)
 
 
+class AheadEngine(FakeEngine):
+    """The fake engine with the interface of a step that takes its tokens from a tensor the
+    host has not read (the generation loop then runs one step ahead)."""
+    takes_device_tokens = True
+
+    def __init__(self, max_tokens=1024):
+        super().__init__(max_tokens)
+        self.ahead_steps = 0
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            assert all(list(e.tokens) == [0] for e in entries) and device_tokens.numel() == len(entries)
+            from hilbert_pruned_8b_b200.engine.batch import StepEntry
+            entries = [StepEntry(e.seq, [int(t)], e.want) for e, t in zip(entries, device_tokens.tolist())]
+            self.ahead_steps += 1
+        return super().step(entries)
+
+
 class FakeSampler:
     def __init__(self):
         self.calls = []
@@ -144,3 +162,35 @@ def test_sampling_helpers():
     assert abs(sum(p) - 1) < 1e-12 and p[2] > p[1] > p[0]
     with pytest.raises(ValueError):
         SamplingParams(temperature=-1.0)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_running_one_step_ahead_changes_no_result(seed):
+    """With an engine that takes a step's tokens from the device the loop launches step k+1
+    before it has read step k's tokens.  Results (tokens, finish reasons) are those of the
+    plain loop, for stop tokens, budgets, the context's end and batch after batch; every page
+    comes back."""
+    import random
+    rnd = random.Random(seed)
+    reqs = []
+    for i in range(rnd.randrange(3, 9)):
+        prompt = [rnd.randrange(1, VOCAB) for _ in range(rnd.randrange(1, 40))]
+        reqs.append(GenerationRequest(prompt, max_new_tokens=rnd.randrange(0, 30), sampling=SamplingParams(0.0, 0),
+                                      stop_token_ids=rnd.sample(range(VOCAB), rnd.randrange(0, 6))))
+    plain_engine, ahead_engine = FakeEngine(max_tokens=256), AheadEngine(max_tokens=256)
+    plain = Generator(plain_engine, FakeSampler(), max_batch=4).generate(reqs)
+    ahead = Generator(ahead_engine, FakeSampler(), max_batch=4).generate(reqs)
+    assert [(r.request_id, r.tokens, r.finish_reason) for r in plain] == [(r.request_id, r.tokens, r.finish_reason) for r in ahead]
+    for r, q in zip(ahead, reqs):
+        want, why = expected(q.prompt, q.max_new_tokens, q.stop_token_ids)
+        if r.finish_reason != "context":
+            assert (r.tokens, r.finish_reason) == (want, why if want else "length")
+    assert ahead_engine.ahead_steps > 0
+    assert min(ahead_engine.cache.pages_free()) == ahead_engine.cache.num_pages
+
+
+def test_running_ahead_stops_at_the_context_end_as_the_plain_loop_does():
+    reqs = [GenerationRequest([3, 4, 5], max_new_tokens=500, sampling=SamplingParams(0.0, 0), stop_token_ids=[])]
+    a = Generator(FakeEngine(max_tokens=64), FakeSampler(), max_batch=2).generate(reqs)
+    b = Generator(AheadEngine(max_tokens=64), FakeSampler(), max_batch=2).generate(reqs)
+    assert a[0].finish_reason == b[0].finish_reason == "context" and a[0].tokens == b[0].tokens
