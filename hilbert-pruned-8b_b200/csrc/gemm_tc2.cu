@@ -194,12 +194,38 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const uint32_t lane_addr = tmem_base + buf * T2_TOKENS + ((uint32_t)(q * 32) << 16);
             const int m0 = (t % p.tiles_m) * T2_TOKENS;
             const int n0 = (t / p.tiles_m) * (2 * FEAT) + (int)rank * FEAT;
+            if (MODE == TC_ADD_F32) {
+                // residual add: 64 tokens at a time, all 64 old values requested before the first
+                // store (16 at a time the loads' round trips, 16 per tile, outlast a short K loop)
+                const int f = n0 + row;
 #pragma unroll 1
-            for (int c = 0; c < T2_TOKENS; c += 16) {
-                if (m0 + c >= p.M) break;
-                float v[16];
-                tmem_ld16(lane_addr + c, v);
-                tc_emit_chunk<MODE>(p, m0, n0, c, v, xchg, q, row, et);
+                for (int c = 0; c < T2_TOKENS; c += 64) {
+                    if (m0 + c >= p.M) break;
+                    float v[4][16], r[4][16];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) tmem_ld16(lane_addr + c + 16 * u, v[u]);
+                    if (f < p.N) {
+                        float* po = (float*)p.out + (size_t)(m0 + c) * p.ldc + f;
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                r[u][j] = (m0 + c + 16 * u + j < p.M) ? __ldcg(po + (size_t)(16 * u + j) * p.ldc) : 0.0f;
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (m0 + c + 16 * u + j < p.M) po[(size_t)(16 * u + j) * p.ldc] = r[u][j] + v[u][j];
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < T2_TOKENS; c += 16) {
+                    if (m0 + c >= p.M) break;
+                    float v[16];
+                    tmem_ld16(lane_addr + c, v);
+                    tc_emit_chunk<MODE>(p, m0, n0, c, v, xchg, q, row, et);
+                }
             }
             tc_fence_before();
             mbar_arrive_cluster(lead_acce0 + 8 * buf);
