@@ -1,13 +1,14 @@
-// Prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head size 128:
+// Prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head size 64 or 128:
 // flash-style, causal, grouped-query, over the paged bfloat16 cache, for batches of sequences
 // with unequal numbers of new tokens.
 //
 // One CTA = 128 consecutive new tokens of one sequence x one query head.  The 128 query rows
 // are the 128 lanes of tensor memory.  Keys and values come in tiles of 128 keys (two pages).
 //   warp 0     TMA producer: the query tile once, then K tiles and V tiles (three stages of
-//              32 KB each, freed separately: a K tile right after S_j, a V tile after O += P_j V_j)
+//              128 keys x head size each, freed separately: a K tile right after S_j, a V tile
+//              after O += P_j V_j)
 //   warp 1     owns tensor memory; one thread issues the MMAs:
-//                S_j = Q K_j^T      (operands in shared memory, K-major, 8 x K16)
+//                S_j = Q K_j^T      (operands in shared memory, K-major, head size / 16 steps)
 //                O  += P_j V_j      (P_j from tensor memory, V_j in shared memory as stored:
 //                                    keys are rows, an MN-major B operand)
 //   warps 2-9  softmax: two threads per query row (64 key columns each): they read S_j from
@@ -25,9 +26,8 @@
 
 #define FA_ROWS 128
 #define FA_KEYS 128
-#define FA_HD 128
 #define FA_HALF_BYTES (128 * 64 * 2)                 // 128 rows x 64 elements: one swizzle-wide sub-tile
-#define FA_TILE_BYTES (2 * FA_HALF_BYTES)            // 128 x 128 bf16
+#define FA_TILE_BYTES(HD) ((HD) / 64 * FA_HALF_BYTES) // 128 rows x head size, bf16
 #define FA_STAGES 3
 #define FA_LOG2E 1.4426950408889634f
 #define FA_RESCALE_THRESHOLD 8.0f
@@ -115,6 +115,7 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t l
     return d;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int pt_width,
@@ -123,13 +124,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        int* __restrict__ error_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    // [Q 32 KB][K stages 3 x 32 KB][V stages 3 x 32 KB][barriers]
-    uint64_t* bars = (uint64_t*)(smem + FA_TILE_BYTES + FA_STAGES * 2 * FA_TILE_BYTES);
+    // [Q tile][K stages 3 x tile][V stages 3 x tile][barriers]; a tile is 128 rows x HD
+    constexpr int TILE = FA_TILE_BYTES(HD);
+    constexpr int HALVES = HD / 64;                      // swizzle-wide sub-tiles per tile
+    uint64_t* bars = (uint64_t*)(smem + TILE + FA_STAGES * 2 * TILE);
     uint32_t* tmem_slot = (uint32_t*)(bars + 18);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     float* xrow = (float*)(tmem_slot + 4);                    // [2 halves][128 rows]: row maxima, at the end row sums
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t k_smem = smem_base + FA_TILE_BYTES, v_smem = k_smem + FA_STAGES * FA_TILE_BYTES;
+    const uint32_t k_smem = smem_base + TILE, v_smem = k_smem + FA_STAGES * TILE;
     const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), k_empty0 = smem_u32(bars + 4);
     const uint32_t v_full0 = smem_u32(bars + 7), v_empty0 = smem_u32(bars + 10);
     const uint32_t s_full0 = smem_u32(bars + 13), p_full0 = smem_u32(bars + 15), pv_done = smem_u32(bars + 17);
@@ -184,18 +187,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0 && n_it > 0) {
             const int* pt = page_table + (size_t)b * pt_width;
-            mbar_expect_tx(q_full, FA_TILE_BYTES);
-            tma_load_2d(smem_base, &map_q, q_full, head * FA_HD, t_begin + row_base);
-            tma_load_2d(smem_base + FA_HALF_BYTES, &map_q, q_full, head * FA_HD + 64, t_begin + row_base);
+            mbar_expect_tx(q_full, TILE);
+            for (int half = 0; half < HALVES; half++)
+                tma_load_2d(smem_base + half * FA_HALF_BYTES, &map_q, q_full, head * HD + half * 64, t_begin + row_base);
             // K tiles run ahead of V tiles: a K stage is free as soon as its scores exist
             auto load_tile = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int it) {
-                mbar_expect_tx(bar, FA_TILE_BYTES);
+                mbar_expect_tx(bar, TILE);
                 for (int pg = 0; pg < 2; pg++) {
                     const int pi = (jt0 + it) * 2 + pg;
                     int page = pi < pt_width ? pt[pi] : -1;
                     if (page < 0 || page >= n_pages) page = 0;      // masked keys; never read outside the cache
                     const int row = (page * nkv + g) * HB_PAGE_TOKENS;
-                    for (int half = 0; half < 2; half++)
+                    for (int half = 0; half < HALVES; half++)
                         tma_load_2d(dst + half * FA_HALF_BYTES + pg * (FA_HALF_BYTES / 2), map, bar, half * 64, row);
                 }
             };
@@ -211,7 +214,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         alive = false;
                         break;
                     }
-                    load_tile(k_smem + s * FA_TILE_BYTES, &map_k, k_full0 + 8 * s, ik);
+                    load_tile(k_smem + s * TILE, &map_k, k_full0 + 8 * s, ik);
                     k_issued = ik + 1;
                 }
                 if (iv >= 0) {
@@ -222,7 +225,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         alive = false;
                         break;
                     }
-                    load_tile(v_smem + s * FA_TILE_BYTES, &map_v, v_full0 + 8 * s, iv);
+                    load_tile(v_smem + s * TILE, &map_v, v_full0 + 8 * s, iv);
                     v_issued = iv + 1;
                 }
             }
@@ -236,7 +239,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0 && n_it > 0) {
             constexpr uint32_t idesc_qk = instr_desc_bf16_mn(128, FA_KEYS);
-            constexpr uint32_t idesc_pv = instr_desc_bf16_mn(128, FA_HD) | (1u << 16);        // B is MN-major
+            constexpr uint32_t idesc_pv = instr_desc_bf16_mn(128, HD) | (1u << 16);           // B is MN-major
             bool alive = mbar_wait(q_full, 0);
             if (!alive) { atomicExch(error_flag, 24); *abort_flag = 1; }
             auto issue_qk = [&](int it) {
@@ -248,9 +251,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     return;
                 }
                 tc_fence_after();
-                const uint32_t kst = k_smem + s * FA_TILE_BYTES;
+                const uint32_t kst = k_smem + s * TILE;
 #pragma unroll
-                for (int kk = 0; kk < FA_HD / 16; kk++) {
+                for (int kk = 0; kk < HD / 16; kk++) {
                     const uint32_t off = (kk >> 2) * FA_HALF_BYTES + (kk & 3) * 32;
                     umma_bf16(tmem_base + sb * 128, smem_desc_sw128(smem_base + off), smem_desc_sw128(kst + off), idesc_qk, kk ? 1u : 0u);
                 }
@@ -274,7 +277,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     break;
                 }
                 tc_fence_after();
-                const uint32_t vst = v_smem + sv * FA_TILE_BYTES;
+                const uint32_t vst = v_smem + sv * TILE;
 #pragma unroll
                 for (int kk = 0; kk < FA_KEYS / 16; kk++)
                     umma_bf16_ts(tm_o, tmem_base + s * 128 + kk * 8, smem_desc_mn_sw128(vst + kk * 16 * 128, FA_HALF_BYTES, 1024),
@@ -286,7 +289,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     } else if (n_it > 0) {
         // ---------------------------------------------------------------- softmax and output
         const int q = warp & 3, r = q * 32 + lane;            // query row of this thread = TMEM lane
-        const int hf = (warp - 2) >> 2;                       // which 64 key columns (and output columns) of the row
+        const int hf = (warp - 2) >> 2;                       // which 64 key columns (and which half of the output columns) of the row
+        constexpr int OC = HD / 2;                            // output columns per thread: 32 or 64
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         const int qpos = first_pos + r;
         const int lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
@@ -345,12 +349,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     m_run = m_new;
                     l *= corr;
 #pragma unroll 1
-                    for (int c = 0; c < 2; c++) {
+                    for (int c = 0; c < OC / 32; c++) {
                         float v[32];
-                        tmem_ld32(tm_o + lane_base + hf * 64 + c * 32, v);
+                        tmem_ld32(tm_o + lane_base + hf * OC + c * 32, v);
 #pragma unroll
                         for (int e = 0; e < 32; e++) v[e] *= corr;
-                        tmem_st32(tm_o + lane_base + hf * 64 + c * 32, v);
+                        tmem_st32(tm_o + lane_base + hf * OC + c * 32, v);
                     }
                     tmem_wait_st();
                 }
@@ -387,11 +391,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_after();
             const float lt = xrow[r] + xrow[128 + r];
             const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
-            bf16* dst = out + (size_t)(t_begin + row_base + r) * out_stride + (size_t)head * FA_HD + hf * 64;
+            bf16* dst = out + (size_t)(t_begin + row_base + r) * out_stride + (size_t)head * HD + hf * OC;
 #pragma unroll 1
-            for (int c = 0; c < 2; c++) {
+            for (int c = 0; c < OC / 32; c++) {
                 float v[32];
-                tmem_ld32(tm_o + lane_base + hf * 64 + c * 32, v);
+                tmem_ld32(tm_o + lane_base + hf * OC + c * 32, v);
                 if (valid) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
@@ -415,12 +419,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 extern "C" int hb_attention_prefill_tc_supported(int n_heads, int n_kv_heads, int head_dim) {
-    return head_dim == FA_HD && n_kv_heads > 0 && n_heads % n_kv_heads == 0;
+    return (head_dim == 64 || head_dim == 128) && n_kv_heads > 0 && n_heads % n_kv_heads == 0;
+}
+
+template <int HD>
+static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, int pt_width,
+                             const int* seq_start, const int* seq_pos0, void* out, long long out_stride, int n_seqs, int q_blocks,
+                             int n_heads, int n_kv_heads, float scale, int window, int n_pages, int* error_flag, cudaStream_t stream) {
+    constexpr int TILE = FA_TILE_BYTES(HD);
+    constexpr int SMEM = TILE + FA_STAGES * 2 * TILE + 18 * 8 + 16 + 2 * 128 * 4 + 1024;
+    static_assert(SMEM <= 227 * 1024, "attention tiles do not fit shared memory");
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return hb_fail("attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    cudaError_t e = hb_launch(attn_prefill_tc_kernel<HD>, dim3(q_blocks, n_heads), dim3(FA_THREADS), SMEM, stream, mq, mk, mv,
+                              page_table, pt_width, seq_start, seq_pos0, (bf16*)out, out_stride, n_seqs, n_heads, n_kv_heads,
+                              scale * FA_LOG2E, window, n_pages, error_flag);
+    if (e != cudaSuccess) return hb_fail("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
+    return hb_check_launch("attention_prefill_tc");
 }
 
 // Tensor map over rows of `cols` bfloat16 with row stride `ld`: boxes of 64 columns x box_rows.
-// q: [tokens, q_stride] (head j at columns [j*128, (j+1)*128)); k_cache / v_cache: one layer,
-// [n_pages][n_kv_heads][64][128]; seq_start / seq_pos0 as for hb_attention_prefill; q_blocks =
+// q: [tokens, q_stride] (head j at columns [j*hd, (j+1)*hd)); k_cache / v_cache: one layer,
+// [n_pages][n_kv_heads][64][hd]; seq_start / seq_pos0 as for hb_attention_prefill; q_blocks =
 // sum over sequences of ceil(new tokens / 128).
 extern "C" int hb_attention_prefill_tc(const void* q, long long q_stride, long long n_tokens, const void* k_cache,
                                        const void* v_cache, const int* page_table, int pt_width, const int* seq_start,
@@ -429,7 +453,7 @@ extern "C" int hb_attention_prefill_tc(const void* q, long long q_stride, long l
                                        int* error_flag, void* stream) {
     if (n_seqs == 0 || q_blocks == 0) return 0;
     HB_REQUIRE(hb_attention_prefill_tc_supported(n_heads, n_kv_heads, head_dim),
-               "attention_prefill_tc: head size %d is not built (128)", head_dim);
+               "attention_prefill_tc: head size %d is not built (64, 128)", head_dim);
     HB_REQUIRE(n_heads <= 65535 && error_flag != nullptr, "attention_prefill_tc: bad sizes");
     HB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0, "attention_prefill_tc: queries must have 16-byte aligned rows");
     HB_REQUIRE(out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0, "attention_prefill_tc: output must have 16-byte aligned rows");
@@ -439,17 +463,10 @@ extern "C" int hb_attention_prefill_tc(const void* q, long long q_stride, long l
     if (tc_make_map(&mq, q, n_tokens, (long long)n_heads * head_dim, q_stride, FA_ROWS)) return 1;
     if (tc_make_map(&mk, k_cache, cache_rows, head_dim, head_dim, HB_PAGE_TOKENS)) return 1;
     if (tc_make_map(&mv, v_cache, cache_rows, head_dim, head_dim, HB_PAGE_TOKENS)) return 1;
-    constexpr int SMEM = FA_TILE_BYTES + FA_STAGES * 2 * FA_TILE_BYTES + 18 * 8 + 16 + 2 * 128 * 4 + 1024;
-    static_assert(SMEM <= 227 * 1024, "attention tiles do not fit shared memory");
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return hb_fail("attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
-        attr_set = true;
-    }
-    cudaError_t e = hb_launch(attn_prefill_tc_kernel, dim3(q_blocks, n_heads), dim3(FA_THREADS), SMEM, (cudaStream_t)stream, mq, mk, mv,
-                              page_table, pt_width, seq_start, seq_pos0, (bf16*)out, out_stride, n_seqs, n_heads, n_kv_heads,
-                              scale * FA_LOG2E, window, n_pages, error_flag);
-    if (e != cudaSuccess) return hb_fail("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
-    return hb_check_launch("attention_prefill_tc");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (head_dim == 128)
+        return launch_prefill_tc<128>(mq, mk, mv, page_table, pt_width, seq_start, seq_pos0, out, out_stride, n_seqs, q_blocks, n_heads,
+                                      n_kv_heads, scale, window, n_pages, error_flag, st);
+    return launch_prefill_tc<64>(mq, mk, mv, page_table, pt_width, seq_start, seq_pos0, out, out_stride, n_seqs, q_blocks, n_heads,
+                                 n_kv_heads, scale, window, n_pages, error_flag, st);
 }

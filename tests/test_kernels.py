@@ -472,7 +472,16 @@ def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
         for splits in ((None, 1, 3) if step.is_decode else (None,)):
             out = torch.full((T, nh * hd), 9.0, device=DEV, dtype=dtype)
             ops.attention(qkv, nh, nkv, hd, cache, step, out, scale, window, splits=splits)
+            ops.check_errors()
             assert _rel(out.view(T, nh, hd).cpu(), ref) < 2 ** -7, f"splits={splits} decode={step.is_decode}"
+        if not step.is_decode:                 # the tcgen05 kernel ran above; now the mma.sync one
+            ops.use_tcgen05_attention = False
+            try:
+                other = torch.full((T, nh * hd), 9.0, device=DEV, dtype=dtype)
+                ops.attention(qkv, nh, nkv, hd, cache, step, other, scale, window)
+            finally:
+                ops.use_tcgen05_attention = True
+            assert _rel(other.view(T, nh, hd).cpu(), ref) < 2 ** -7
         ops.use_fast_attention = False
         try:
             gen = torch.empty(T, nh * hd, device=DEV, dtype=dtype)
