@@ -31,6 +31,7 @@ int hb_gemm_general(const void* a, int a_dtype, long long lda, const void* w, in
 int hb_gemm_tc_token_tile(int M);
 long long hb_gemm_tc_scratch_floats(int M, int N, int K, int mode, int schedule);
 long long hb_gemm_tc_tiles(int M, int N, int mode);
+int hb_gemm_tc_resident_clusters(int mode, int size);
 int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,
                int M, int N, int K, int mode, int up_row0, int schedule, float* partials, long long partials_capacity,
                int* tile_counters, long long counters_capacity, int* error_flag, int packed, void* stream);

@@ -543,9 +543,11 @@ static bool clusters_enabled() {
 // The work split of a product: tiles, grid, stream-K or not, scratch.  schedule: 0 automatic,
 // 1 whole tiles round-robin, 2 stream-K, 3 cut tiles first and whole tiles after.
 struct TcPlan {
-    int bn, feat, tiles_m, tiles_n, kb_total, grid, stream_k, max_slots, split;
+    int bn, feat, tiles_m, tiles_n, kb_total, grid, stream_k, max_slots, split, cluster;
     long long scratch_floats, tiles;
 };
+// whether `tiles` clusters of `size` CTAs of the cluster variant can be resident at once
+static bool clusters_fit_mode(int mode, int size, long long tiles);
 
 static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
     TcPlan pl;
@@ -559,6 +561,7 @@ static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
     const long long units = pl.tiles * pl.kb_total;
     pl.stream_k = schedule == 2 || (schedule == 0 && pl.tiles_m == 1 && pl.bn <= 64);
     pl.split = 1;
+    pl.cluster = 0;
     if (schedule == 3 || (schedule == 0 && pl.stream_k && pl.tiles >= sms)) {
         // As many tiles as SMs or more: tiles % SMs tiles are cut over all CTAs first, then
         // every CTA takes tiles / SMs whole tiles: the sums of the cut tiles overlap the whole
@@ -577,14 +580,24 @@ static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
         long long g = units / 4;                  // at least four K blocks per CTA
         g = g < 1 ? 1 : g > sms ? sms : g;
         if (schedule == 0 && pl.tiles < sms) {
-            const long long split = sms / pl.tiles;
-            // (four where the K ranges of a tile can be a cluster, which sums in shared memory)
-            const int fixed = (pl.bn == 16 && split >= 2 && split <= TC_MAX_CLUSTER && clusters_enabled()) ? 4 : 6;
-            const long long aligned_cost = (pl.kb_total + split - 1) / split + fixed;
+            long long split = sms / pl.tiles;
+            // The K ranges of a tile as one cluster, which sums in shared memory (fixed time of
+            // about four K blocks instead of six), if all clusters can be resident at once;
+            // up to a fifth fewer ranges than SMs allow are accepted for that.
+            bool cluster = false;
+            if (pl.bn == 16 && clusters_enabled())
+                for (long long s = split < TC_MAX_CLUSTER ? split : TC_MAX_CLUSTER; s >= 2 && s * 5 >= split * 4; s--)
+                    if (pl.kb_total / s >= 4 && clusters_fit_mode(mode, (int)s, pl.tiles)) {
+                        split = s;
+                        cluster = true;
+                        break;
+                    }
+            const long long aligned_cost = (pl.kb_total + split - 1) / split + (cluster ? 4 : 6);
             const long long stream_cost = units / g + 12;
             if (aligned_cost <= stream_cost && pl.kb_total / split >= 4) {
                 pl.stream_k = 2;
                 pl.split = (int)split;
+                pl.cluster = cluster ? 1 : 0;
                 g = pl.tiles * split;
             }
         }
@@ -670,6 +683,27 @@ static bool clusters_fit(int size, long long tiles) {
     return cached[size] >= tiles;
 }
 
+// How many clusters of `size` CTAs of the cluster variant can be resident at once (diagnostics
+// and tests; 0 if the size is not built).
+extern "C" int hb_gemm_tc_resident_clusters(int mode, int size) {
+    if (size < 2 || size > TC_MAX_CLUSTER) return 0;
+    switch (mode & 3) {
+        case TC_STORE_BF16: return TcClusterLaunch<TC_STORE_BF16>::resident_clusters(size);
+        case TC_STORE_F32: return TcClusterLaunch<TC_STORE_F32>::resident_clusters(size);
+        case TC_ADD_F32: return TcClusterLaunch<TC_ADD_F32>::resident_clusters(size);
+        default: return TcClusterLaunch<TC_SWIGLU_BF16>::resident_clusters(size);
+    }
+}
+
+static bool clusters_fit_mode(int mode, int size, long long tiles) {
+    switch (mode & 3) {
+        case TC_STORE_BF16: return clusters_fit<TC_STORE_BF16>(size, tiles);
+        case TC_STORE_F32: return clusters_fit<TC_STORE_F32>(size, tiles);
+        case TC_ADD_F32: return clusters_fit<TC_ADD_F32>(size, tiles);
+        default: return clusters_fit<TC_SWIGLU_BF16>(size, tiles);
+    }
+}
+
 template <int MODE>
 static int dispatch_bn(int bn, bool cluster, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
     if (cluster) return TcClusterLaunch<MODE>::launch(mw, ma, prm, grid, s);
@@ -729,17 +763,7 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
     prm.counters = tile_counters;
     prm.error_flag = error_flag;
     prm.packed = packed ? 1 : 0;
-    // every tile cut into 2..8 equal K ranges, 16 tokens: the ranges' CTAs as one cluster, if
-    // all clusters can be resident at once (HILBERT_B200_CLUSTER=0: never)
-    bool cluster = pl.stream_k == 2 && pl.bn == 16 && pl.split >= 2 && pl.split <= TC_MAX_CLUSTER && clusters_enabled();
-    if (cluster) {
-        switch (mode) {
-            case TC_STORE_BF16: cluster = clusters_fit<TC_STORE_BF16>(pl.split, pl.tiles); break;
-            case TC_STORE_F32: cluster = clusters_fit<TC_STORE_F32>(pl.split, pl.tiles); break;
-            case TC_ADD_F32: cluster = clusters_fit<TC_ADD_F32>(pl.split, pl.tiles); break;
-            default: cluster = clusters_fit<TC_SWIGLU_BF16>(pl.split, pl.tiles); break;
-        }
-    }
+    const bool cluster = pl.cluster != 0;      // the K ranges of a tile are one cluster (make_plan)
     prm.cluster = cluster ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     switch (mode) {

@@ -75,6 +75,7 @@ def load_library():
         lib.hb_gemm_tc_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int, _c_int]
         lib.hb_gemm_tc_scratch_floats.restype = _c_ll
         lib.hb_gemm_tc_tiles.argtypes, lib.hb_gemm_tc_tiles.restype = [_c_int, _c_int, _c_int], _c_ll
+        lib.hb_gemm_tc_resident_clusters.argtypes, lib.hb_gemm_tc_resident_clusters.restype = [_c_int, _c_int], _c_int
         lib.hb_gemm_tc2_wanted.argtypes, lib.hb_gemm_tc2_wanted.restype = [_c_int, _c_int, _c_int], _c_int
         lib.hb_gemm_tc2_resident_pairs.argtypes, lib.hb_gemm_tc2_resident_pairs.restype = [_c_int], _c_int
         for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported", "hb_attention_prefill_tc_supported"):

@@ -277,6 +277,7 @@ def test_gemm_tensor_core_cluster_split(ops, M, N, K):
     cluster and sum their partial tiles through the first CTA's shared memory (the last size
     leaves one CTA of each cluster without work).  Every epilogue, twice (same bits)."""
     torch.manual_seed(34)
+    assert ops.lib.hb_gemm_tc_resident_clusters(2, 4) >= 32, "clusters of 4 do not fit: the cluster variant is not what runs here"
     a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
     ref = a.double() @ w.double().t()
     res = torch.randn(M, N, device=DEV)
