@@ -24,11 +24,16 @@
 // so[4][16][HD] unnormalised outputs, sm[4][16] maxima (log2 domain), sl[4][16] sums.
 // `after_prologue` runs once the first pages are requested and before any of them is used: the
 // place to build the query fragments (and to append a new key) while the loads are in flight.
+// `fresh_page` (>= 0): the logical page the kernel in front writes to; the pages before it are
+// requested BEFORE griddepcontrol.wait (they hold older tokens only, and the page table and
+// the positions come from a copy that finished before the step's first kernel), the wait
+// happens before the first request of that page, or after the prologue.  -1: the caller
+// has waited already.
 template <int HD, typename F>
 __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], const bf16* kc, const bf16* vc,
                                                   const int* __restrict__ pt, int n_pages, int nkv, int g, int lo,
                                                   int len, int p_begin, int p_end, float scale_log2e, uint8_t* smem,
-                                                  F&& after_prologue) {
+                                                  F&& after_prologue, int fresh_page = -1) {
     constexpr int ROW_BYTES = HD * 2;
     constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;        // one page of K (or V) of one kv head
     constexpr int CHUNKS = ROW_BYTES / 16;
@@ -58,8 +63,16 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
     for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
+    bool waited = fresh_page < 0;
 #pragma unroll
-    for (int s = 0; s < AD_STAGES - 1; s++) load_page(s, p_begin + s);
+    for (int s = 0; s < AD_STAGES - 1; s++) {
+        if (!waited && p_begin + s >= fresh_page) {
+            pdl_wait();
+            waited = true;
+        }
+        load_page(s, p_begin + s);
+    }
+    if (!waited) pdl_wait();
     after_prologue();
 
     for (int pi = p_begin; pi < p_end; pi++) {
@@ -169,7 +182,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, float scale_log2e,
                    int window, int pages_per_split, int n_pages) {
     pdl_trigger();
-    pdl_wait();
+    // positions and page table come from the step's metadata copy, which finished before the
+    // step's first kernel: they may be read before the wait for the kernel in front
     constexpr int KSTEPS = HD / 16;
     extern __shared__ __align__(128) uint8_t smem[];
     const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z, S = gridDim.x;
@@ -182,6 +196,7 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
     const int* pt = page_table + (size_t)b * pt_width;
 
     if (p_begin >= p_end) {                       // nothing to read: an empty partial
+        pdl_wait();                               // the scratch may still be read by the step before
         if (tid < G) {
             float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
             ml[0] = -INFINITY;
@@ -190,22 +205,24 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
         return;
     }
 
-    // query fragments: row r of the tile is head g*G + r (rows >= G are zero)
+    // query fragments: row r of the tile is head g*G + r (rows >= G are zero); read after the
+    // wait for the kernel in front (which rotated them), while the first pages are in flight.
+    // ld.global.cg, not a plain load: the pointer is const __restrict__, and a plain load from
+    // it counts as a load from memory that never changes, which the compiler may move above
+    // the wait (it did: the queries of the layer before came back).
     uint32_t qf[KSTEPS][4];
-    {
+    decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&] {
         const int r0 = lane >> 2, c = (lane & 3) * 2;
-        const bf16* q0 = q + (size_t)b * q_stride + (size_t)(g * G + r0) * HD;
-        const bf16* q1 = q0 + (size_t)8 * HD;
+        const unsigned int* q0 = reinterpret_cast<const unsigned int*>(q + (size_t)b * q_stride + (size_t)(g * G + r0) * HD + c);
+        const unsigned int* q1 = q0 + 8 * HD / 2;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) {
-            qf[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c) : 0u;
-            qf[ks][1] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c) : 0u;
-            qf[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + c + 8) : 0u;
-            qf[ks][3] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + c + 8) : 0u;
+            qf[ks][0] = r0 < G ? __ldcg(q0 + ks * 8) : 0u;
+            qf[ks][1] = r0 + 8 < G ? __ldcg(q1 + ks * 8) : 0u;
+            qf[ks][2] = r0 < G ? __ldcg(q0 + ks * 8 + 4) : 0u;
+            qf[ks][3] = r0 + 8 < G ? __ldcg(q1 + ks * 8 + 4) : 0u;
         }
-    }
-
-    decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [] {});
+    }, (len - 1) / HB_PAGE_TOKENS);
     const float* so = reinterpret_cast<const float*>(smem);
     const float* sm = so + 4 * 16 * HD;
     const float* sl = sm + 4 * 16;
@@ -259,6 +276,8 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                          float scale_log2e, int window, int pages_per_split, int n_pages, int append) {
     pdl_trigger();
     pdl_wait();
+    qkv = pdl_fresh(qkv);
+    table = pdl_fresh(table);
     constexpr int KSTEPS = HD / 16;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
@@ -401,6 +420,8 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
                                            TO* __restrict__ out, long long out_stride, int nh, int hd, int S) {
     pdl_trigger();
     pdl_wait();
+    part_o = pdl_fresh(part_o);
+    part_ml = pdl_fresh(part_ml);
     const int b = blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)b * nh + head) * S;
     float M = -INFINITY;

@@ -21,6 +21,9 @@ attention_general_kernel(const TQ* __restrict__ q, long long q_stride, const TC*
                          long long out_stride, int nh, int nkv, int hd, float scale, int window) {
     pdl_trigger();
     pdl_wait();
+    q = pdl_fresh(q);
+    k_cache = pdl_fresh(k_cache);
+    v_cache = pdl_fresh(v_cache);
     __shared__ float qs[AG_MAX_HD];
     __shared__ float ps[AG_THREADS];
     __shared__ int pages[AG_THREADS / HB_PAGE_TOKENS + 2];

@@ -26,6 +26,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
                     int nkv, float scale_log2e, int window, int n_pages) {
     pdl_trigger();
     pdl_wait();
+    q = pdl_fresh(q);
+    kc = pdl_fresh(kc);
+    vc = pdl_fresh(vc);
     constexpr int ROW_BYTES = HD * 2;
     constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;
     constexpr int CHUNKS = ROW_BYTES / 16;

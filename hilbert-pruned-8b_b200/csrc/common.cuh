@@ -124,6 +124,16 @@ static TlRegistrar g_tl_registrar;
 }  // namespace
 #endif
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// A pointer to memory that an earlier kernel of the step wrote goes through pdl_fresh() after
+// pdl_wait().  A plain load through a `const T* __restrict__` parameter counts as a load from
+// memory that never changes: the compiler may move it above the wait, whose "memory" clobber
+// does not hold it back (seen: a kernel read its queries before the kernel in front had
+// written them).  The pointer that comes out of the asm statement carries no such promise.
+template <typename T>
+__device__ __forceinline__ T* pdl_fresh(T* p) {
+    asm volatile("" : "+l"(p)::"memory");
+    return p;
+}
 
 bool hb_pdl_enabled();
 

@@ -43,6 +43,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_trigger();
     pdl_wait();
+    x = pdl_fresh(x);
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -66,6 +67,7 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, fl
                     TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_trigger();
     pdl_wait();
+    x = pdl_fresh(x);
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -143,6 +145,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, long long in_stride, 
                                 long long out_stride, int inter) {
     pdl_trigger();
     pdl_wait();
+    gu = pdl_fresh(gu);
     const int t = blockIdx.x;
     const int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= inter) return;
@@ -208,6 +211,7 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
                       const int* __restrict__ positions, int n_pages, int append) {
     pdl_trigger();
     pdl_wait();
+    table = pdl_fresh(table);          // written by the rope table kernel of this step
     const int t = blockIdx.x;
     const int half = rot >> 1;
     T* row = qkv + (size_t)t * qkv_stride;
@@ -277,6 +281,7 @@ rope_kv_append_vec_kernel(bf16* __restrict__ qkv, long long qkv_stride, const fl
                           const int* __restrict__ positions, int n_pages, int append) {
     pdl_trigger();
     pdl_wait();
+    table = pdl_fresh(table);
     const int t = blockIdx.x;
     const int half = rot >> 1, hv = half >> 3;                 // 8-element pieces per half head
     bf16* row = qkv + (size_t)t * qkv_stride;

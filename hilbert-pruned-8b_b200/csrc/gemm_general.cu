@@ -23,6 +23,7 @@ gemm_general_kernel(const TA* __restrict__ A, long long lda, const TW* __restric
                     TO* __restrict__ C, long long ldc, int M, int N, int K, int accumulate) {
     pdl_trigger();
     pdl_wait();
+    A = pdl_fresh(A);
     __shared__ float As[GB_K][GB_M + 4];
     __shared__ float Ws[GB_K][GB_N + 4];
     const int tid = threadIdx.x;

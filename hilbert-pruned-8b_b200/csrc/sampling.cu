@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(SM_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ out, int vocab) {
     pdl_trigger();
     pdl_wait();
+    logits = pdl_fresh(logits);
     __shared__ float sval[33];
     __shared__ int sidx[33];
     int idx;
@@ -106,6 +107,7 @@ sample_kernel(const float* __restrict__ logits, long long stride, const float* _
               const long long* __restrict__ steps, int* __restrict__ out, int vocab) {
     pdl_trigger();
     pdl_wait();
+    logits = pdl_fresh(logits);
     __shared__ float sval[33];
     __shared__ int sidx[33];
     __shared__ float prefix[SM_THREADS];
