@@ -210,15 +210,23 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
                       const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
                       const int* __restrict__ positions, int n_pages, int append) {
     pdl_trigger();
-    pdl_wait();
-    table = pdl_fresh(table);          // written by the rope table kernel of this step
     const int t = blockIdx.x;
     const int half = rot >> 1;
+    // positions and page table are the step's metadata, copied before its first kernel ran:
+    // the block that appends looks its page up while the kernel in front still runs
+    const bool appends = append && blockIdx.y + 1 == gridDim.y;
+    int pos = 0, page = -1;
+    if (appends) {
+        pos = positions[t];
+        page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
+    }
+    pdl_wait();
+    table = pdl_fresh(table);          // written by the rope table kernel of this step
     T* row = qkv + (size_t)t * qkv_stride;
     const float2* cs_row = table + (size_t)t * half;
     // blockIdx.y < gridDim.y - 1: a group of ROPE_GROUP query heads, rotated in place;
     // the last block of a token handles the key and value heads
-    if (blockIdx.y + 1 < gridDim.y || !append) {
+    if (!appends) {
         const int h0 = blockIdx.y * ROPE_GROUP, h1 = min(nh, h0 + ROPE_GROUP);
         for (int idx = threadIdx.x; idx < (h1 - h0) * half; idx += blockDim.x) {
             const int h = h0 + idx / half, i = idx % half;
@@ -231,8 +239,6 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
         }
         return;
     }
-    const int pos = positions[t];
-    const int page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
     if (page < 0 || page >= n_pages) return;   // the host reserved the pages; never write outside the cache
     const T* krow = row + (size_t)nh * hd;
     const T* vrow = krow + (size_t)nkv * hd;
