@@ -33,6 +33,7 @@ class Attention(Mixer):
         self.scale = 1.0 / math.sqrt(float(self.head_dim))
         pos = p.get("position")
         self.position = ctx.shared_part(POSITION_ENCODINGS, pos) if pos is not None else None
+        self.graph_safe = getattr(self.position, "graph_safe", True)      # a step is as capturable as its parts
         self.q_width = self.heads * self.head_dim
         self.kv_width = self.kv_heads * self.head_dim
         self.w_qkv = None

@@ -5,6 +5,8 @@ import dataclasses
 import json
 import math
 
+import numpy as np
+
 import pytest
 import torch
 
@@ -268,6 +270,151 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     finally:
         unregister_architecture(ToyConfig)
         MIXERS.unregister("toy_decay")
+
+
+# ------------------------------------------- a toy feed-forward with routing, another position encoding
+def _register_toy_routed():
+    """A feed-forward that routes every token to one of two small experts (router logits and
+    the softmax in 32-bit, the chosen expert's output scaled by its probability), and a rotary
+    position encoding with its own law of frequencies over half of each head.  Both are defined
+    here, registered, and named by an architecture of their own; the library is not touched."""
+    from hilbert_pruned_8b_b200.config import LlamaConfig, PartSpec, register_architecture
+    from hilbert_pruned_8b_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, ParamSpec, PositionEncoding
+
+    @FEED_FORWARDS.register("toy_top1")
+    class ToyTop1(FeedForward):
+        graph_safe = False          # plain torch operations that allocate
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.hidden, self.inner, self.experts = (int(spec.params[k]) for k in ("hidden_size", "inner_size", "experts"))
+
+        def params(self):
+            out = [ParamSpec("router.weight", (self.experts, self.hidden))]
+            for e in range(self.experts):
+                out += [ParamSpec(f"experts.{e}.in.weight", (self.inner, self.hidden)),
+                        ParamSpec(f"experts.{e}.out.weight", (self.hidden, self.inner))]
+            return out
+
+        def bind(self, tensors):
+            self.router = tensors["router.weight"].float()
+            self.w_in = [tensors[f"experts.{e}.in.weight"].float() for e in range(self.experts)]
+            self.w_out = [tensors[f"experts.{e}.out.weight"].float() for e in range(self.experts)]
+
+        def forward(self, h, residual, step):
+            x = h.float()
+            prob = torch.softmax(x @ self.router.t(), dim=-1)
+            top = prob.argmax(dim=-1)
+            for e in range(self.experts):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel():
+                    y = torch.relu(x[rows] @ self.w_in[e].t()) @ self.w_out[e].t()
+                    residual[rows] += y * prob[rows, e].unsqueeze(1)
+
+    @POSITION_ENCODINGS.register("toy_linear_rotary")
+    class ToyLinearRotary(PositionEncoding):
+        graph_safe = False
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.rotary_dim = int(spec.params["rotary_dim"])
+            self.slope = float(spec.params["slope"])
+
+        def table(self, step):
+            """[tokens, rot/2, 2] cosines and sines: pair i turns by position * slope * (i + 1)."""
+            key = f"toy_linear_rotary:{self.rotary_dim}:{self.slope}"
+            if key not in step.shared:
+                freq = self.slope * torch.arange(1, self.rotary_dim // 2 + 1, dtype=torch.float32, device=step.positions.device)
+                ang = step.positions.float().unsqueeze(1) * freq.unsqueeze(0)
+                step.shared[key] = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+            return step.shared[key]
+
+    class ToyRoutedConfig:
+        architecture = "ToyRoutedForCausalLM"
+        model_type = "toy_routed"
+
+        def __init__(self, base, slope):
+            self.base, self.slope = base, slope
+
+        @classmethod
+        def from_dict(cls, root):
+            return cls(LlamaConfig.from_dict({**root, "architectures": ["LlamaForCausalLM"]}), root["toy_slope"])
+
+        def to_dict(self):
+            return {**self.base.to_dict(), "architectures": [self.architecture], "model_type": self.model_type,
+                    "toy_slope": self.slope}
+
+        def model_spec(self):
+            s, b = self.base.model_spec(), self.base
+            pos = PartSpec("toy_linear_rotary", {"rotary_dim": b.head_dim // 2, "slope": self.slope})
+            routed = PartSpec("toy_top1", {"hidden_size": b.hidden_size, "inner_size": 48, "experts": 2})
+            layers = []
+            for i, ls in enumerate(s.layers):
+                mixer = PartSpec(ls.mixer.kind, {**ls.mixer.params, "position": pos})
+                ls = dataclasses.replace(ls, mixer=mixer)
+                if i % 2:
+                    ls = dataclasses.replace(ls, feed_forward=routed, feed_forward_prefix="routed.")
+                layers.append(ls)
+            return dataclasses.replace(s, architecture=self.architecture, layers=layers)
+
+    register_architecture(ToyRoutedConfig)
+    return ToyRoutedConfig
+
+
+class PlainToyRouted(pl.PlainLlama):
+    def __init__(self, folder, slope):
+        super().__init__(folder)
+        hd = self.cfg["head_dim"]
+        self.cfg["rotary_dim"] = hd // 2
+        self.inv_freq = (np.float32(slope) * np.arange(1, hd // 4 + 1, dtype=np.float32)).astype(np.float32)
+
+    def layer(self, x, i, positions):
+        if i % 2 == 0:
+            return super().layer(x, i, positions)
+        c, w, p = self.cfg, self.w, f"{self.prefix}layers.{i}."
+        nh, nkv, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        T = x.shape[0]
+        h = pl.rms_norm(x, w[p + "input_layernorm.weight"], c["rms_norm_eps"])
+        q = pl.rope(pl.linear(h, w[p + "self_attn.q_proj.weight"]).view(T, nh, hd), positions, self.inv_freq, c["rotary_dim"])
+        k = pl.rope(pl.linear(h, w[p + "self_attn.k_proj.weight"]).view(T, nkv, hd), positions, self.inv_freq, c["rotary_dim"])
+        v = pl.linear(h, w[p + "self_attn.v_proj.weight"]).view(T, nkv, hd)
+        x = x + pl.linear(pl.attention(q, k, v).reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"])
+        h = pl.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["rms_norm_eps"])
+        prob = torch.softmax(h.float() @ w[p + "routed.router.weight"].float().t(), dim=-1).double()   # router in 32-bit
+        rows = []
+        for t in range(T):
+            e = int(prob[t].argmax())
+            y = torch.relu(h[t] @ w[p + f"routed.experts.{e}.in.weight"].t()) @ w[p + f"routed.experts.{e}.out.weight"].t()
+            rows.append(y * prob[t, e])
+        return x + torch.stack(rows)
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    require_gpu()
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.config import unregister_architecture
+    from hilbert_pruned_8b_b200.engine.step import Engine
+    from hilbert_pruned_8b_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS
+    Cfg = _register_toy_routed()
+    try:
+        cfg = Cfg(hb.LlamaConfig.from_dict(TINY_B), 0.013)
+        folder = hb.weights.write_random_model(str(tmp_path / "routed"), cfg, seed=41, fan_in_scale=1.0, norm_std=0.05)
+        eng = Engine.from_folder(folder, "float32", max_tokens=1024)
+        table = eng.model.weight_table()
+        assert any(n.endswith("layers.1.routed.experts.1.out.weight") for n in table)
+        assert not any("layers.1.mlp." in n for n in table) and any("layers.0.mlp.gate_proj.weight" in n for n in table)
+        v = TINY_B["vocab_size"]
+        reqs = {"p": tt.random_tokens(50, v, 920), "q": tt.random_tokens(21, v, 921), "r": tt.random_tokens(70, v, 922)}
+        ref = tt.plain_logits(PlainToyRouted(folder, 0.013), reqs)
+        for make in (tt.trace_whole, lambda r: tt.trace_tail(r, 16),
+                     lambda r: tt.trace_batches([{"p": (r["p"], 30), "q": (r["q"], 21)}, {"r": (r["r"], 5)}])):
+            steps, _ = make(reqs)
+            tt.compare(tt.run_in_process(eng, steps), ref, "float32", "toy routed")
+        assert min(eng.cache.pages_free()) == eng.cache.num_pages
+    finally:
+        unregister_architecture(Cfg)
+        FEED_FORWARDS.unregister("toy_top1")
+        POSITION_ENCODINGS.unregister("toy_linear_rotary")
 
 
 # --------------------------------------------------------------------------- the run order is data
