@@ -334,6 +334,8 @@ def timeline_table(llm, batch, context, steps=8):
     for n in ops.call_log:
         if n == "hb_attention_decode":
             names += ["attention_decode", "attention_decode_combine"]
+        elif n == "hb_attention_decode_combined":
+            names.append("attention_decode")
         elif n not in ("hb_device_info", "hb_timeline_set"):
             names.append(n[3:])
     ops.call_log = None

@@ -49,6 +49,10 @@ int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, 
                         const int* page_table, int pt_width, const int* positions, float* scratch, void* out,
                         long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim, float scale,
                         int window, int splits, int max_pages, int n_pages, void* stream);
+int hb_attention_decode_combined(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                 const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
+                                 void* out, long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim,
+                                 float scale, int window, int splits, int max_pages, int n_pages, void* stream);
 int hb_attention_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* k_cache,
                               void* v_cache, const int* page_table, int pt_width, const int* positions, float* scratch,
                               int* counters, void* out, long long out_stride, int batch, int n_heads, int n_kv_heads,

@@ -175,12 +175,71 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
     __syncthreads();
 }
 
+// The last split of a (sequence, kv head) to get here combines all of them: a counter per pair
+// (left at zero), then the weights of the splits, one (row, split) pair per thread (all maxima
+// and sums requested at once), then all partial outputs: two round trips.  Called by every
+// thread of the block after it has written its partial result.
 template <int HD>
+__device__ __forceinline__ void combine_by_last_split(int b, int g, int G, int S, int nh, int nkv, const float* part_o,
+                                                      const float* part_ml, int* counters, bf16* out, long long out_stride,
+                                                      float* w_split, float* l_split, int* is_last_flag) {
+    const int tid = threadIdx.x;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(counters + (size_t)b * nkv + g, 1);
+        const int last = prev == S - 1;
+        if (last) counters[(size_t)b * nkv + g] = 0;     // ready for the next launch
+        *is_last_flag = last;
+    }
+    __syncthreads();
+    if (!*is_last_flag) return;
+    __threadfence();
+    for (int i = tid; i < G * S; i += AD_THREADS) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + ((size_t)b * nh + g * G) * S + i);
+        w_split[i] = ml.x;
+        l_split[i] = ml.y;
+    }
+    __syncthreads();
+    if (tid < G) {
+        float M = -INFINITY;
+        for (int zz = 0; zz < S; zz++) M = fmaxf(M, w_split[tid * S + zz]);
+        float L = 0.0f;
+        for (int zz = 0; zz < S; zz++) {
+            const float mz = w_split[tid * S + zz];
+            const float e = mz != -INFINITY ? exp2f(mz - M) : 0.0f;
+            L += l_split[tid * S + zz] * e;
+            w_split[tid * S + zz] = e;
+        }
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+        for (int zz = 0; zz < S; zz++) w_split[tid * S + zz] *= inv;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += AD_THREADS) {
+        const int r = idx / HD, d = idx - r * HD, head = g * G + r;
+        const float* po = part_o + ((size_t)b * nh + head) * S * HD + d;
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int zz = 0; zz < S; zz++) {
+            const float w = w_split[r * S + zz];
+            const float v = __ldcg(po + (size_t)zz * HD);
+            if (w != 0.0f) acc += v * w;
+        }
+        out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc);
+    }
+}
+
+// COMBINE: the last split of a (sequence, kv head) to finish also combines the splits (no
+// second kernel); with one split the result goes straight to `out`.
+template <int HD, bool COMBINE>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                    const int* __restrict__ page_table, int pt_width, const int* __restrict__ positions,
-                   float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, float scale_log2e,
-                   int window, int pages_per_split, int n_pages) {
+                   float* part_o, float* part_ml, int nh, int nkv, float scale_log2e,
+                   int window, int pages_per_split, int n_pages, int* counters, bf16* out, long long out_stride) {
+    __shared__ int is_last;
+    __shared__ float w_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];
+    __shared__ float l_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];
     pdl_trigger();
     // positions and page table come from the step's metadata copy, which finished before the
     // step's first kernel: they may be read before the wait for the kernel in front
@@ -201,6 +260,14 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
             float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
             ml[0] = -INFINITY;
             ml[1] = 0.0f;
+        }
+        if (COMBINE) {
+            if (S == 1) {
+                for (int idx = tid; idx < G * HD; idx += AD_THREADS)
+                    out[(size_t)b * out_stride + (size_t)(g * G) * HD + idx] = __float2bfloat16_rn(0.0f);
+            } else {
+                combine_by_last_split<HD>(b, g, G, S, nh, nkv, part_o, part_ml, counters, out, out_stride, w_split, l_split, &is_last);
+            }
         }
         return;
     }
@@ -240,6 +307,10 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
                 L += sl[w * 16 + r] * e;
             }
         }
+        if (COMBINE && S == 1) {                  // the only split: the result itself
+            out[(size_t)b * out_stride + (size_t)(g * G + r) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+            continue;
+        }
         const size_t base = ((size_t)b * nh + g * G + r) * S + z;
         part_o[base * HD + d] = acc;
         if (d == 0) {
@@ -247,6 +318,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
             part_ml[base * 2 + 1] = L;
         }
     }
+    if (COMBINE && S > 1)
+        combine_by_last_split<HD>(b, g, G, S, nh, nkv, part_o, part_ml, counters, out, out_stride, w_split, l_split, &is_last);
 }
 
 // One rotated element of a head: x is the head's row before rotation, cs_row the token's
@@ -367,51 +440,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
         ml[1] = 0.0f;
     }
 
-    // the last split of this (sequence, kv head) to get here combines all of them
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const int prev = atomicAdd(counters + (size_t)b * nkv + g, 1);
-        is_last = prev == S - 1;
-        if (is_last) counters[(size_t)b * nkv + g] = 0;     // ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // weights of the splits, one (row, split) pair per thread: all maxima and sums are
-    // requested at once, then all partial outputs, so the tail costs two round trips
-    for (int i = tid; i < G * S; i += AD_THREADS) {
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + ((size_t)b * nh + g * G) * S + i);
-        w_split[i] = ml.x;
-        l_split[i] = ml.y;
-    }
-    __syncthreads();
-    if (tid < G) {
-        float M = -INFINITY;
-        for (int zz = 0; zz < S; zz++) M = fmaxf(M, w_split[tid * S + zz]);
-        float L = 0.0f;
-        for (int zz = 0; zz < S; zz++) {
-            const float mz = w_split[tid * S + zz];
-            const float e = mz != -INFINITY ? exp2f(mz - M) : 0.0f;
-            L += l_split[tid * S + zz] * e;
-            w_split[tid * S + zz] = e;
-        }
-        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-        for (int zz = 0; zz < S; zz++) w_split[tid * S + zz] *= inv;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < G * HD; idx += AD_THREADS) {
-        const int r = idx / HD, d = idx - r * HD, head = g * G + r;
-        const float* po = part_o + ((size_t)b * nh + head) * S * HD + d;
-        float acc = 0.0f;
-#pragma unroll 4
-        for (int zz = 0; zz < S; zz++) {
-            const float w = w_split[r * S + zz];
-            const float v = __ldcg(po + (size_t)zz * HD);
-            if (w != 0.0f) acc += v * w;
-        }
-        out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc);
-    }
+    combine_by_last_split<HD>(b, g, G, S, nh, nkv, part_o, part_ml, counters, out, out_stride, w_split, l_split, &is_last);
 }
 
 // out[b, head, :] = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M)
@@ -452,27 +481,40 @@ extern "C" long long hb_attention_decode_scratch_floats(int batch, int n_heads, 
     return (long long)batch * n_heads * splits * (head_dim + 2);
 }
 
-template <int HD>
-static int launch_decode(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
-                         int pt_width, const int* positions, float* scratch, void* out, long long out_stride, int batch,
-                         int nh, int nkv, float scale, int window, int splits, int pages_per_split, int n_pages,
-                         cudaStream_t s) {
+// counters == nullptr: the splits are combined by a second kernel.
+template <int HD, bool COMBINE>
+static int launch_decode_splits(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
+                                int pt_width, const int* positions, float* part_o, float* part_ml, int* counters, void* out,
+                                long long out_stride, int batch, int nh, int nkv, float scale, int window, int splits,
+                                int pages_per_split, int n_pages, cudaStream_t s) {
     constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
     constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("attention_decode: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
+    hb_launch(attn_decode_kernel<HD, COMBINE>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)q, q_stride,
+              (const bf16*)kc, (const bf16*)vc, page_table, pt_width, positions, part_o, part_ml, nh, nkv, scale * AD_LOG2E, window,
+              pages_per_split, n_pages, counters, (bf16*)out, out_stride);
+    return hb_check_launch("attention_decode");
+}
+
+template <int HD>
+static int launch_decode(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
+                         int pt_width, const int* positions, float* scratch, int* counters, void* out, long long out_stride,
+                         int batch, int nh, int nkv, float scale, int window, int splits, int pages_per_split, int n_pages,
+                         cudaStream_t s) {
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)batch * nh * splits * HD;
-    dim3 grid(splits, nkv, batch);
-    hb_launch(attn_decode_kernel<HD>, dim3(grid), dim3(AD_THREADS), SMEM, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
-                                                          pt_width, positions, part_o, part_ml, nh, nkv, scale * AD_LOG2E,
-                                                          window, pages_per_split, n_pages);
-    if (hb_check_launch("attention_decode")) return 1;
+    if (counters != nullptr)
+        return launch_decode_splits<HD, true>(q, q_stride, kc, vc, page_table, pt_width, positions, part_o, part_ml, counters, out,
+                                              out_stride, batch, nh, nkv, scale, window, splits, pages_per_split, n_pages, s);
+    if (launch_decode_splits<HD, false>(q, q_stride, kc, vc, page_table, pt_width, positions, part_o, part_ml, nullptr, out,
+                                        out_stride, batch, nh, nkv, scale, window, splits, pages_per_split, n_pages, s))
+        return 1;
     dim3 cgrid(batch, nh);
     hb_launch(attn_decode_combine_kernel<bf16>, dim3(cgrid), dim3(HD), 0, s, part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
     return hb_check_launch("attention_decode_combine");
@@ -482,10 +524,10 @@ static int launch_decode(const void* q, long long q_stride, const void* kc, cons
 // query's position (its own key, already in the cache, is the last one it sees).  `scratch`
 // holds hb_attention_decode_scratch_floats floats.  `max_pages` bounds the pages of any
 // sequence of the batch; the keys are cut into `splits` ranges of whole pages.
-extern "C" int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
-                                   const int* page_table, int pt_width, const int* positions, float* scratch, void* out,
-                                   long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim, float scale,
-                                   int window, int splits, int max_pages, int n_pages, void* stream) {
+static int attention_decode_any(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
+                                void* out, long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim,
+                                float scale, int window, int splits, int max_pages, int n_pages, void* stream) {
     if (batch == 0) return 0;
     HB_REQUIRE(hb_attention_decode_supported(n_heads, n_kv_heads, head_dim),
                "attention_decode: head size %d with %d heads over %d kv heads is not built (64 or 128, groups up to 16)",
@@ -495,13 +537,35 @@ extern "C" int hb_attention_decode(const void* q, long long q_stride, const void
     HB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q & 3) == 0, "attention_decode: queries must be 4-byte aligned");
     HB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_decode: cache must be 16-byte aligned");
     if (splits > max_pages) splits = max_pages;
+    HB_REQUIRE(counters == nullptr || splits <= AD_MAX_SPLITS, "attention_decode: at most %d splits when the last one combines, got %d",
+               AD_MAX_SPLITS, splits);
     const int pps = (max_pages + splits - 1) / splits;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 128)
-        return launch_decode<128>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride,
-                                  batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
-    return launch_decode<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride, batch,
-                             n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+        return launch_decode<128>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out,
+                                  out_stride, batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+    return launch_decode<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out, out_stride,
+                             batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+}
+
+extern "C" int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                   const int* page_table, int pt_width, const int* positions, float* scratch, void* out,
+                                   long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                   int window, int splits, int max_pages, int n_pages, void* stream) {
+    return attention_decode_any(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, nullptr, out, out_stride,
+                                batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
+}
+
+// The same in ONE launch: the last split of a (sequence, kv head) to finish combines the
+// splits.  `counters`: batch * n_kv_heads ints, zero before the first use (left at zero).
+extern "C" int hb_attention_decode_combined(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                            const int* page_table, int pt_width, const int* positions, float* scratch,
+                                            int* counters, void* out, long long out_stride, int batch, int n_heads,
+                                            int n_kv_heads, int head_dim, float scale, int window, int splits, int max_pages,
+                                            int n_pages, void* stream) {
+    HB_REQUIRE(counters != nullptr, "attention_decode_combined: no counters");
+    return attention_decode_any(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out, out_stride,
+                                batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
 }
 
 template <int HD>

@@ -40,6 +40,8 @@ _SIGNATURES = {
                              _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
     "hb_attention_decode": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                             _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_attention_decode_combined": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int,
+                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_attention_decode_fused": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                   _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int,
                                   _c_ptr],
@@ -192,6 +194,11 @@ class Ops:
         # 4.0 + 43.5 + 4.2 us (its own round trips are as long as theirs), and at batch 64 it is
         # 1 % slower.
         self.fuse_decode_attention = False
+        # Split-K decode attention whose last split combines the splits, instead of a second
+        # kernel.  Off: at batch 8 / 8192 tokens a step of 8 layers takes 1319 us against 1313 us, at
+        # batch 1 1079 against 1052 us (the last split's two round trips are longer than a kernel
+        # that is already resident).  A single split always writes the result itself.
+        self.combine_in_attention = False
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
@@ -461,6 +468,17 @@ class Ops:
             if need > self._decode_scratch.numel():
                 self._retired.append(self._decode_scratch)
                 self._decode_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+            if ((n_splits == 1 or self.combine_in_attention) and n_splits <= 16
+                    and T * kv_heads <= self._decode_counters.numel()):
+                # one split writes the result itself; with more, the last split of a (sequence, kv
+                # head) to finish can combine them (a switch: measured slower than the second kernel)
+                self._call("hb_attention_decode_combined", qkv.data_ptr(), _rows(qkv, "attention queries"), cache.k.data_ptr(),
+                           cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.positions.data_ptr(),
+                           self._decode_scratch.data_ptr(), self._decode_counters.data_ptr(), out.data_ptr(),
+                           _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale), win, n_splits, max_pages,
+                           cache.k.shape[0], self._stream())
+                self.launches += 1
+                return
             self._call("hb_attention_decode", qkv.data_ptr(), _rows(qkv, "attention queries"), cache.k.data_ptr(),
                        cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.positions.data_ptr(),
                        self._decode_scratch.data_ptr(), out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,

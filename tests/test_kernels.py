@@ -475,6 +475,15 @@ def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
             ops.attention(qkv, nh, nkv, hd, cache, step, out, scale, window, splits=splits)
             ops.check_errors()
             assert _rel(out.view(T, nh, hd).cpu(), ref) < 2 ** -7, f"splits={splits} decode={step.is_decode}"
+            if step.is_decode:                 # a second kernel combined above; now the last split does
+                ops.combine_in_attention = True
+                try:
+                    two = torch.full((T, nh * hd), 9.0, device=DEV, dtype=dtype)
+                    ops.attention(qkv, nh, nkv, hd, cache, step, two, scale, window, splits=splits)
+                finally:
+                    ops.combine_in_attention = False
+                assert _rel(two.view(T, nh, hd).cpu(), ref) < 2 ** -7
+                assert int(ops._decode_counters.abs().sum()) == 0
         if not step.is_decode:                 # the tcgen05 kernel ran above; now the mma.sync one
             ops.use_tcgen05_attention = False
             try:
