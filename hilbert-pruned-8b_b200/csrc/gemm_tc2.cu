@@ -32,6 +32,14 @@
 // last, partly filled wave over all pairs (float32 partial tiles of 128 KB per CTA in scratch,
 // summed by the last contributor) was measured too: the sums cost more than the idle pairs
 // (o projection at 2048 tokens: 99 us against 73 us), so tiles stay whole.
+// What bounds the K loop is an SM's TMA intake: 32 KB per K block (16 KB of weights, 16 KB of
+// tokens) at about 60 GB/s is 0.47 us, the four MMAs need 0.27 us.  One SM takes over 100
+// GB/s from L2 through cp.async (measured with 128 KB in flight), so the token tiles were moved
+// to four loader warps (cp.async into the swizzled layout, cp.async.mbarrier.arrive on a local
+// barrier, a forwarder thread for the arrival on the leader's barrier): correct, but 174 us
+// for the qkv product against 82 us: with six stages the chain stage free -> copies -> barrier
+// -> forwarder -> MMA is twice as long as TMA's.  (A loader thread that arrives remotely
+// itself waits, with the release, for all its copies in flight: 261 us.)
 #define T2_STAGES(MODE) 6
 
 template <int MODE, int STAGES>
