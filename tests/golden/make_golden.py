@@ -22,7 +22,9 @@ from golden_models import GOLDEN_MODELS, golden_tokens, write_golden_model  # no
 
 
 def main() -> None:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref = sys.argv[1]
     work = tempfile.mkdtemp(prefix="golden_")
     src = os.path.join(work, "ct")
     shutil.copytree(os.path.join(ref, "cleanroom-transformer"), src)
