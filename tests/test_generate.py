@@ -55,6 +55,36 @@ def test_stop_tokens_end_sequences_early(model_folders):
     assert eos == [3, 5]
 
 
+def test_many_requests_with_stops_and_budgets_equal_plain(model_folders):
+    """70 requests in batches of up to 32: sequences stop at different times (stop tokens, budgets
+    from 0 to 14), so the decode batch shrinks step by step, replayed graphs of many batch sizes
+    take turns, and the loop, which runs one step ahead of the tokens it has read, has to drop
+    the sequences that stopped.  Every result is the plain model's."""
+    require_gpu()
+    import random
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.engine.generate import GenerationRequest
+    from hilbert_pruned_8b_b200.sampling import SamplingParams
+    rnd = random.Random(7)
+    vocab = TINY_A["vocab_size"]
+    plain = PlainLlama(model_folders["strong_a"])
+    reqs, want = [], []
+    for i in range(70):
+        prompt = tt.random_tokens(rnd.randrange(1, 40), vocab, 2000 + i)
+        budget = rnd.randrange(0, 15)
+        free = generate_greedy(plain, prompt, budget) if budget else []
+        stop = [free[rnd.randrange(len(free))]] if free and rnd.random() < 0.5 else []
+        reqs.append(GenerationRequest(prompt, max_new_tokens=budget, sampling=SamplingParams(0.0, 0), stop_token_ids=stop))
+        want.append(generate_greedy(plain, prompt, budget, stop=stop) if budget else [])
+    llm = hb.load(model_folders["strong_a"], dtype="float32", max_tokens=64 * 40, max_batch=32)
+    res = llm.generate_requests(reqs)
+    assert [r.tokens for r in res] == want
+    for r, q, w in zip(res, reqs, want):
+        assert r.finish_reason == ("stop" if w and w[-1] in (q.stop_token_ids or []) else "length")
+    assert llm.generator.stats.batches >= 3 and llm.engine.graph_replays > 0
+    assert min(llm.engine.cache.pages_free()) == llm.engine.cache.num_pages
+
+
 def test_bfloat16_greedy_follows_plain_rounded_model(model_folders):
     require_gpu()
     import hilbert_pruned_8b_b200 as hb
