@@ -336,6 +336,8 @@ def timeline_table(llm, batch, context, steps=8):
             names += ["attention_decode", "attention_decode_combine"]
         elif n == "hb_attention_decode_combined":
             names.append("attention_decode")
+        elif n == "hb_attention_decode_fused":      # rotation and append inside; a single split has no combine kernel
+            names += ["attention_decode_fused", "attention_decode_combine"]
         elif n not in ("hb_device_info", "hb_timeline_set"):
             names.append(n[3:])
     ops.call_log = None
@@ -347,6 +349,8 @@ def timeline_table(llm, batch, context, steps=8):
         one(5 + k)
     marks = [m for m in ops.timeline_end() if m[0] > 10 ** 9]      # kernel marks (events carry small codes)
     per = len(marks) // steps
+    if per == len(names) - names.count("attention_decode_fused"):
+        names = [n for n in names if n != "attention_decode_combine"]
     if per != len(names):
         names = [f"kernel {i}" for i in range(per)]
     rows, total = [], 0.0

@@ -28,12 +28,16 @@
 // requested BEFORE griddepcontrol.wait (they hold older tokens only, and the page table and
 // the positions come from a copy that finished before the step's first kernel), the wait
 // happens before the first request of that page, or after the prologue.  -1: the caller
-// has waited already.
-template <int HD, typename F>
+// has waited already.  `after_wait` runs right after the wait (the place to write that page).
+// `patch_page` (>= 0): when that page has arrived, row `patch_row` of its key and value tiles is
+// overwritten with k_new / v_new (HD values each, in shared memory): the new token's key and
+// value, for a page that was requested before they existed.
+template <int HD, typename F, typename W>
 __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], const bf16* kc, const bf16* vc,
                                                   const int* __restrict__ pt, int n_pages, int nkv, int g, int lo,
                                                   int len, int p_begin, int p_end, float scale_log2e, uint8_t* smem,
-                                                  F&& after_prologue, int fresh_page = -1) {
+                                                  F&& after_prologue, int fresh_page, W&& after_wait, int patch_page = -1,
+                                                  int patch_row = 0, const bf16* k_new = nullptr, const bf16* v_new = nullptr) {
     constexpr int ROW_BYTES = HD * 2;
     constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;        // one page of K (or V) of one kv head
     constexpr int CHUNKS = ROW_BYTES / 16;
@@ -68,11 +72,15 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
     for (int s = 0; s < AD_STAGES - 1; s++) {
         if (!waited && p_begin + s >= fresh_page) {
             pdl_wait();
+            after_wait();
             waited = true;
         }
         load_page(s, p_begin + s);
     }
-    if (!waited) pdl_wait();
+    if (!waited) {
+        pdl_wait();
+        after_wait();
+    }
     after_prologue();
 
     for (int pi = p_begin; pi < p_end; pi++) {
@@ -81,6 +89,16 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
         __syncthreads();
         load_page((it + AD_STAGES - 1) % AD_STAGES, pi + AD_STAGES - 1);
         const uint32_t kt = smem_base + (it % AD_STAGES) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
+        if (pi == patch_page) {
+            if (tid < 2 * CHUNKS) {
+                const int ch = tid % CHUNKS;
+                const bool value = tid >= CHUNKS;
+                const uint4 x = reinterpret_cast<const uint4*>(value ? v_new : k_new)[ch];
+                *reinterpret_cast<uint4*>(smem + (it % AD_STAGES) * 2 * TILE_BYTES + (value ? TILE_BYTES : 0) +
+                                          swizzled<ROW_BYTES>(patch_row, ch)) = x;
+            }
+            __syncthreads();
+        }
 
         // scores of this warp's 16 keys of the page
         float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
@@ -289,7 +307,7 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
             qf[ks][2] = r0 < G ? __ldcg(q0 + ks * 8 + 4) : 0u;
             qf[ks][3] = r0 + 8 < G ? __ldcg(q1 + ks * 8 + 4) : 0u;
         }
-    }, (len - 1) / HB_PAGE_TOKENS);
+    }, (len - 1) / HB_PAGE_TOKENS, [] {});
     const float* so = reinterpret_cast<const float*>(smem);
     const float* sm = so + 4 * 16 * HD;
     const float* sl = sm + 4 * 16;
@@ -322,25 +340,14 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
         combine_by_last_split<HD>(b, g, G, S, nh, nkv, part_o, part_ml, counters, out, out_stride, w_split, l_split, &is_last);
 }
 
-// One rotated element of a head: x is the head's row before rotation, cs_row the token's
-// (cos, sin) pairs; pairs are (i, i + rot/2), elements beyond `rot` pass through
-// (cleanroom-transformer/src/cpu_backend.c:92-97).
-__device__ __forceinline__ float rotated(const bf16* __restrict__ x, int d, int rot, const float2* __restrict__ cs_row) {
-    const int half = rot >> 1;
-    if (d >= rot) return __bfloat162float(x[d]);
-    const int i = d < half ? d : d - half;
-    const float2 cs = cs_row[i];
-    float y1, y2;
-    rope_pair(__bfloat162float(x[i]), __bfloat162float(x[i + half]), cs.x, cs.y, y1, y2);
-    return d < half ? y1 : y2;
-}
-
-// The whole attention of a decode step in one launch: rotate the new token's queries and key,
-// append key and value to the cache, attend over the cache in splits, and let the last split
-// of a (sequence, kv head) to finish combine the partial results (a counter per pair, left at
-// zero).  qkv holds the projections BEFORE rotation; it is not written.  The split that owns
-// the page of the new position appends before it reads that page.
-template <int HD>
+// The attention of a decode step without a rotation kernel in front: rotate the new token's
+// queries and key, append key and value to the cache, attend over the cache in splits.  COMBINE:
+// the last split of a (sequence, kv head) to finish combines the partial results (a counter per
+// pair, left at zero); else the combination kernel follows.  qkv holds the projections BEFORE
+// rotation; it is not written.  All pages of a split are requested before the wait for the
+// kernel in front; the split that owns the page of the new position puts the new key and value
+// into its copy of that page in shared memory (and into the cache, for the steps to come).
+template <int HD, bool COMBINE>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot,
                          bf16* kc, bf16* vc, const int* __restrict__ page_table, int pt_width,
@@ -348,15 +355,13 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                          int* __restrict__ counters, bf16* __restrict__ out, long long out_stride, int nh, int nkv,
                          float scale_log2e, int window, int pages_per_split, int n_pages, int append) {
     pdl_trigger();
-    pdl_wait();
-    qkv = pdl_fresh(qkv);
-    table = pdl_fresh(table);
     constexpr int KSTEPS = HD / 16;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
     __shared__ __align__(16) bf16 q_rot[16 * HD];          // the group's rotated queries, rows >= G zero
-    __shared__ float w_split[16 * AD_MAX_SPLITS];          // maxima, then combination weights [row][split]
-    __shared__ float l_split[16 * AD_MAX_SPLITS];          // sums [row][split]
+    __shared__ __align__(16) bf16 kv_new[2 * HD];          // the new token's rotated key, then its value
+    __shared__ float w_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];   // maxima, then combination weights [row][split]
+    __shared__ float l_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];   // sums [row][split]
     const int z = blockIdx.x, g = blockIdx.y, b = blockIdx.z, S = gridDim.x;
     const int tid = threadIdx.x, lane = tid & 31;
     const int G = nh / nkv;
@@ -365,40 +370,101 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
     const int p_begin = max(z * pages_per_split, lo / HB_PAGE_TOKENS);
     const int p_end = min((z + 1) * pages_per_split, (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS);
     const int* pt = page_table + (size_t)b * pt_width;
-    const bf16* row = qkv + (size_t)b * qkv_stride;
-    const float2* cs_row = table + (size_t)b * (rot >> 1);
+    // what the kernels in front wrote (projections, table) is read after the wait only, through
+    // pointers that the compiler cannot take for memory that never changes
+    const bf16* row = nullptr;
+    const float2* cs_row = nullptr;
+    auto waited = [&]() {
+        row = pdl_fresh(qkv) + (size_t)b * qkv_stride;
+        cs_row = pdl_fresh(table) + (size_t)b * (rot >> 1);
+    };
 
-    // The split that owns the page of the new position appends the rotated key and the value.
-    // With the page among the first ones requested it has to happen before the requests, else
-    // it runs while they are in flight.
+    // The split that owns the page of the new position rotates the new key and writes it and the
+    // value to the cache, for later steps.  This step reads them from shared memory: the page is
+    // requested with all the others before the wait, and its row of the new position is
+    // overwritten when it has arrived.  The loads are requested together with the queries'.
     const bool owner = append && z == (pos / HB_PAGE_TOKENS) / pages_per_split;
+    const int half = rot >> 1;
+    float kx1 = 0.0f, kx2 = 0.0f;               // one pair of the key per thread (tid < rot/2), or
+    float2 kcs = make_float2(1.0f, 0.0f);       // one element beyond the rotated ones (tid >= rot)
+    bf16 vx = __float2bfloat16_rn(0.0f);
+    auto load_new = [&]() {
+        static_assert(HD <= AD_THREADS, "one thread per element of the new key and value");
+        const bf16* kn = row + (size_t)(nh + g) * HD;
+        const bf16* vn = row + (size_t)(nh + nkv + g) * HD;
+        if (tid < half) {
+            kcs = cs_row[tid];
+            kx1 = __bfloat162float(kn[tid]);
+            kx2 = __bfloat162float(kn[tid + half]);
+        } else if (tid >= rot && tid < HD) {
+            kx1 = __bfloat162float(kn[tid]);
+        }
+        if (tid < HD) vx = vn[tid];
+    };
     auto append_new = [&]() {
         const int page = pt[pos / HB_PAGE_TOKENS];
-        if (page >= 0 && page < n_pages) {       // the host reserved the page; never write outside the cache
-            const bf16* kn = row + (size_t)(nh + g) * HD;
-            const bf16* vn = row + (size_t)(nh + nkv + g) * HD;
-            const size_t off = cache_offset(page, g, pos, nkv, HD);
-            for (int d = tid; d < HD; d += AD_THREADS) {
-                kc[off + d] = __float2bfloat16_rn(rotated(kn, d, rot, cs_row));
-                vc[off + d] = vn[d];
+        const bool in_cache = page >= 0 && page < n_pages;   // the host reserved the page; never write outside the cache
+        const size_t off = in_cache ? cache_offset(page, g, pos, nkv, HD) : 0;
+        if (tid < half) {
+            float y1, y2;
+            rope_pair(kx1, kx2, kcs.x, kcs.y, y1, y2);
+            const bf16 k1 = __float2bfloat16_rn(y1), k2 = __float2bfloat16_rn(y2);
+            kv_new[tid] = k1;
+            kv_new[tid + half] = k2;
+            if (in_cache) {
+                kc[off + tid] = k1;
+                kc[off + tid + half] = k2;
             }
+        } else if (tid >= rot && tid < HD) {
+            const bf16 k = __float2bfloat16_rn(kx1);
+            kv_new[tid] = k;
+            if (in_cache) kc[off + tid] = k;
         }
-        __threadfence();
-        __syncthreads();
+        if (tid < HD) {
+            kv_new[HD + tid] = vx;
+            if (in_cache) vc[off + tid] = vx;
+        }
     };
-    const bool early_append = owner && (pos / HB_PAGE_TOKENS) < p_begin + AD_STAGES - 1;
-    if (owner && (early_append || p_begin >= p_end)) append_new();
 
     if (p_begin < p_end) {
         uint32_t qf[KSTEPS][4];
+        for (int idx = G * HD + tid; idx < 16 * HD; idx += AD_THREADS) q_rot[idx] = __float2bfloat16_rn(0.0f);
         decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&]() {
-            if (owner && !early_append) append_new();
             // the group's queries, rotated once by the whole block; row r of the tile is head
-            // g*G + r (rows >= G are zero), fragments come from shared memory
-            for (int idx = tid; idx < 16 * HD; idx += AD_THREADS) {
-                const int r = idx / HD, d = idx - r * HD;
-                q_rot[idx] = r < G ? __float2bfloat16_rn(rotated(row + (size_t)(g * G + r) * HD, d, rot, cs_row))
-                                   : __float2bfloat16_rn(0.0f);
+            // g*G + r (rows >= G stay zero), fragments come from shared memory.  One pair
+            // (i, i + rot/2) per item.
+            const bf16* qrow = row + (size_t)(g * G) * HD;
+            constexpr int ITEMS = 16 * (HD / 2) / AD_THREADS;     // G <= 16, rot <= HD
+            float x1[ITEMS], x2[ITEMS];
+            float2 cs[ITEMS];
+#pragma unroll
+            for (int u = 0; u < ITEMS; u++) {                     // all loads first: one round trip
+                const int idx = tid + u * AD_THREADS;
+                if (idx < G * half) {
+                    const int r = idx / half, i = idx - r * half;
+                    cs[u] = cs_row[i];
+                    x1[u] = __bfloat162float(qrow[r * HD + i]);
+                    x2[u] = __bfloat162float(qrow[r * HD + i + half]);
+                }
+            }
+            if (owner) {
+                load_new();
+                append_new();
+            }
+#pragma unroll
+            for (int u = 0; u < ITEMS; u++) {
+                const int idx = tid + u * AD_THREADS;
+                if (idx < G * half) {
+                    const int r = idx / half, i = idx - r * half;
+                    float y1, y2;
+                    rope_pair(x1[u], x2[u], cs[u].x, cs[u].y, y1, y2);
+                    q_rot[r * HD + i] = __float2bfloat16_rn(y1);
+                    q_rot[r * HD + i + half] = __float2bfloat16_rn(y2);
+                }
+            }
+            for (int idx = tid; idx < G * (HD - rot); idx += AD_THREADS) {
+                const int r = idx / (HD - rot), d = rot + idx - r * (HD - rot);
+                q_rot[r * HD + d] = qrow[r * HD + d];
             }
             __syncthreads();
             const int r0 = lane >> 2, c = (lane & 3) * 2;
@@ -409,7 +475,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                 qf[ks][2] = *reinterpret_cast<const uint32_t*>(q_rot + r0 * HD + ks * 16 + c + 8);
                 qf[ks][3] = *reinterpret_cast<const uint32_t*>(q_rot + (r0 + 8) * HD + ks * 16 + c + 8);
             }
-        });
+        }, 1 << 30, waited, owner ? pos / HB_PAGE_TOKENS : -1, pos % HB_PAGE_TOKENS, kv_new, kv_new + HD);
         const float* so = reinterpret_cast<const float*>(smem);
         const float* sm = so + 4 * 16 * HD;
         const float* sl = sm + 4 * 16;
@@ -427,6 +493,10 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                     L += sl[w * 16 + r] * e;
                 }
             }
+            if (COMBINE && S == 1) {                 // the only split: the result itself
+                out[(size_t)b * out_stride + (size_t)(g * G + r) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+                continue;
+            }
             const size_t base = ((size_t)b * nh + g * G + r) * S + z;
             part_o[base * HD + d] = acc;
             if (d == 0) {
@@ -434,13 +504,25 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                 part_ml[base * 2 + 1] = L;
             }
         }
-    } else if (tid < G) {                        // nothing to read: an empty partial
-        float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
-        ml[0] = -INFINITY;
-        ml[1] = 0.0f;
+    } else {                                     // nothing to read: an empty partial
+        pdl_wait();                              // the scratch may still be read by the kernels in front
+        waited();
+        if (owner) {
+            load_new();
+            append_new();
+        }
+        if (tid < G) {
+            float* ml = part_ml + (((size_t)b * nh + g * G + tid) * S + z) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.0f;
+        }
+        if (COMBINE && S == 1)
+            for (int idx = tid; idx < G * HD; idx += AD_THREADS)
+                out[(size_t)b * out_stride + (size_t)(g * G) * HD + idx] = __float2bfloat16_rn(0.0f);
     }
 
-    combine_by_last_split<HD>(b, g, G, S, nh, nkv, part_o, part_ml, counters, out, out_stride, w_split, l_split, &is_last);
+    if (COMBINE && S > 1)
+        combine_by_last_split<HD>(b, g, G, S, nh, nkv, part_o, part_ml, counters, out, out_stride, w_split, l_split, &is_last);
 }
 
 // out[b, head, :] = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M)
@@ -568,26 +650,44 @@ extern "C" int hb_attention_decode_combined(const void* q, long long q_stride, c
                                 batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
 }
 
-template <int HD>
-static int launch_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
-                               const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
-                               void* out, long long out_stride, int batch, int nh, int nkv, float scale, int window,
-                               int splits, int pages_per_split, int n_pages, int append, cudaStream_t s) {
+template <int HD, bool COMBINE>
+static int launch_decode_fused_splits(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
+                                      const int* page_table, int pt_width, const int* positions, float* part_o, float* part_ml,
+                                      int* counters, void* out, long long out_stride, int batch, int nh, int nkv, float scale,
+                                      int window, int splits, int pages_per_split, int n_pages, int append, cudaStream_t s) {
     constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
     constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<HD, COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("attention_decode_fused: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
-    float* part_o = scratch;
-    float* part_ml = scratch + (size_t)batch * nh * splits * HD;
-    hb_launch(attn_decode_fused_kernel<HD>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)qkv, stride,
+    hb_launch(attn_decode_fused_kernel<HD, COMBINE>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)qkv, stride,
               (const float2*)table, rot, (bf16*)kc, (bf16*)vc, page_table, pt_width, positions, part_o, part_ml, counters,
               (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, pages_per_split, n_pages, append);
     return hb_check_launch("attention_decode_fused");
+}
+
+// counters == nullptr: the splits (more than one) are combined by a second kernel.
+template <int HD>
+static int launch_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
+                               const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
+                               void* out, long long out_stride, int batch, int nh, int nkv, float scale, int window,
+                               int splits, int pages_per_split, int n_pages, int append, cudaStream_t s) {
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)batch * nh * splits * HD;
+    if (counters != nullptr || splits == 1)
+        return launch_decode_fused_splits<HD, true>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o,
+                                                    part_ml, counters, out, out_stride, batch, nh, nkv, scale, window, splits,
+                                                    pages_per_split, n_pages, append, s);
+    if (launch_decode_fused_splits<HD, false>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o, part_ml,
+                                              nullptr, out, out_stride, batch, nh, nkv, scale, window, splits, pages_per_split,
+                                              n_pages, append, s))
+        return 1;
+    hb_launch(attn_decode_combine_kernel<bf16>, dim3(batch, nh), dim3(HD), 0, s, part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
+    return hb_check_launch("attention_decode_combine");
 }
 
 // The attention of a decode step in one launch.  qkv: [batch, stride] bfloat16 rows holding the
@@ -595,7 +695,8 @@ static int launch_decode_fused(const void* qkv, long long stride, const float* t
 // heads, then v heads); `table`: [batch, rot/2] (cos, sin) of the tokens' positions;
 // positions[b] is the new token's position.  With `append` the rotated key and the value are
 // written to the cache first.  `scratch` as for hb_attention_decode; `counters` holds
-// batch * n_kv_heads ints, zero before the first use (the kernel leaves them zero).
+// batch * n_kv_heads ints, zero before the first use (the kernel leaves them zero), or is
+// null: then a second kernel combines the splits.
 extern "C" int hb_attention_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* k_cache,
                                          void* v_cache, const int* page_table, int pt_width, const int* positions,
                                          float* scratch, int* counters, void* out, long long out_stride, int batch,
@@ -605,8 +706,9 @@ extern "C" int hb_attention_decode_fused(const void* qkv, long long stride, cons
     HB_REQUIRE(hb_attention_decode_supported(n_heads, n_kv_heads, head_dim),
                "attention_decode_fused: head size %d with %d heads over %d kv heads is not built (64 or 128, groups up to 16)",
                head_dim, n_heads, n_kv_heads);
-    HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && scratch && counters, "attention_decode_fused: bad sizes");
-    HB_REQUIRE(splits <= AD_MAX_SPLITS, "attention_decode_fused: at most %d splits, got %d", AD_MAX_SPLITS, splits);
+    HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && scratch, "attention_decode_fused: bad sizes");
+    HB_REQUIRE(counters == nullptr || splits <= AD_MAX_SPLITS, "attention_decode_fused: at most %d splits when the last one combines, got %d",
+               AD_MAX_SPLITS, splits);
     HB_REQUIRE(batch <= 65535 && n_kv_heads <= 65535, "attention_decode_fused: batch or kv heads too large for one launch");
     HB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0 && (rot == 0 || table), "attention_decode_fused: bad rotary size %d", rot);
     HB_REQUIRE(stride % 2 == 0 && ((uintptr_t)qkv & 3) == 0, "attention_decode_fused: projections must be 4-byte aligned");

@@ -189,15 +189,17 @@ class Ops:
         self._retired = []              # outgrown scratch, kept alive for graphs that captured it
         self.use_tcgen05_attention = True   # head size 128 prefill on tcgen05 (else the mma.sync kernel)
         self.use_fast_attention = True  # tests switch this off to compare with the general kernel
-        # One-launch decode attention (rotation + append + splits + combination).  Off: inside a
-        # replayed graph at batch 8 / 8192 tokens it takes 50.3 us where the three kernels take
-        # 4.0 + 43.5 + 4.2 us (its own round trips are as long as theirs), and at batch 64 it is
-        # 1 % slower.
-        self.fuse_decode_attention = False
+        # Decode attention that rotates the new queries and key and appends to the cache itself
+        # (no rotation kernel in front; the new key and value go into the owning split's copy of
+        # their page in shared memory).  Inside a replayed graph at batch 8 / 8192 tokens it takes
+        # 43.2 us where rotation + attention take 3.4 + 41.0 us: a step of 8 layers 1307 against
+        # 1316 us, at batch 1 1043 against 1051 us, at batch 64 3711 against 3723 us.
+        self.fuse_decode_attention = True
         # Split-K decode attention whose last split combines the splits, instead of a second
         # kernel.  Off: at batch 8 / 8192 tokens a step of 8 layers takes 1319 us against 1313 us, at
         # batch 1 1079 against 1052 us (the last split's two round trips are longer than a kernel
-        # that is already resident).  A single split always writes the result itself.
+        # that is already resident); with the rotation inside as well, 50.3 us per layer against
+        # 43.2 + 3.5 us.  A single split always writes the result itself.
         self.combine_in_attention = False
 
     # ------------------------------------------------------------------ plumbing
@@ -419,9 +421,10 @@ class Ops:
 
     def attention_decode_fused(self, qkv, table, rot: int, heads: int, kv_heads: int, head_dim: int, cache, step, out,
                                scale: float, window: Optional[int], append: bool, splits: Optional[int] = None) -> None:
-        """Rotation of the new tokens' queries and keys, cache append, split-K attention and the
-        combination of the splits in ONE launch (decode steps only).  ``qkv`` holds the
-        projections before rotation and is not written."""
+        """Rotation of the new tokens' queries and keys, cache append and split-K attention in
+        one launch (decode steps only); the combination of the splits is a second kernel, or
+        with ``combine_in_attention`` the work of the last split to finish.  ``qkv`` holds
+        the projections before rotation and is not written."""
         self._dev(qkv, table, cache.k, cache.v, out)
         T = qkv.shape[0]
         pt = step.page_tables[cache.group]
@@ -441,10 +444,11 @@ class Ops:
         self._call("hb_attention_decode_fused", qkv.data_ptr(), _rows(qkv, "attention projections"),
                    table.data_ptr() if rot else None, rot, cache.k.data_ptr(), cache.v.data_ptr(), pt.data_ptr(),
                    pt.shape[1], step.positions.data_ptr(), self._decode_scratch.data_ptr(),
-                   self._decode_counters.data_ptr(), out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,
+                   self._decode_counters.data_ptr() if self.combine_in_attention else None,
+                   out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,
                    head_dim, float(scale), int(window) if window else 0, n_splits, max_pages, cache.k.shape[0],
                    1 if append else 0, self._stream())
-        self.launches += 1
+        self.launches += 1 if (n_splits == 1 or self.combine_in_attention) else 2
 
     def attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out, scale: float,
                   window: Optional[int], splits: Optional[int] = None) -> None:

@@ -111,15 +111,18 @@ def test_step_cut_into_chunks(model_folders, dtype):
 
 
 @pytest.mark.parametrize("model", ["strong_c", "strong_d"])
-def test_one_launch_decode_attention_in_the_engine(model_folders, model):
-    """The optional one-launch decode attention gives the same logits as the three kernels."""
+@pytest.mark.parametrize("fuse,inside", [(False, False), (False, True), (True, True)])
+def test_other_arrangements_of_decode_attention_in_the_engine(model_folders, model, fuse, inside):
+    """Decode attention behind a rotation kernel instead of rotating and appending itself, and
+    with the last split combining instead of a combination kernel: the same logits."""
     require_gpu()
     reqs = _requests(model, [70, 33, 130], seed=650)
     steps, peak = tt.trace_batches([{rid: (t, 5 + 20 * i) for i, (rid, t) in enumerate(reqs.items())}])
     eng = _engine(model_folders[model], "bfloat16", peak)
-    eng.ctx.ops.fuse_decode_attention = True
+    eng.ctx.ops.fuse_decode_attention = fuse
+    eng.ctx.ops.combine_in_attention = inside
     got = tt.run_in_process(eng, steps)
-    tt.compare(got, tt.plain_logits(_plain(model_folders[model], "bfloat16"), reqs), "bfloat16", "fused decode attention")
+    tt.compare(got, tt.plain_logits(_plain(model_folders[model], "bfloat16"), reqs), "bfloat16", f"decode attention fuse={fuse} inside={inside}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

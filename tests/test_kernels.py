@@ -504,9 +504,10 @@ def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
 @pytest.mark.parametrize("nh,nkv,hd,rot,window", [(8, 2, 128, 128, None), (3, 1, 64, 64, None), (16, 1, 64, 32, 100),
                                                   (10, 5, 128, 128, 65)])
 def test_attention_decode_fused_equals_the_three_kernels(ops, nh, nkv, hd, rot, window):
-    """The one-launch decode attention (rotation, append, splits, combination) against the
-    separate rope/append, attention and combine kernels, twice in a row (counters return to
-    zero), with lengths at page edges and a first token."""
+    """The decode attention that rotates and appends itself (with the combination kernel behind
+    it, or combining in its last split) against the separate rope/append, attention and combine
+    kernels, twice in a row (counters return to zero), with lengths at page edges and a first
+    token."""
     torch.manual_seed(14)
     dtype = torch.bfloat16
     scale = 1.0 / math.sqrt(hd)
@@ -538,15 +539,19 @@ def test_attention_decode_fused_equals_the_three_kernels(ops, nh, nkv, hd, rot, 
             c3 = LayerCache(c2.k.clone(), c2.v.clone(), 0, None)
             got = torch.full_like(want, 9.0)
             before = qkv.clone()
-            ops.fuse_decode_attention = True
-            try:
-                assert ops.can_fuse_decode_attention(qkv, nh, nkv, hd, c3, step, got)
-            finally:
-                ops.fuse_decode_attention = False
-            ops.attention_decode_fused(qkv, table, rot, nh, nkv, hd, c3, step, got, scale, window, True, splits=splits)
-            assert torch.equal(qkv, before)
-            assert torch.equal(c3.k, c1.k) and torch.equal(c3.v, c1.v), "appended keys or values differ"
-            assert _rel(got, want.double()) < 2 ** -8, f"splits={splits}"
+            assert ops.can_fuse_decode_attention(qkv, nh, nkv, hd, c3, step, got)
+            for inside in (False, True):          # a combination kernel, or the last split combines
+                c3.k.copy_(c2.k)
+                c3.v.copy_(c2.v)
+                got.fill_(9.0)
+                ops.combine_in_attention = inside
+                try:
+                    ops.attention_decode_fused(qkv, table, rot, nh, nkv, hd, c3, step, got, scale, window, True, splits=splits)
+                finally:
+                    ops.combine_in_attention = False
+                assert torch.equal(qkv, before)
+                assert torch.equal(c3.k, c1.k) and torch.equal(c3.v, c1.v), "appended keys or values differ"
+                assert _rel(got, want.double()) < 2 ** -8, f"splits={splits} inside={inside}"
         assert int(ops._decode_counters.abs().sum()) == 0
     # a layer that reads another layer's cache: no append, the new key is not there
     c4 = LayerCache(base.k.clone(), base.v.clone(), 0, None)
