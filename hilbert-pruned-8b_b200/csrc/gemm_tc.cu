@@ -324,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // TC_ADD_F32 with a split tile: the output's old values are requested now, by every
             // contributor, so that the one that turns out to be last need not wait for them
             // (nobody writes the tile before all contributors have counted themselves in)
-            constexpr int NV = BN <= 64 ? BN / 4 : 1;
+            constexpr int NV = BN <= 64 ? BN / 4 : 16;
             constexpr bool RES_AHEAD = MODE == TC_ADD_F32 && BN <= 32;
             float4 res[NV];
             const bool have_res = RES_AHEAD && !whole && (p.ldc & 3) == 0 && (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
@@ -386,48 +386,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 __threadfence();
                 if (et == 0) TL_EVENT(6);
             }
-            if (finish && !whole && BN <= 64) {
+            if (finish && !whole) {
                 // Sum of the partial tiles in K order with 16-byte loads: every load of one
                 // contributor is in flight at once, so the sum costs one L2 round trip per
                 // contributor (two are overlapped) instead of one per 16 tokens of each.
-                const float4* src4 = reinterpret_cast<const float4*>(p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM)) + et;
-                float4 acc[NV];
-#pragma unroll
-                for (int i = 0; i < NV; i++) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                // Token tiles above 64 go in groups of 64 tokens (registers).
+                constexpr int GROUP = BN <= 64 ? BN : 64, GV = GROUP / 4;
                 const int tw = et >> 5;
+#pragma unroll 1
+                for (int g0 = 0; g0 < BN; g0 += GROUP) {
+                    if (m0 + g0 >= p.M) break;
+                    const float4* src4 = reinterpret_cast<const float4*>(p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM) +
+                                                                         (size_t)g0 * TC_BM) + et;
+                    float4 acc[GV];
+#pragma unroll
+                    for (int i = 0; i < GV; i++) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 2
-                for (int z = 0; z < contributors; z++) {
-                    const float4* pz = src4 + (size_t)z * (BN * TC_BM / 4);
-                    float4 t[NV];
+                    for (int z = 0; z < contributors; z++) {
+                        const float4* pz = src4 + (size_t)z * (BN * TC_BM / 4);
+                        float4 t[GV];
 #pragma unroll
-                    for (int i = 0; i < NV; i++)
-                        t[i] = (m0 + i * 4 + tw < p.M) ? __ldcg(pz + i * TC_BM) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        for (int i = 0; i < GV; i++)
+                            t[i] = (m0 + g0 + i * 4 + tw < p.M) ? __ldcg(pz + i * TC_BM) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-                    for (int i = 0; i < NV; i++) {
-                        acc[i].x += t[i].x;
-                        acc[i].y += t[i].y;
-                        acc[i].z += t[i].z;
-                        acc[i].w += t[i].w;
+                        for (int i = 0; i < GV; i++) {
+                            acc[i].x += t[i].x;
+                            acc[i].y += t[i].y;
+                            acc[i].z += t[i].z;
+                            acc[i].w += t[i].w;
+                        }
                     }
+                    tc_emit_flat<MODE, GROUP>(p, m0 + g0, n0, acc, et, res, have_res);     // read ahead: one group only
                 }
-                tc_emit_flat<MODE, BN <= 64 ? BN : 4>(p, m0, n0, acc, et, res, have_res);
             } else if (finish) {
-                const float* src = p.partials + (size_t)tile * p.max_slots * (size_t)(BN * TC_BM);
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     if (m0 + c >= p.M) break;
                     float v[16];
-                    if (whole) {
-                        tmem_ld16(lane_addr + c, v);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) v[j] = 0.0f;
-                        for (int z = 0; z < contributors; z++) {
-                            const float* pz = src + (size_t)z * (BN * TC_BM);
-#pragma unroll
-                            for (int j = 0; j < 16; j++) v[j] += __ldcg(pz + (size_t)(c + j) * TC_BM + row);
-                        }
-                    }
+                    tmem_ld16(lane_addr + c, v);
                     tc_emit_chunk<MODE>(p, m0, n0, c, v, xchg, q, row, et);
                 }
             }
@@ -559,7 +555,11 @@ static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
     pl.kb_total = (K + TC_BK - 1) / TC_BK;
     const int sms = sm_count();
     const long long units = pl.tiles * pl.kb_total;
-    pl.stream_k = schedule == 2 || (schedule == 0 && pl.tiles_m == 1 && pl.bn <= 64);
+    // Few tiles: K is cut.  Tiles enough to fill the device run whole when there are several
+    // token tiles, or when the token tile is above 64: its partial tiles (64 KB and more) cost
+    // more than the last wave's idle SMs (gate/up product of 128 tokens: 65-74 us cut, 61 us whole).
+    const bool few = pl.tiles < sm_count();
+    pl.stream_k = schedule == 2 || (schedule == 0 && (few || (pl.tiles_m == 1 && pl.bn <= 64)));
     pl.split = 1;
     pl.cluster = 0;
     if (schedule == 3 || (schedule == 0 && pl.stream_k && pl.tiles >= sms)) {

@@ -264,6 +264,21 @@ template <int MODE, int BN>
 __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, const float4 (&acc)[BN / 4], int et,
                                              const float4 (&res)[BN / 4], bool have_res) {
     const int lane = et & 31, tw = et >> 5;
+    // TC_ADD_F32 without values read ahead: all loads of the old output first, then the stores
+    // (written one by one the compiler must keep each load behind the store before it: one
+    // round trip per token instead of one in all)
+    float4 old[MODE == TC_ADD_F32 ? BN / 4 : 1];
+    const bool old_here = MODE == TC_ADD_F32 && !have_res && (p.ldc & 3) == 0 && (((uintptr_t)p.out) & 15) == 0;
+    if (MODE == TC_ADD_F32 && old_here) {
+        const int n = n0 + lane * 4;
+#pragma unroll
+        for (int i = 0; i < BN / 4; i++) {
+            const int m = m0 + i * 4 + tw;
+            old[MODE == TC_ADD_F32 ? i : 0] = (m < p.M && n + 4 <= p.N)
+                ? __ldcg(reinterpret_cast<const float4*>((const float*)p.out + (size_t)m * p.ldc + n))
+                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    }
 #pragma unroll
     for (int i = 0; i < BN / 4; i++) {
         const int m = m0 + i * 4 + tw;                      // uniform in a warp
@@ -304,7 +319,8 @@ __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, 
                 float* o = (float*)p.out + off;
                 if (n + 4 <= p.N && (((uintptr_t)o) & 15) == 0) {
                     float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    if (MODE == TC_ADD_F32) r = have_res ? res[i] : __ldcg(reinterpret_cast<const float4*>(o));
+                    if (MODE == TC_ADD_F32)
+                        r = have_res ? res[i] : old_here ? old[MODE == TC_ADD_F32 ? i : 0] : __ldcg(reinterpret_cast<const float4*>(o));
                     *reinterpret_cast<float4*>(o) = make_float4(r.x + v[0], r.y + v[1], r.z + v[2], r.w + v[3]);
                 } else {
                     for (int e = 0; e < 4 && n + e < p.N; e++) o[e] = (MODE == TC_ADD_F32 ? o[e] : 0.0f) + v[e];

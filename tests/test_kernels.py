@@ -220,7 +220,8 @@ def test_gemm_tensor_core_against_plain_and_general(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(8, 512, 1024), (1, 384, 4096), (64, 256, 2048), (5, 100, 416), (40, 4096, 512),
-                                   (16, 20000, 256), (200, 384, 1024), (8, 28672, 512), (3, 19000, 64)])
+                                   (16, 20000, 256), (200, 384, 1024), (8, 28672, 512), (3, 19000, 64),
+                                   (100, 512, 2048), (130, 4096, 1024), (256, 640, 4096), (300, 384, 2048)])
 def test_gemm_tensor_core_stream_k_and_tiles(ops, M, N, K):
     """The work splits of the tensor-core kernel: stream-K (partial tiles in scratch, summed
     in K order by the last contributor), whole tiles round-robin (several per CTA), and cut
