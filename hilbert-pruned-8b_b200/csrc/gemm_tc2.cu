@@ -41,6 +41,8 @@
 // -> forwarder -> MMA is twice as long as TMA's.  (A loader thread that arrives remotely
 // itself waits, with the release, for all its copies in flight: 261 us.)
 #define T2_STAGES(MODE) 6
+// SwiGLU epilogue: gates and ups handed over [2][32][64] float32, products [64][64] bfloat16
+#define T2_XCHG_BYTES (2 * 32 * 64 * 4 + 64 * 64 * 2)
 
 template <int MODE, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
@@ -48,7 +50,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     constexpr bool SWIGLU = MODE == TC_SWIGLU_BF16;
     constexpr int FEAT = SWIGLU ? 64 : TC_BM;                     // output features per CTA
     constexpr int W_BYTES = TC_BM * TC_BK * 2;
-    constexpr int XCHG = SWIGLU ? TC_XCHG_BYTES : 0;
+    constexpr int XCHG = SWIGLU ? T2_XCHG_BYTES : 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* xchg = smem + STAGES * T2_STAGE_BYTES;
@@ -226,6 +228,55 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                                 if (m0 + c + 16 * u + j < p.M) po[(size_t)(16 * u + j) * p.ldc] = r[u][j] + v[u][j];
                     }
                 }
+            } else if (MODE == TC_SWIGLU_BF16) {
+                // 64 tokens at a time.  Rows 0..63 of this CTA's half tile are gate rows, rows
+                // 64..127 the up rows of the same 64 features.  The gate threads hand the gates
+                // of tokens 32..63 to the up threads and take the ups of tokens 0..31 from them
+                // (through shared memory), so that all four warps share the activation; the
+                // products go to shared memory as bfloat16 [token][feature] and leave with
+                // 16-byte stores.  Two block barriers per 64 tokens.
+                float* xf = (float*)xchg;                                  // [2][32 tokens][64 features] float32
+                bf16* yb = (bf16*)(xchg + 2 * 32 * 64 * 4);                // [64 tokens][64 features]
+                const bool gate_thread = row < 64;
+                const int f = row & 63;
+#pragma unroll 1
+                for (int c = 0; c < T2_TOKENS; c += 64) {
+                    if (m0 + c >= p.M) break;
+                    float v[4][16];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) tmem_ld16(lane_addr + c + 16 * u, v[u]);
+                    // gates of tokens 32..63 -> xf[0], ups of tokens 0..31 -> xf[1]
+                    float* mine = xf + (gate_thread ? 0 : 32 * 64);
+#pragma unroll
+                    for (int u = 0; u < 2; u++)
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            mine[(16 * u + j) * 64 + f] = gate_thread ? v[2 + u][j] : v[u][j];
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const float* theirs = xf + (gate_thread ? 32 * 64 : 0);
+#pragma unroll
+                    for (int u = 0; u < 2; u++)
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const float other = theirs[(16 * u + j) * 64 + f];
+                            const float y = gate_thread ? silu_f32(v[u][j]) * other : silu_f32(other) * v[2 + u][j];
+                            yb[((gate_thread ? 0 : 32) + 16 * u + j) * 64 + f] = __float2bfloat16_rn(y);
+                        }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int idx = et + 128 * k, r = idx >> 3, ch = idx & 7;     // token of the group, 8-feature piece
+                        const int m = m0 + c + r, n = n0 + ch * 8;
+                        if (m < p.M && n < p.N) {
+                            bf16* o = (bf16*)p.out + (size_t)m * p.ldc + n;
+                            if (n + 8 <= p.N) {
+                                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(yb + r * 64 + ch * 8);
+                            } else {
+                                for (int e = 0; e < p.N - n; e++) o[e] = yb[r * 64 + ch * 8 + e];
+                            }
+                        }
+                    }
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < T2_TOKENS; c += 16) {
@@ -251,7 +302,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 template <int MODE>
 static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int pairs, cudaStream_t s) {
     constexpr int STAGES = T2_STAGES(MODE);
-    constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? TC_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? T2_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
     static_assert(SMEM <= 227 * 1024, "tile pipeline does not fit shared memory");
     static bool attr_set = false;
     if (!attr_set) {
@@ -269,7 +320,7 @@ static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& ma, const TcPara
 template <int MODE>
 static int query_pairs() {
     constexpr int STAGES = T2_STAGES(MODE);
-    constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? TC_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? T2_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
     cudaFuncSetAttribute(gemm_tc2_kernel<MODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     cudaLaunchConfig_t cfg = {};
     int sms = 0, dev = 0;
