@@ -35,11 +35,12 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     constexpr int KSTEPS = HD / 16;
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int head = blockIdx.y, g = head / (nh / nkv);
+    const int head = blockIdx.x, g = head / (nh / nkv);
 
-    // which sequence and which block of its new tokens this CTA serves
-    // blocks are taken from the back: late query blocks see the most keys and should start first
-    int b = 0, blk = gridDim.x - 1 - blockIdx.x;
+    // which sequence and which block of its new tokens this CTA serves.  Blocks are taken
+    // from the back and the heads are the fast grid index: the query blocks that see the most
+    // keys start first, for all heads
+    int b = 0, blk = gridDim.y - 1 - blockIdx.y;
     for (; b < n_seqs; b++) {
         const int nb = (seq_start[b + 1] - seq_start[b] + AP_ROWS - 1) / AP_ROWS;
         if (blk < nb) break;
@@ -221,7 +222,7 @@ static int launch_prefill(const void* q, long long q_stride, const void* kc, con
         if (e != cudaSuccess) return hb_fail("attention_prefill: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
-    dim3 grid(q_blocks, nh);
+    dim3 grid(nh, q_blocks);
     hb_launch(attn_prefill_kernel<HD>, dim3(grid), dim3(AP_THREADS), SMEM, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
                                                            pt_width, seq_start, seq_pos0, (bf16*)out, out_stride, n_seqs, nh, nkv,
                                                            scale * AP_LOG2E, window, n_pages);
@@ -239,7 +240,7 @@ extern "C" int hb_attention_prefill(const void* q, long long q_stride, const voi
     HB_REQUIRE(hb_attention_prefill_supported(n_heads, n_kv_heads, head_dim),
                "attention_prefill: head size %d with %d heads over %d kv heads is not built (64 or 128)", head_dim, n_heads,
                n_kv_heads);
-    HB_REQUIRE(n_seqs > 0 && q_blocks > 0 && n_heads <= 65535, "attention_prefill: bad sizes");
+    HB_REQUIRE(n_seqs > 0 && q_blocks > 0 && q_blocks <= 65535, "attention_prefill: bad sizes");
     HB_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)q & 3) == 0 && ((uintptr_t)out & 3) == 0,
                "attention_prefill: queries and output must be 4-byte aligned");
     HB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_prefill: cache must be 16-byte aligned");
