@@ -142,10 +142,13 @@ struct TcSchedule {
 // full (epilogue), 5 partial tile written and fenced, 6 tile counter known, 7 tile emitted,
 // 8 block end.
 //
-// CLUSTER (few tokens, every tile cut into `split` <= 8 equal K ranges): the CTAs of a tile are
-// one thread-block cluster.  Each writes its partial tile into the shared memory of the
+// CLUSTER (up to 64 tokens, every tile cut into `split` <= 8 equal K ranges): the CTAs of a tile
+// are one thread-block cluster.  Each writes its partial tile into the shared memory of the
 // cluster's first CTA (st.shared::cluster), one cluster barrier later that CTA sums the partial
 // tiles in K order and runs the epilogue: no scratch in global memory, no fence, no counter.
+// With 16 tokens the partial tiles have a region of their own; with 32 and 64 they lie over
+// the first CTA's pipeline stages, which a first cluster barrier declares free (every CTA's
+// MMAs have finished).
 template <int BN, int MODE, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
@@ -154,8 +157,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* xchg = smem + STAGES * L::STAGE_BYTES;
-    uint8_t* xpart = xchg + L::XCHG_BYTES;                     // CLUSTER: partial tiles [part][token][row] (first CTA's copy is used)
-    uint64_t* bars = (uint64_t*)(xpart + (CLUSTER ? TC_MAX_CLUSTER * L::PART_BYTES : 0));   // full[S], empty[S], acc_full[2], acc_empty[2]
+    // CLUSTER: partial tiles [part][token][row] in the first CTA's shared memory: a region of
+    // their own (16 tokens), or over its pipeline stages (more tokens: no room beside them)
+    constexpr bool RING = CLUSTER && BN > 16;
+    uint8_t* xpart = RING ? smem : xchg + L::XCHG_BYTES;
+    uint64_t* bars = (uint64_t*)(xchg + L::XCHG_BYTES + (CLUSTER && !RING ? TC_MAX_CLUSTER * L::PART_BYTES : 0));   // full[S], empty[S], acc_full[2], acc_empty[2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* last_flag = (int*)(tmem_slot + 2);
@@ -222,6 +228,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // CLUSTER: what the first CTA's epilogue threads carry across the cluster barrier
     constexpr int CL_NV = BN <= 64 ? BN / 4 : 1;
     float4 cl_res[CL_NV];
+    float cl_row[CLUSTER && BN > 16 ? BN : 16];    // RING: this thread's weight row of the partial tile, all tokens
     int cl_m0 = 0, cl_n0 = 0;
     bool cl_have_res = false, cl_done = false;
     const int et = (warp - 2) * 32 + lane;         // 0..127 among the epilogue threads (warps 2..5)
@@ -338,19 +345,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
             if (CLUSTER) {
-                // partial tile into the first CTA's shared memory, slot = this CTA's K range
                 cl_m0 = m0;
                 cl_n0 = n0;
                 cl_have_res = have_res;
 #pragma unroll
                 for (int i = 0; i < NV; i++) cl_res[i] = res[i];
-                const uint32_t dst = mapa_shared(smem_u32(xpart) + (blockIdx.x % p.split) * L::PART_BYTES, 0);
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 16) {
-                    float v[16];
-                    tmem_ld16(lane_addr + c, v);
+                if (RING) {
+                    // this CTA's row of the partial tile stays in registers until the first
+                    // CTA's pipeline is free (the first cluster barrier, below)
 #pragma unroll
-                    for (int j = 0; j < 16; j++) st_cluster_f32(dst + ((c + j) * TC_BM + row) * 4, v[j]);
+                    for (int c = 0; c < BN; c += 16) tmem_ld16(lane_addr + c, *reinterpret_cast<float(*)[16]>(cl_row + (RING ? c : 0)));
+                } else {
+                    // partial tile into the first CTA's shared memory, slot = this CTA's K range
+                    const uint32_t dst = mapa_shared(smem_u32(xpart) + (blockIdx.x % p.split) * L::PART_BYTES, 0);
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 16) {
+                        float v[16];
+                        tmem_ld16(lane_addr + c, v);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) st_cluster_f32(dst + ((c + j) * TC_BM + row) * 4, v[j]);
+                    }
                 }
                 tc_fence_before();
                 mbar_arrive(acce0 + 8 * buf);
@@ -437,8 +451,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     if (CLUSTER) {
         // Every thread of every CTA of the cluster gets here exactly once (the loops above are
-        // left by `break`, never by `return`).  After the barrier the partial tiles of all K
-        // ranges lie in the first CTA's shared memory.
+        // left by `break`, never by `return`).  RING: after a first barrier every CTA's copies
+        // have landed and its MMAs have finished (its epilogue threads have read the
+        // accumulator), so the first CTA's stages can take the partial tiles.  After the
+        // (second) barrier the partial tiles of all K ranges lie in the first CTA's shared memory.
+        if (RING) {
+            cluster_sync_all();
+            if (warp >= 2 && cl_done) {
+                const int q = warp & 3, row = q * 32 + lane;
+                const uint32_t dst = mapa_shared(smem_u32(xpart) + (blockIdx.x % p.split) * L::PART_BYTES, 0);
+#pragma unroll
+                for (int c = 0; c < (RING ? BN : 1); c++) st_cluster_f32(dst + (c * TC_BM + row) * 4, cl_row[c]);
+            }
+        }
         cluster_sync_all();
         if (warp >= 2 && blockIdx.x % p.split == 0 && cl_done && !*abort_flag) {
             const int parts = (p.kb_total + ((p.kb_total + p.split - 1) / p.split) - 1) / ((p.kb_total + p.split - 1) / p.split);
@@ -542,8 +567,9 @@ struct TcPlan {
     int bn, feat, tiles_m, tiles_n, kb_total, grid, stream_k, max_slots, split, cluster;
     long long scratch_floats, tiles;
 };
-// whether `tiles` clusters of `size` CTAs of the cluster variant can be resident at once
-static bool clusters_fit_mode(int mode, int size, long long tiles);
+// whether `tiles` clusters of `size` CTAs of the cluster variant for token tile `bn` can be
+// resident at once, and whether `size` partial tiles fit over its pipeline stages
+static bool clusters_fit_mode(int bn, int mode, int size, long long tiles);
 
 static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
     TcPlan pl;
@@ -585,9 +611,9 @@ static TcPlan make_plan(int M, int N, int K, int mode, int schedule) {
             // about four K blocks instead of six), if all clusters can be resident at once;
             // up to a fifth fewer ranges than SMs allow are accepted for that.
             bool cluster = false;
-            if (pl.bn == 16 && clusters_enabled())
+            if (pl.bn <= 64 && clusters_enabled())
                 for (long long s = split < TC_MAX_CLUSTER ? split : TC_MAX_CLUSTER; s >= 2 && s * 5 >= split * 4; s--)
-                    if (pl.kb_total / s >= 4 && clusters_fit_mode(mode, (int)s, pl.tiles)) {
+                    if (pl.kb_total / s >= 4 && clusters_fit_mode(pl.bn, mode, (int)s, pl.tiles)) {
                         split = s;
                         cluster = true;
                         break;
@@ -625,8 +651,11 @@ extern "C" long long hb_gemm_tc_tiles(int M, int N, int mode) { return make_plan
 template <int BN, int MODE, int STAGES, bool CLUSTER>
 struct TcLaunch {
     using L = TcLayout<BN, MODE>;
-    static constexpr int SMEM = STAGES * L::STAGE_BYTES + L::XCHG_BYTES + (CLUSTER ? TC_MAX_CLUSTER * L::PART_BYTES : 0) +
+    static constexpr int SMEM = STAGES * L::STAGE_BYTES + L::XCHG_BYTES + (CLUSTER && BN == 16 ? TC_MAX_CLUSTER * L::PART_BYTES : 0) +
                                 (2 * STAGES + 4) * 8 + 16 + 1024;
+    // CLUSTER: the most K ranges of a tile: what fits over the first CTA's stages (above 16 tokens)
+    static constexpr int MAX_PARTS = BN == 16 || STAGES * L::STAGE_BYTES / L::PART_BYTES >= TC_MAX_CLUSTER
+                                         ? TC_MAX_CLUSTER : STAGES * L::STAGE_BYTES / L::PART_BYTES;
     static_assert(SMEM <= 227 * 1024, "tile pipeline does not fit shared memory");
     static int prepare() {
         static bool attr_set = false;
@@ -668,45 +697,64 @@ struct TcLaunch {
     }
 };
 
-// The cluster variant of the 16-token kernel: fewer stages, room for the partial tiles.
-template <int MODE>
-using TcClusterLaunch = TcLaunch<16, MODE, MODE == TC_SWIGLU_BF16 ? 7 : 8, true>;
+// The cluster variants.  16 tokens: fewer stages, room for the partial tiles beside them (a
+// step of 8 layers at batch 8: 1305 us; with the partial tiles over 11 stages and the second
+// cluster barrier that needs: 1327 us).  32 and 64 tokens: the stages of the plain kernels.
+template <int BN, int MODE>
+using TcClusterLaunch = TcLaunch<BN, MODE, BN == 16 ? (MODE == TC_SWIGLU_BF16 ? 7 : 8) : BN == 32 ? 10 : 8, true>;
 
-template <int MODE>
+template <int BN, int MODE>
 static bool clusters_fit(int size, long long tiles) {
     static int cached[TC_MAX_CLUSTER + 1] = {0};      // 0: not asked yet, -1: none
-    if (size < 2 || size > TC_MAX_CLUSTER) return false;
+    if (size < 2 || size > TcClusterLaunch<BN, MODE>::MAX_PARTS) return false;
     if (cached[size] == 0) {
-        const int n = TcClusterLaunch<MODE>::resident_clusters(size);
+        const int n = TcClusterLaunch<BN, MODE>::resident_clusters(size);
         cached[size] = n > 0 ? n : -1;
     }
     return cached[size] >= tiles;
 }
 
-// How many clusters of `size` CTAs of the cluster variant can be resident at once (diagnostics
-// and tests; 0 if the size is not built).
+// How many clusters of `size` CTAs of the 16-token cluster variant can be resident at once
+// (diagnostics and tests; 0 if the size is not built).
 extern "C" int hb_gemm_tc_resident_clusters(int mode, int size) {
     if (size < 2 || size > TC_MAX_CLUSTER) return 0;
     switch (mode & 3) {
-        case TC_STORE_BF16: return TcClusterLaunch<TC_STORE_BF16>::resident_clusters(size);
-        case TC_STORE_F32: return TcClusterLaunch<TC_STORE_F32>::resident_clusters(size);
-        case TC_ADD_F32: return TcClusterLaunch<TC_ADD_F32>::resident_clusters(size);
-        default: return TcClusterLaunch<TC_SWIGLU_BF16>::resident_clusters(size);
+        case TC_STORE_BF16: return TcClusterLaunch<16, TC_STORE_BF16>::resident_clusters(size);
+        case TC_STORE_F32: return TcClusterLaunch<16, TC_STORE_F32>::resident_clusters(size);
+        case TC_ADD_F32: return TcClusterLaunch<16, TC_ADD_F32>::resident_clusters(size);
+        default: return TcClusterLaunch<16, TC_SWIGLU_BF16>::resident_clusters(size);
     }
 }
 
-static bool clusters_fit_mode(int mode, int size, long long tiles) {
+template <int BN>
+static bool clusters_fit_bn(int mode, int size, long long tiles) {
     switch (mode & 3) {
-        case TC_STORE_BF16: return clusters_fit<TC_STORE_BF16>(size, tiles);
-        case TC_STORE_F32: return clusters_fit<TC_STORE_F32>(size, tiles);
-        case TC_ADD_F32: return clusters_fit<TC_ADD_F32>(size, tiles);
-        default: return clusters_fit<TC_SWIGLU_BF16>(size, tiles);
+        case TC_STORE_BF16: return clusters_fit<BN, TC_STORE_BF16>(size, tiles);
+        case TC_STORE_F32: return clusters_fit<BN, TC_STORE_F32>(size, tiles);
+        case TC_ADD_F32: return clusters_fit<BN, TC_ADD_F32>(size, tiles);
+        default: return clusters_fit<BN, TC_SWIGLU_BF16>(size, tiles);
     }
+}
+
+static bool clusters_fit_mode(int bn, int mode, int size, long long tiles) {
+    switch (bn) {
+        case 16: return clusters_fit_bn<16>(mode, size, tiles);
+        case 32: return clusters_fit_bn<32>(mode, size, tiles);
+        case 64: return clusters_fit_bn<64>(mode, size, tiles);
+    }
+    return false;
 }
 
 template <int MODE>
 static int dispatch_bn(int bn, bool cluster, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
-    if (cluster) return TcClusterLaunch<MODE>::launch(mw, ma, prm, grid, s);
+    if (cluster) {
+        switch (bn) {
+            case 16: return TcClusterLaunch<16, MODE>::launch(mw, ma, prm, grid, s);
+            case 32: return TcClusterLaunch<32, MODE>::launch(mw, ma, prm, grid, s);
+            case 64: return TcClusterLaunch<64, MODE>::launch(mw, ma, prm, grid, s);
+        }
+        return hb_fail("gemm_tc: no cluster variant for token tile %d", bn);
+    }
     switch (bn) {
         case 16: return TcLaunch<16, MODE, 11, false>::launch(mw, ma, prm, grid, s);
         case 32: return TcLaunch<32, MODE, 10, false>::launch(mw, ma, prm, grid, s);
