@@ -44,6 +44,7 @@ int hb_attention_general(const void* q, int q_dtype, long long q_stride, const v
                          const int* positions, void* out, int out_dtype, long long out_stride, int n_tokens,
                          int n_heads, int n_kv_heads, int head_dim, float scale, int window, void* stream);
 int hb_attention_decode_supported(int n_heads, int n_kv_heads, int head_dim);
+int hb_attention_decode_ctas_per_sm(int head_dim);
 long long hb_attention_decode_scratch_floats(int batch, int n_heads, int head_dim, int splits);
 int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                         const int* page_table, int pt_width, const int* positions, float* scratch, void* out,

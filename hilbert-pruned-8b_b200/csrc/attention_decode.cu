@@ -670,6 +670,31 @@ static int launch_decode_fused_splits(const void* qkv, long long stride, const f
     return hb_check_launch("attention_decode_fused");
 }
 
+template <int HD>
+static int decode_ctas_per_sm() {
+    constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
+    constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
+    constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
+    if (cudaFuncSetAttribute(attn_decode_fused_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_fused_kernel<HD, false>, AD_THREADS, SMEM) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+// How many CTAs of the split-K decode attention one SM holds at once (0: head size not built or
+// the query failed): what the host sizes the number of splits with.
+extern "C" int hb_attention_decode_ctas_per_sm(int head_dim) {
+    if (head_dim == 128) return decode_ctas_per_sm<128>();
+    if (head_dim == 64) return decode_ctas_per_sm<64>();
+    return 0;
+}
+
 // counters == nullptr: the splits (more than one) are combined by a second kernel.
 template <int HD>
 static int launch_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,

@@ -82,6 +82,7 @@ def load_library():
         lib.hb_gemm_tc2_resident_pairs.argtypes, lib.hb_gemm_tc2_resident_pairs.restype = [_c_int], _c_int
         for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported", "hb_attention_prefill_tc_supported"):
             getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
+        lib.hb_attention_decode_ctas_per_sm.argtypes, lib.hb_attention_decode_ctas_per_sm.restype = [_c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
         lib.hb_attention_decode_scratch_floats.restype = _c_ll
         _lib = lib
@@ -187,6 +188,7 @@ class Ops:
         self._decode_scratch = torch.empty(4 << 20, dtype=torch.float32, device=self.device)
         self._decode_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
         self._retired = []              # outgrown scratch, kept alive for graphs that captured it
+        self._splits_cache = {}
         self.use_tcgen05_attention = True   # head size 128 prefill on tcgen05 (else the mma.sync kernel)
         self.use_fast_attention = True  # tests switch this off to compare with the general kernel
         # Decode attention that rotates the new queries and key and appends to the cache itself
@@ -403,11 +405,32 @@ class Ops:
         self.silu_mul(gu, act)
 
     # ------------------------------------------------------------------ attention
-    def decode_splits_for(self, batch: int, kv_heads: int, max_pages: int) -> int:
-        """Key splits of decode attention: at most two CTAs per SM in one wave, at least eight
-        pages per split, at most 16 splits (measured: more splits cost more in the combine
-        than they gain)."""
-        return max(1, min(2 * self.sm_count // max(1, batch * kv_heads), -(-max_pages // 8), 16))
+    def decode_splits_for(self, batch: int, kv_heads: int, max_pages: int, head_dim: int = 128) -> int:
+        """Key splits of decode attention: at most 16, at least eight pages each (measured: more
+        splits cost more in the combine than they gain).  One wave of the resident CTAs (two
+        per SM at head size 128) if that fills the device: batch 8 at 8192 tokens takes
+        4 splits.  Where one wave would leave a third of the device idle (batch 24: 192 CTAs)
+        or a second wave would (batch 48: 384 CTAs), the splits that fill whole waves best, of
+        32 pages or more each (batch 24 and 48: 3 splits, 12 % of a step at batch 48)."""
+        key = (batch, kv_heads, max_pages, head_dim)
+        hit = self._splits_cache.get(key)
+        if hit is not None:
+            return hit
+        slots = self.sm_count * max(1, self.lib.hb_attention_decode_ctas_per_sm(head_dim) or 2)
+        ctas1 = max(1, batch * kv_heads)
+        limit = max(1, min(16, -(-max_pages // 8)))
+
+        def fill(s):                      # share of the waves' CTA slots that have work
+            ctas = ctas1 * s
+            return ctas / (-(-ctas // slots) * slots)
+
+        best = max(1, min(slots // ctas1, limit))
+        if fill(best) < 0.8:
+            for s in range(1, limit + 1):
+                if -(-max_pages // s) >= 32 and fill(s) - 0.01 * s > fill(best) - 0.01 * best + 0.1:
+                    best = s
+        self._splits_cache[key] = best
+        return best
 
     def can_fuse_decode_attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out) -> bool:
         """Whether ``attention_decode_fused`` takes this step: one token per sequence,
@@ -435,7 +458,7 @@ class Ops:
         if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim):
             raise KernelError("attention: cache layer shape does not match the heads")
         max_pages = (step.max_len + 63) // 64
-        n_splits = splits if splits is not None else self.decode_splits_for(T, kv_heads, max_pages)
+        n_splits = splits if splits is not None else self.decode_splits_for(T, kv_heads, max_pages, head_dim)
         n_splits = max(1, min(n_splits, max_pages))
         need = self.lib.hb_attention_decode_scratch_floats(T, heads, head_dim, n_splits)
         if need > self._decode_scratch.numel():
@@ -466,7 +489,7 @@ class Ops:
                 and out.dtype == torch.bfloat16 and cache.k.is_contiguous() and cache.v.is_contiguous())
         if fast and step.is_decode and self.lib.hb_attention_decode_supported(heads, kv_heads, head_dim):
             max_pages = (step.max_len + 63) // 64
-            n_splits = splits if splits is not None else self.decode_splits_for(T, kv_heads, max_pages)
+            n_splits = splits if splits is not None else self.decode_splits_for(T, kv_heads, max_pages, head_dim)
             n_splits = max(1, min(n_splits, max_pages))
             need = self.lib.hb_attention_decode_scratch_floats(T, heads, head_dim, n_splits)
             if need > self._decode_scratch.numel():

@@ -503,6 +503,23 @@ def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
         assert _rel(out, gen.double()) < 2 ** -7
 
 
+def test_decode_attention_split_choice(ops):
+    """The number of key splits: one wave of CTAs that fills the device where there is one, whole
+    waves where one split per (sequence, kv head) would leave a third of a wave idle, never
+    fewer than eight pages per split, never more than 16 splits."""
+    per_sm = ops.lib.hb_attention_decode_ctas_per_sm(128)
+    assert per_sm >= 1 and ops.lib.hb_attention_decode_ctas_per_sm(64) >= per_sm and ops.lib.hb_attention_decode_ctas_per_sm(80) == 0
+    slots = ops.sm_count * per_sm
+    for batch, kv, pages in [(1, 8, 128), (8, 8, 128), (8, 8, 4), (24, 8, 128), (48, 8, 128), (64, 8, 128), (3, 1, 1000), (500, 8, 40)]:
+        s = ops.decode_splits_for(batch, kv, pages, 128)
+        assert 1 <= s <= 16 and (s == 1 or -(-pages // s) >= 8), (batch, kv, pages, s)
+        ctas = batch * kv * s
+        if batch * kv <= slots // 2 and pages >= 16 * (slots // (batch * kv)):
+            assert ctas > slots // 2 or s == 16, (batch, kv, pages, s)           # few sequences with long caches fill the device
+    if ops.sm_count == 148 and per_sm == 2:
+        assert [ops.decode_splits_for(b, 8, 128, 128) for b in (8, 16, 32, 48, 64)] == [4, 2, 1, 2, 1]
+
+
 @pytest.mark.parametrize("nh,nkv,hd,rot,window", [(8, 2, 128, 128, None), (3, 1, 64, 64, None), (16, 1, 64, 32, 100),
                                                   (10, 5, 128, 128, 65)])
 def test_attention_decode_fused_equals_the_three_kernels(ops, nh, nkv, hd, rot, window):
