@@ -194,8 +194,9 @@ class Ops:
         # Decode attention that rotates the new queries and key and appends to the cache itself
         # (no rotation kernel in front; the new key and value go into the owning split's copy of
         # their page in shared memory).  Inside a replayed graph at batch 8 / 8192 tokens it takes
-        # 43.2 us where rotation + attention take 3.4 + 41.0 us: a step of 8 layers 1307 against
-        # 1316 us, at batch 1 1043 against 1051 us, at batch 64 3711 against 3723 us.
+        # 43.2 us where rotation + attention take 3.4 + 41.0 us; alternating runs on one GPU, a step
+        # of 8 layers: 1310 against 1312 us, at batch 1 1046 against 1047 us, 1B sizes 613 against
+        # 616 us.  One launch less, the time of the hand-over between kernels stays.
         self.fuse_decode_attention = True
         # Split-K decode attention whose last split combines the splits, instead of a second
         # kernel.  Off: at batch 8 / 8192 tokens a step of 8 layers takes 1319 us against 1313 us, at
