@@ -247,6 +247,17 @@ __device__ __forceinline__ void combine_by_last_split(int b, int g, int G, int S
     }
 }
 
+// The pages [p_begin, p_end) that split z of S takes of a sequence whose keys lo .. len-1 count:
+// equal shares of THIS sequence's pages, not of the longest sequence's or of the page table's
+// width, so that every split has work whatever the length (a sequence a little above half the
+// table's width would leave half the splits empty otherwise).
+__device__ __forceinline__ void split_pages(int z, int S, int lo, int len, int& p_begin, int& p_end, int& per_split) {
+    const int first = lo / HB_PAGE_TOKENS, last = (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS;
+    per_split = max(1, (last - first + S - 1) / S);
+    p_begin = first + z * per_split;
+    p_end = min(p_begin + per_split, last);
+}
+
 // COMBINE: the last split of a (sequence, kv head) to finish also combines the splits (no
 // second kernel); with one split the result goes straight to `out`.
 template <int HD, bool COMBINE>
@@ -254,7 +265,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                    const int* __restrict__ page_table, int pt_width, const int* __restrict__ positions,
                    float* part_o, float* part_ml, int nh, int nkv, float scale_log2e,
-                   int window, int pages_per_split, int n_pages, int* counters, bf16* out, long long out_stride) {
+                   int window, int n_pages, int* counters, bf16* out, long long out_stride) {
     __shared__ int is_last;
     __shared__ float w_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];
     __shared__ float l_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];
@@ -268,8 +279,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
     const int G = nh / nkv;
     const int len = positions[b] + 1;
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;
-    const int p_begin = max(z * pages_per_split, lo / HB_PAGE_TOKENS);
-    const int p_end = min((z + 1) * pages_per_split, (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS);
+    int p_begin, p_end, pages_per_split;
+    split_pages(z, S, lo, len, p_begin, p_end, pages_per_split);
     const int* pt = page_table + (size_t)b * pt_width;
 
     if (p_begin >= p_end) {                       // nothing to read: an empty partial
@@ -353,7 +364,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                          bf16* kc, bf16* vc, const int* __restrict__ page_table, int pt_width,
                          const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
                          int* __restrict__ counters, bf16* __restrict__ out, long long out_stride, int nh, int nkv,
-                         float scale_log2e, int window, int pages_per_split, int n_pages, int append) {
+                         float scale_log2e, int window, int n_pages, int append) {
     pdl_trigger();
     constexpr int KSTEPS = HD / 16;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -367,8 +378,8 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
     const int G = nh / nkv;
     const int pos = positions[b], len = pos + 1;
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;
-    const int p_begin = max(z * pages_per_split, lo / HB_PAGE_TOKENS);
-    const int p_end = min((z + 1) * pages_per_split, (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS);
+    int p_begin, p_end, pages_per_split;
+    split_pages(z, S, lo, len, p_begin, p_end, pages_per_split);
     const int* pt = page_table + (size_t)b * pt_width;
     // what the kernels in front wrote (projections, table) is read after the wait only, through
     // pointers that the compiler cannot take for memory that never changes
@@ -383,7 +394,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
     // value to the cache, for later steps.  This step reads them from shared memory: the page is
     // requested with all the others before the wait, and its row of the new position is
     // overwritten when it has arrived.  The loads are requested together with the queries'.
-    const bool owner = append && z == (pos / HB_PAGE_TOKENS) / pages_per_split;
+    const bool owner = append && z == (pos / HB_PAGE_TOKENS - lo / HB_PAGE_TOKENS) / pages_per_split;
     const int half = rot >> 1;
     float kx1 = 0.0f, kx2 = 0.0f;               // one pair of the key per thread (tid < rot/2), or
     float2 kcs = make_float2(1.0f, 0.0f);       // one element beyond the rotated ones (tid >= rot)
@@ -568,7 +579,7 @@ template <int HD, bool COMBINE>
 static int launch_decode_splits(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
                                 int pt_width, const int* positions, float* part_o, float* part_ml, int* counters, void* out,
                                 long long out_stride, int batch, int nh, int nkv, float scale, int window, int splits,
-                                int pages_per_split, int n_pages, cudaStream_t s) {
+                                int n_pages, cudaStream_t s) {
     constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
     constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
@@ -580,22 +591,22 @@ static int launch_decode_splits(const void* q, long long q_stride, const void* k
     }
     hb_launch(attn_decode_kernel<HD, COMBINE>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)q, q_stride,
               (const bf16*)kc, (const bf16*)vc, page_table, pt_width, positions, part_o, part_ml, nh, nkv, scale * AD_LOG2E, window,
-              pages_per_split, n_pages, counters, (bf16*)out, out_stride);
+              n_pages, counters, (bf16*)out, out_stride);
     return hb_check_launch("attention_decode");
 }
 
 template <int HD>
 static int launch_decode(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
                          int pt_width, const int* positions, float* scratch, int* counters, void* out, long long out_stride,
-                         int batch, int nh, int nkv, float scale, int window, int splits, int pages_per_split, int n_pages,
+                         int batch, int nh, int nkv, float scale, int window, int splits, int n_pages,
                          cudaStream_t s) {
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)batch * nh * splits * HD;
     if (counters != nullptr)
         return launch_decode_splits<HD, true>(q, q_stride, kc, vc, page_table, pt_width, positions, part_o, part_ml, counters, out,
-                                              out_stride, batch, nh, nkv, scale, window, splits, pages_per_split, n_pages, s);
+                                              out_stride, batch, nh, nkv, scale, window, splits, n_pages, s);
     if (launch_decode_splits<HD, false>(q, q_stride, kc, vc, page_table, pt_width, positions, part_o, part_ml, nullptr, out,
-                                        out_stride, batch, nh, nkv, scale, window, splits, pages_per_split, n_pages, s))
+                                        out_stride, batch, nh, nkv, scale, window, splits, n_pages, s))
         return 1;
     dim3 cgrid(batch, nh);
     hb_launch(attn_decode_combine_kernel<bf16>, dim3(cgrid), dim3(HD), 0, s, part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
@@ -621,13 +632,12 @@ static int attention_decode_any(const void* q, long long q_stride, const void* k
     if (splits > max_pages) splits = max_pages;
     HB_REQUIRE(counters == nullptr || splits <= AD_MAX_SPLITS, "attention_decode: at most %d splits when the last one combines, got %d",
                AD_MAX_SPLITS, splits);
-    const int pps = (max_pages + splits - 1) / splits;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 128)
         return launch_decode<128>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out,
-                                  out_stride, batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+                                  out_stride, batch, n_heads, n_kv_heads, scale, window, splits, n_pages, s);
     return launch_decode<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out, out_stride,
-                             batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages, s);
+                             batch, n_heads, n_kv_heads, scale, window, splits, n_pages, s);
 }
 
 extern "C" int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
@@ -654,7 +664,7 @@ template <int HD, bool COMBINE>
 static int launch_decode_fused_splits(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
                                       const int* page_table, int pt_width, const int* positions, float* part_o, float* part_ml,
                                       int* counters, void* out, long long out_stride, int batch, int nh, int nkv, float scale,
-                                      int window, int splits, int pages_per_split, int n_pages, int append, cudaStream_t s) {
+                                      int window, int splits, int n_pages, int append, cudaStream_t s) {
     constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
     constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
@@ -666,7 +676,7 @@ static int launch_decode_fused_splits(const void* qkv, long long stride, const f
     }
     hb_launch(attn_decode_fused_kernel<HD, COMBINE>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)qkv, stride,
               (const float2*)table, rot, (bf16*)kc, (bf16*)vc, page_table, pt_width, positions, part_o, part_ml, counters,
-              (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, pages_per_split, n_pages, append);
+              (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, n_pages, append);
     return hb_check_launch("attention_decode_fused");
 }
 
@@ -700,15 +710,15 @@ template <int HD>
 static int launch_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
                                const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
                                void* out, long long out_stride, int batch, int nh, int nkv, float scale, int window,
-                               int splits, int pages_per_split, int n_pages, int append, cudaStream_t s) {
+                               int splits, int n_pages, int append, cudaStream_t s) {
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)batch * nh * splits * HD;
     if (counters != nullptr || splits == 1)
         return launch_decode_fused_splits<HD, true>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o,
                                                     part_ml, counters, out, out_stride, batch, nh, nkv, scale, window, splits,
-                                                    pages_per_split, n_pages, append, s);
+                                                    n_pages, append, s);
     if (launch_decode_fused_splits<HD, false>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o, part_ml,
-                                              nullptr, out, out_stride, batch, nh, nkv, scale, window, splits, pages_per_split,
+                                              nullptr, out, out_stride, batch, nh, nkv, scale, window, splits,
                                               n_pages, append, s))
         return 1;
     hb_launch(attn_decode_combine_kernel<bf16>, dim3(batch, nh), dim3(HD), 0, s, part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
@@ -739,14 +749,13 @@ extern "C" int hb_attention_decode_fused(const void* qkv, long long stride, cons
     HB_REQUIRE(stride % 2 == 0 && ((uintptr_t)qkv & 3) == 0, "attention_decode_fused: projections must be 4-byte aligned");
     HB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_decode_fused: cache must be 16-byte aligned");
     if (splits > max_pages) splits = max_pages;
-    const int pps = (max_pages + splits - 1) / splits;
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 128)
         return launch_decode_fused<128>(qkv, stride, table, rot, k_cache, v_cache, page_table, pt_width, positions, scratch,
-                                        counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits, pps,
+                                        counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits,
                                         n_pages, append, s);
     return launch_decode_fused<64>(qkv, stride, table, rot, k_cache, v_cache, page_table, pt_width, positions, scratch,
-                                   counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits, pps, n_pages,
+                                   counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits, n_pages,
                                    append, s);
 }
 
