@@ -273,11 +273,11 @@ def test_gemm_tensor_core_cta_pairs(ops, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (3, 3072, 3072), (16, 6144, 4096), (8, 2560, 2048), (8, 2304, 2112),
                                    (1, 4000, 1536), (32, 4096, 4096), (27, 2304, 2112), (64, 4096, 14336),
-                                   (50, 3072, 3072), (64, 2560, 1024)])
+                                   (50, 3072, 3072), (64, 2560, 1024), (32, 2816, 1600), (64, 2816, 1600)])
 def test_gemm_tensor_core_cluster_split(ops, M, N, K):
     """Up to 64 tokens and 19 to 74 tiles: every tile is cut into 2 to 8 K ranges whose CTAs
-    form a cluster and sum their partial tiles over the first CTA's pipeline stages (one size
-    leaves one CTA of each cluster without work).  Every epilogue, twice (same bits)."""
+    form a cluster and sum their partial tiles over the first CTA's pipeline stages (K = 1536 and
+    K = 1600 leave one CTA of each cluster without work).  Every epilogue, twice (same bits)."""
     torch.manual_seed(34)
     assert ops.lib.hb_gemm_tc_resident_clusters(2, 4) >= 32, "clusters of 4 do not fit: the cluster variant is not what runs here"
     a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
