@@ -32,7 +32,7 @@
 // `patch_page` (>= 0): when that page has arrived, row `patch_row` of its key and value tiles is
 // overwritten with k_new / v_new (HD values each, in shared memory): the new token's key and
 // value, for a page that was requested before they existed.
-template <int HD, typename F, typename W>
+template <int HD, int STAGES, typename F, typename W>
 __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], const bf16* kc, const bf16* vc,
                                                   const int* __restrict__ pt, int n_pages, int nkv, int g, int lo,
                                                   int len, int p_begin, int p_end, float scale_log2e, uint8_t* smem,
@@ -69,7 +69,7 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
 
     bool waited = fresh_page < 0;
 #pragma unroll
-    for (int s = 0; s < AD_STAGES - 1; s++) {
+    for (int s = 0; s < STAGES - 1; s++) {
         if (!waited && p_begin + s >= fresh_page) {
             pdl_wait();
             after_wait();
@@ -85,16 +85,16 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
 
     for (int pi = p_begin; pi < p_end; pi++) {
         const int it = pi - p_begin;
-        cp_async_wait<AD_STAGES - 2>();
+        cp_async_wait<STAGES - 2>();
         __syncthreads();
-        load_page((it + AD_STAGES - 1) % AD_STAGES, pi + AD_STAGES - 1);
-        const uint32_t kt = smem_base + (it % AD_STAGES) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
+        load_page((it + STAGES - 1) % STAGES, pi + STAGES - 1);
+        const uint32_t kt = smem_base + (it % STAGES) * 2 * TILE_BYTES, vt = kt + TILE_BYTES;
         if (pi == patch_page) {
             if (tid < 2 * CHUNKS) {
                 const int ch = tid % CHUNKS;
                 const bool value = tid >= CHUNKS;
                 const uint4 x = reinterpret_cast<const uint4*>(value ? v_new : k_new)[ch];
-                *reinterpret_cast<uint4*>(smem + (it % AD_STAGES) * 2 * TILE_BYTES + (value ? TILE_BYTES : 0) +
+                *reinterpret_cast<uint4*>(smem + (it % STAGES) * 2 * TILE_BYTES + (value ? TILE_BYTES : 0) +
                                           swizzled<ROW_BYTES>(patch_row, ch)) = x;
             }
             __syncthreads();
@@ -307,7 +307,7 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
     // it counts as a load from memory that never changes, which the compiler may move above
     // the wait (it did: the queries of the layer before came back).
     uint32_t qf[KSTEPS][4];
-    decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&] {
+    decode_split_core<HD, AD_STAGES>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&] {
         const int r0 = lane >> 2, c = (lane & 3) * 2;
         const unsigned int* q0 = reinterpret_cast<const unsigned int*>(q + (size_t)b * q_stride + (size_t)(g * G + r0) * HD + c);
         const unsigned int* q1 = q0 + 8 * HD / 2;
@@ -358,7 +358,7 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
 // rotation; it is not written.  All pages of a split are requested before the wait for the
 // kernel in front; the split that owns the page of the new position puts the new key and value
 // into its copy of that page in shared memory (and into the cache, for the steps to come).
-template <int HD, bool COMBINE>
+template <int HD, bool COMBINE, int STAGES>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot,
                          bf16* kc, bf16* vc, const int* __restrict__ page_table, int pt_width,
@@ -440,7 +440,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
     if (p_begin < p_end) {
         uint32_t qf[KSTEPS][4];
         for (int idx = G * HD + tid; idx < 16 * HD; idx += AD_THREADS) q_rot[idx] = __float2bfloat16_rn(0.0f);
-        decode_split_core<HD>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&]() {
+        decode_split_core<HD, STAGES>(qf, kc, vc, pt, n_pages, nkv, g, lo, len, p_begin, p_end, scale_log2e, smem, [&]() {
             // the group's queries, rotated once by the whole block; row r of the tile is head
             // g*G + r (rows >= G stay zero), fragments come from shared memory.  One pair
             // (i, i + rot/2) per item.
@@ -660,24 +660,53 @@ extern "C" int hb_attention_decode_combined(const void* q, long long q_stride, c
                                 batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
 }
 
+#define AD_DEEP_STAGES 6        // when every CTA has an SM of its own: five pages in flight instead of two
+
+template <int HD, bool COMBINE, int STAGES>
+static int launch_decode_fused_stages(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
+                                      const int* page_table, int pt_width, const int* positions, float* part_o, float* part_ml,
+                                      int* counters, void* out, long long out_stride, int batch, int nh, int nkv, float scale,
+                                      int window, int splits, int n_pages, int append, cudaStream_t s) {
+    constexpr int PIPE = STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
+    constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
+    constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
+    static_assert(SMEM + 8 * 1024 <= 227 * 1024, "page pipeline does not fit shared memory");
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<HD, COMBINE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return hb_fail("attention_decode_fused: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    hb_launch(attn_decode_fused_kernel<HD, COMBINE, STAGES>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)qkv, stride,
+              (const float2*)table, rot, (bf16*)kc, (bf16*)vc, page_table, pt_width, positions, part_o, part_ml, counters,
+              (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, n_pages, append);
+    return hb_check_launch("attention_decode_fused");
+}
+
+static int decode_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    }
+    return n;
+}
+
+// With no more CTAs than SMs (one sequence with a long cache) a CTA cannot share an SM anyway:
+// the deep pipeline keeps five pages in flight per CTA instead of two.
 template <int HD, bool COMBINE>
 static int launch_decode_fused_splits(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
                                       const int* page_table, int pt_width, const int* positions, float* part_o, float* part_ml,
                                       int* counters, void* out, long long out_stride, int batch, int nh, int nkv, float scale,
                                       int window, int splits, int n_pages, int append, cudaStream_t s) {
-    constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
-    constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
-    constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<HD, COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return hb_fail("attention_decode_fused: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
-        attr_set = true;
-    }
-    hb_launch(attn_decode_fused_kernel<HD, COMBINE>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)qkv, stride,
-              (const float2*)table, rot, (bf16*)kc, (bf16*)vc, page_table, pt_width, positions, part_o, part_ml, counters,
-              (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, n_pages, append);
-    return hb_check_launch("attention_decode_fused");
+    if ((long long)splits * nkv * batch <= decode_sm_count())
+        return launch_decode_fused_stages<HD, COMBINE, AD_DEEP_STAGES>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions,
+                                                                       part_o, part_ml, counters, out, out_stride, batch, nh, nkv,
+                                                                       scale, window, splits, n_pages, append, s);
+    return launch_decode_fused_stages<HD, COMBINE, AD_STAGES>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o,
+                                                              part_ml, counters, out, out_stride, batch, nh, nkv, scale, window,
+                                                              splits, n_pages, append, s);
 }
 
 template <int HD>
@@ -685,12 +714,12 @@ static int decode_ctas_per_sm() {
     constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
     constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
-    if (cudaFuncSetAttribute(attn_decode_fused_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(attn_decode_fused_kernel<HD, false, AD_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_fused_kernel<HD, false>, AD_THREADS, SMEM) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_fused_kernel<HD, false, AD_STAGES>, AD_THREADS, SMEM) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }

@@ -520,21 +520,24 @@ def test_decode_attention_split_choice(ops):
         assert [ops.decode_splits_for(b, 8, 128, 128) for b in (8, 16, 32, 48, 64)] == [4, 2, 1, 2, 1]
 
 
-@pytest.mark.parametrize("nh,nkv,hd,rot,window", [(8, 2, 128, 128, None), (3, 1, 64, 64, None), (16, 1, 64, 32, 100),
-                                                  (10, 5, 128, 128, 65)])
-def test_attention_decode_fused_equals_the_three_kernels(ops, nh, nkv, hd, rot, window):
+@pytest.mark.parametrize("nh,nkv,hd,rot,window,copies", [(8, 2, 128, 128, None, 1), (3, 1, 64, 64, None, 1),
+                                                         (16, 1, 64, 32, 100, 1), (10, 5, 128, 128, 65, 1),
+                                                         (8, 4, 128, 128, None, 14), (8, 2, 64, 64, 100, 32)])
+def test_attention_decode_fused_equals_the_three_kernels(ops, nh, nkv, hd, rot, window, copies):
     """The decode attention that rotates and appends itself (with the combination kernel behind
     it, or combining in its last split) against the separate rope/append, attention and combine
     kernels, twice in a row (counters return to zero), with lengths at page edges and a first
-    token."""
+    token.  Few sequences run the deep page pipeline (a CTA per SM at most), `copies` of them
+    the shallow one."""
     torch.manual_seed(14)
     dtype = torch.bfloat16
     scale = 1.0 / math.sqrt(hd)
-    positions = [130, 0, 63, 300, 64]
+    positions = [130, 0, 63, 300, 64] * copies
     B = len(positions)
-    tables = torch.tensor([[7, 1, 4, -1, -1], [3, 8, -1, -1, -1], [0, 15, -1, -1, -1], [9, 10, 11, 12, 13],
-                           [2, 5, -1, -1, -1]], dtype=torch.int32, device=DEV)
-    base = _cache(16, nkv, hd, dtype)
+    rows = [[7, 1, 4, -1, -1], [3, 8, -1, -1, -1], [0, 15, -1, -1, -1], [9, 10, 11, 12, 13], [2, 5, -1, -1, -1]]
+    tables = torch.tensor([[p + 16 * c if p >= 0 else -1 for p in row] for c in range(copies) for row in rows],
+                          dtype=torch.int32, device=DEV)
+    base = _cache(16 * copies, nkv, hd, dtype)
     base.k.normal_()
     base.v.normal_()
     step = _step(torch.arange(B, dtype=torch.int32, device=DEV), torch.tensor(positions, dtype=torch.int32, device=DEV), tables)
