@@ -105,7 +105,7 @@ struct TcSchedule {
 // TL_EVENT(code) marks exist in timeline builds only (common.cuh): 1 predecessors finished
 // (producer), 2 first stage full (MMA thread), 3 last MMA of a work item committed, 4 accumulator
 // full (epilogue), 5 partial tile written and fenced, 6 tile counter known, 7 tile emitted,
-// 8 block end.
+// 8 block end (in a cluster's first CTA: 5 behind the last cluster barrier, 6 partial tiles summed).
 //
 // CLUSTER (up to 64 tokens, every tile cut into `split` <= 8 equal K ranges): the CTAs of a tile
 // are one thread-block cluster.  Each writes its partial tile into the shared memory of the
@@ -297,6 +297,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // contributor, so that the one that turns out to be last need not wait for them
             // (nobody writes the tile before all contributors have counted themselves in)
             constexpr int NV = BN <= 64 ? BN / 4 : 16;
+            // (Not for 64 tokens: in the cluster variant, where the first CTA's residual add takes
+            // 6-9 us behind the second barrier, reading its 16 float4 ahead made a step at batch
+            // 64 1.5-2 % slower, measured on one GPU in alternating runs.)
             constexpr bool RES_AHEAD = MODE == TC_ADD_F32 && BN <= 32;
             float4 res[NV];
             const bool have_res = RES_AHEAD && !whole && (p.ldc & 3) == 0 && (p.N & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
@@ -432,6 +435,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         cluster_sync_all();
         if (warp >= 2 && blockIdx.x % p.split == 0 && cl_done && !*abort_flag) {
             const int parts = (p.kb_total + ((p.kb_total + p.split - 1) / p.split) - 1) / ((p.kb_total + p.split - 1) / p.split);
+            if (et == 0) TL_EVENT(5);
             float4 acc[CL_NV];
 #pragma unroll
             for (int i = 0; i < CL_NV; i++) acc[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -446,7 +450,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     acc[i].w += t.w;
                 }
             }
+            if (et == 0) TL_EVENT(6);
             tc_emit_flat<MODE, BN <= 64 ? BN : 4>(p, cl_m0, cl_n0, acc, et, cl_res, cl_have_res);
+            if (et == 0) TL_EVENT(7);
         }
     }
     tc_fence_before();
