@@ -18,6 +18,7 @@ from typing import Optional
 import torch
 
 from . import build
+from .plan import decode_splits
 
 _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
 
@@ -407,31 +408,14 @@ class Ops:
 
     # ------------------------------------------------------------------ attention
     def decode_splits_for(self, batch: int, kv_heads: int, max_pages: int, head_dim: int = 128) -> int:
-        """Key splits of decode attention: at most 16, at least eight pages each (measured: more
-        splits cost more in the combine than they gain).  One wave of the resident CTAs (two
-        per SM at head size 128) if that fills the device: batch 8 at 8192 tokens takes
-        4 splits.  Where one wave would leave a third of the device idle (batch 24: 192 CTAs)
-        or a second wave would (batch 48: 384 CTAs), the splits that fill whole waves best, of
-        32 pages or more each (batch 24 and 48: 3 splits, 12 % of a step at batch 48)."""
+        """Key splits of decode attention (``plan.decode_splits``) for this device: the CTAs it
+        holds at once are the kernel's CTAs per SM (two at head size 128) times its SMs."""
         key = (batch, kv_heads, max_pages, head_dim)
         hit = self._splits_cache.get(key)
-        if hit is not None:
-            return hit
-        slots = self.sm_count * max(1, self.lib.hb_attention_decode_ctas_per_sm(head_dim) or 2)
-        ctas1 = max(1, batch * kv_heads)
-        limit = max(1, min(16, -(-max_pages // 8)))
-
-        def fill(s):                      # share of the waves' CTA slots that have work
-            ctas = ctas1 * s
-            return ctas / (-(-ctas // slots) * slots)
-
-        best = max(1, min(slots // ctas1, limit))
-        if fill(best) < 0.8:
-            for s in range(1, limit + 1):
-                if -(-max_pages // s) >= 32 and fill(s) - 0.01 * s > fill(best) - 0.01 * best + 0.1:
-                    best = s
-        self._splits_cache[key] = best
-        return best
+        if hit is None:
+            slots = self.sm_count * max(1, self.lib.hb_attention_decode_ctas_per_sm(head_dim) or 2)
+            hit = self._splits_cache[key] = decode_splits(batch, kv_heads, max_pages, slots)
+        return hit
 
     def can_fuse_decode_attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out) -> bool:
         """Whether ``attention_decode_fused`` takes this step: one token per sequence,

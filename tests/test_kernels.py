@@ -506,13 +506,13 @@ def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
 def test_decode_attention_split_choice(ops):
     """The number of key splits: one wave of CTAs that fills the device where there is one, whole
     waves where one split per (sequence, kv head) would leave a third of a wave idle, never
-    fewer than eight pages per split, never more than 16 splits."""
+    more than a split for every eight pages, never more than 16 splits."""
     per_sm = ops.lib.hb_attention_decode_ctas_per_sm(128)
     assert per_sm >= 1 and ops.lib.hb_attention_decode_ctas_per_sm(64) >= per_sm and ops.lib.hb_attention_decode_ctas_per_sm(80) == 0
     slots = ops.sm_count * per_sm
     for batch, kv, pages in [(1, 8, 128), (8, 8, 128), (8, 8, 4), (24, 8, 128), (48, 8, 128), (64, 8, 128), (3, 1, 1000), (500, 8, 40)]:
         s = ops.decode_splits_for(batch, kv, pages, 128)
-        assert 1 <= s <= 16 and (s == 1 or -(-pages // s) >= 8), (batch, kv, pages, s)
+        assert 1 <= s <= 16 and s <= -(-pages // 8), (batch, kv, pages, s)
         ctas = batch * kv * s
         if batch * kv <= slots // 2 and pages >= 16 * (slots // (batch * kv)):
             assert ctas > slots // 2 or s == 16, (batch, kv, pages, s)           # few sequences with long caches fill the device
