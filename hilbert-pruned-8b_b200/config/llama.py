@@ -9,15 +9,11 @@ from __future__ import annotations
 
 import json
 import math
-import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
+from .base import ConfigError
 from .spec import LayerSpec, ModelSpec, PartSpec, PlanEntry
-
-
-class ConfigError(ValueError):
-    """Raised for a config.json the architecture cannot run."""
 
 
 def _is_number(v: Any) -> bool:
@@ -231,8 +227,11 @@ class LlamaConfig:
             "num_kv_heads": self.num_key_value_heads, "head_dim": self.head_dim,
             "window": None, "position": rope})
         ffn = PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size})
-        layers = [LayerSpec(prefix=f"layers.{i}.", mixer=mixer, feed_forward=ffn,
-                            mixer_norm=norm, feed_forward_norm=norm)
+        # tensor names below ``layers.{i}.`` (model.c:416-428)
+        prefixes = {"mixer": "self_attn.", "feed_forward": "mlp.", "mixer_norm": "input_layernorm.",
+                    "feed_forward_norm": "post_attention_layernorm."}
+        layers = [LayerSpec(prefix=f"layers.{i}.", block="prenorm", part_prefixes=dict(prefixes),
+                            parts={"mixer": mixer, "feed_forward": ffn, "mixer_norm": norm, "feed_forward_norm": norm})
                   for i in range(self.num_hidden_layers)]
         plan = [PlanEntry(i) for i in range(self.num_hidden_layers)]
         spec = ModelSpec(
@@ -242,17 +241,9 @@ class LlamaConfig:
             final_norm=norm,
             head=PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
                                       "tied": self.tie_word_embeddings}),
+            # model.c:394-406: the decoder's tensors sit below one of two prefixes; the head has none
+            weight_prefixes=["model.language_model.", "model."], embedding_prefix="embed_tokens.",
+            final_norm_prefix="norm.", head_prefix="lm_head.",
             stop_token_ids=list(self.eos_token_ids), max_position=self.max_position_embeddings)
         spec.validate()
         return spec
-
-
-def read_config_json(model_dir: str) -> Dict[str, Any]:
-    path = os.path.join(model_dir, "config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as f:
-            return json.load(f)
-    except OSError as e:
-        raise ConfigError(f"config: cannot open {path}: {e.strerror}") from None
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"config: {path} is not valid JSON: {e}") from None

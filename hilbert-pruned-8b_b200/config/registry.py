@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from typing import Any, Dict, Protocol
 
-from .llama import ConfigError, LlamaConfig, read_config_json
+from .base import ConfigError, read_config_json
 from .spec import ModelSpec
 
 
@@ -70,5 +70,3 @@ def load_config(model_dir: str) -> Any:
     root = read_config_json(model_dir)
     return config_class_for(root).from_dict(root)
 
-
-register_architecture(LlamaConfig)

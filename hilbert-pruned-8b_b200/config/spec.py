@@ -2,8 +2,8 @@
 
 A configuration class (one per architecture) turns its ``config.json`` into a ``ModelSpec``.
 Nothing below this level knows which architecture it serves: a ``ModelSpec`` is a list of
-layers, each naming its mixer, feed-forward and norms with their sizes and constants, plus
-the order in which the layers run.
+layers, each naming its block (the arrangement) and the block's parts (mixer, feed-forward,
+norms, ...) with their sizes and constants, plus the order in which the layers run.
 
 The reference keeps a per-layer type array and per-kind counters for the same purpose
 (cleanroom-transformer/src/transformer.h:275,289-290,307-318); here the per-layer choice is
@@ -28,23 +28,48 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer.
+    """One decoder layer: the registered ``block`` (the arrangement) and the parts it arranges.
 
-    ``prefix`` is the tensor-name prefix of the layer's weights (``layers.3.``); the part
-    names below it (``self_attn.q_proj.weight``) are the parts' own.
+    ``parts`` maps a role name to the part in that role; which roles exist is the block's
+    business (the pre-norm block asks for ``mixer``, ``feed_forward``, ``mixer_norm`` and
+    ``feed_forward_norm``; a block of another shape names its own and this class does not
+    change).  ``prefix`` is the tensor-name prefix of the layer's weights (``layers.3.``),
+    ``part_prefixes[role]`` the prefix of a part's tensors below it (``self_attn.``); the
+    names below that (``q_proj.weight``) are the part's own.  The architecture's
+    configuration supplies all of them: none is a default of this file.
     """
 
     prefix: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Dict[str, PartSpec]
+    part_prefixes: Dict[str, str]
     block: str = "prenorm"
-    # tensor-name prefixes of the parts below the layer's prefix (model.c:416-428)
-    mixer_prefix: str = "self_attn."
-    feed_forward_prefix: str = "mlp."
-    mixer_norm_prefix: str = "input_layernorm."
-    feed_forward_norm_prefix: str = "post_attention_layernorm."
+
+    def part(self, role: str) -> PartSpec:
+        if role not in self.parts:
+            raise KeyError(f"layer {self.prefix!r} ({self.block}) has no part in the role {role!r} "
+                           f"({', '.join(sorted(self.parts))})")
+        return self.parts[role]
+
+    def part_prefix(self, role: str) -> str:
+        return self.part_prefixes.get(role, role + ".")
+
+    def with_part(self, role: str, spec: PartSpec, prefix: Optional[str] = None) -> "LayerSpec":
+        """A copy with the part in ``role`` replaced (or added) and, if given, its tensor prefix."""
+        parts = {**self.parts, role: spec}
+        prefixes = dict(self.part_prefixes) if prefix is None else {**self.part_prefixes, role: prefix}
+        return LayerSpec(self.prefix, parts, prefixes, self.block)
+
+    def with_block(self, block: str) -> "LayerSpec":
+        return LayerSpec(self.prefix, dict(self.parts), dict(self.part_prefixes), block)
+
+    # the two roles most layers have, by name (a block without one of them raises KeyError)
+    @property
+    def mixer(self) -> PartSpec:
+        return self.part("mixer")
+
+    @property
+    def feed_forward(self) -> PartSpec:
+        return self.part("feed_forward")
 
 
 @dataclass(frozen=True)
@@ -72,13 +97,17 @@ class ModelSpec:
     embedding: PartSpec
     final_norm: PartSpec
     head: PartSpec
-    # candidate prefixes of the decoder's tensors, tried in order (model.c:394-395)
-    weight_prefixes: List[str] = field(default_factory=lambda: ["model.language_model.", "model."])
+    # candidate prefixes of the decoder's tensors, tried in order: the first under which the
+    # embedding table exists is the checkpoint's, else the last
+    weight_prefixes: List[str]
+    # tensor-name prefixes of the parts outside the layers, below the decoder's prefix
+    embedding_prefix: str
+    final_norm_prefix: str
+    head_prefix: str
     stop_token_ids: List[int] = field(default_factory=list)
+    # the longest sequence the checkpoint was made for (None: not stated); the generation loop
+    # ends a request there, the step function does not read it
     max_position: Optional[int] = None
-    embedding_prefix: str = "embed_tokens."
-    final_norm_prefix: str = "norm."
-    head_prefix: str = "lm_head."
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -69,6 +69,9 @@ int hb_attention_prefill_tc(const void* q, long long q_stride, long long n_token
                             const int* page_table, int pt_width, const int* seq_start, const int* seq_pos0, void* out,
                             long long out_stride, int n_seqs, int q_blocks, int n_heads, int n_kv_heads, int head_dim,
                             float scale, int window, int n_pages, int* error_flag, void* stream);
+// out[i] = mean + stdev * N(0, 1): element i of the counter-based stream `base`
+int hb_random_normal(void* out, int out_dtype, long long n, unsigned long long base, float stdev, float mean,
+                     void* stream);
 int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, void* stream);
 int hb_sample(const float* logits, long long stride, const float* temperature, const long long* seeds,
               const long long* request_ids, const long long* steps, int* out, int n_rows, int vocab, void* stream);

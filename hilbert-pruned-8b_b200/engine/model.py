@@ -38,7 +38,8 @@ class DecoderModel:
         self.final_norm = NORMS.build(spec.final_norm, ctx)
         self.head = HEADS.build(spec.head, ctx)
         self.prefix = spec.weight_prefixes[-1]
-        self.graph_safe = all(getattr(part, "graph_safe", True) for _, part in self.named_parts())
+        self.graph_safe = (all(getattr(part, "graph_safe", True) for _, part in self.named_parts())
+                           and all(getattr(b, "graph_safe", True) for b in self.blocks))
 
     # ------------------------------------------------------------------ weights
     def named_parts(self) -> List[Tuple[str, object]]:
@@ -81,7 +82,7 @@ class DecoderModel:
     def cache_needs(self) -> Dict[int, CacheNeed]:
         out = {}
         for i, e in enumerate(self.spec.plan):
-            need = self.blocks[e.layer].mixer.cache_need()
+            need = self.blocks[e.layer].cache_need()
             if need is not None and e.cache_of is None:
                 out[i] = need
         return out
@@ -89,7 +90,7 @@ class DecoderModel:
     def state_needs(self) -> Dict[int, StateNeed]:
         out = {}
         for i, e in enumerate(self.spec.plan):
-            need = self.blocks[e.layer].mixer.state_need()
+            need = self.blocks[e.layer].state_need()
             if need is not None:
                 out[i] = need
         return out

@@ -64,29 +64,36 @@ class Engine:
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def from_folder(cls, model_dir: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0", **kw) -> "Engine":
+    def from_folder(cls, model_dir: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
+                    strict_weights: bool = False, **kw) -> "Engine":
+        """``strict_weights``: tensors in the folder that no part of the model reads are an error
+        (default: ignored, as the reference ignores what it does not bind)."""
         config = load_config(model_dir)
         eng = cls(config.model_spec(), dtype, max_tokens, device, **kw)
         eng.config = config
         names = folder_names(model_dir)
         prefix = choose_prefix(names, eng.spec.weight_prefixes, eng.model.first_weight_name())
         table = eng.model.weight_table(prefix)
-        tensors = load_tensors(model_dir, table, eng.dtype, eng.device)
+        tensors = load_tensors(model_dir, table, eng.dtype, eng.device, strict=strict_weights)
         eng.model.bind(tensors, prefix)
         eng._make_cache()
         return eng
 
     @classmethod
     def from_random(cls, config, seed: int, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
-                    std: float = 0.02, norm_std: float = 0.0, fan_in_scale=None, **kw) -> "Engine":
-        """Random weights drawn on the device (no folder is written)."""
+                    std: float = 0.02, norm_std: float = 0.0, fan_in_scale=None, stored_dtype=torch.bfloat16,
+                    **kw) -> "Engine":
+        """Random weights drawn on the device (no folder is written).  The values are a function
+        of (seed, tensor name, element): the model that ``write_random_model(folder, config, seed,
+        ...)`` writes from the CPU with the same arguments, bit for bit; ``stored_dtype`` is that
+        folder's dtype, and a 32-bit engine widens it exactly, as it does when it loads."""
         from ..weights.random_init import random_tensors
         eng = cls(config.model_spec(), dtype, max_tokens, device, **kw)
         eng.config = config
         table = eng.model.weight_table()
-        # one tensor at a time would be kinder to memory; a table's worth is drawn per part
-        tensors = random_tensors(table, seed, eng.device, std, norm_std,
-                                 torch.bfloat16 if eng.dtype == torch.bfloat16 else torch.float32, fan_in_scale)
+        tensors = random_tensors(table, seed, eng.device, std, norm_std, stored_dtype, fan_in_scale, ops=eng.ctx.ops)
+        if eng.dtype == torch.float32:
+            tensors = {n: (t.to(torch.float32) if t.is_floating_point() else t) for n, t in tensors.items()}
         eng.model.bind(tensors)
         del tensors
         eng._make_cache()

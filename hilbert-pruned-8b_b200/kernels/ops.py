@@ -50,6 +50,7 @@ _SIGNATURES = {
                              _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr],
     "hb_attention_prefill_tc": [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_random_normal": [_c_ptr, _c_int, _c_ll, ctypes.c_ulonglong, _c_float, _c_float, _c_ptr],
     "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
 }
@@ -519,6 +520,17 @@ class Ops:
                    cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k), pt.data_ptr(), pt.shape[1],
                    step.tok_seq.data_ptr(), step.positions.data_ptr(), out.data_ptr(), _code(out),
                    _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale), win, self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ random weights
+    def random_normal(self, out, base: int, std: float, mean: float = 0.0) -> None:
+        """``out.flat[i] = mean + std * N(0, 1)``, element ``i`` of the counter-based stream
+        ``base`` (``weights.random_init.stream_base``): the values the CPU draws, bit for bit."""
+        self._dev(out)
+        if not out.is_contiguous():
+            raise KernelError("random_normal: contiguous output expected")
+        self._call("hb_random_normal", out.data_ptr(), _code(out), out.numel(), int(base) & ((1 << 64) - 1), float(std),
+                   float(mean), self._stream())
         self.launches += 1
 
     # ------------------------------------------------------------------ sampling

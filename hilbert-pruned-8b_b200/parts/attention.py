@@ -34,6 +34,9 @@ class Attention(Mixer):
         pos = p.get("position")
         self.position = ctx.shared_part(POSITION_ENCODINGS, pos) if pos is not None else None
         self.graph_safe = getattr(self.position, "graph_safe", True)      # a step is as capturable as its parts
+        # whether decode steps may run the kernel that rotates, appends and attends in one launch
+        # (the part decides; the kernel library only says whether it can)
+        self.fuse_decode = bool(p.get("fuse_decode", True))
         self.q_width = self.heads * self.head_dim
         self.kv_width = self.kv_heads * self.head_dim
         self.w_qkv = None
@@ -72,12 +75,21 @@ class Attention(Mixer):
             # a layer that reads another layer's cache needs its queries only
             w_q = self.w_qkv.first_rows(self.q_width) if hasattr(self.w_qkv, "first_rows") else self.w_qkv[: self.q_width]
             ops.linear(h, w_q, qkv[:, : self.q_width])
-        table = self.position.table(step) if self.position is not None else None
-        rot = self.position.rotary_dim if self.position is not None else 0
+        # positions: a table of rotations that the kernels apply, or the part turns q and k itself
+        table, rot = None, 0
+        fusable = self.fuse_decode
+        if self.position is not None:
+            rotation = self.position.rotation_table(step)
+            if rotation is None:
+                q = qkv[:, : self.q_width].unflatten(1, (self.heads, self.head_dim))
+                k = qkv[:, self.q_width: self.q_width + self.kv_width].unflatten(1, (self.kv_heads, self.head_dim))
+                self.position.apply(q, k if append else None, step)
+            else:
+                table, rot = rotation
+                fusable = fusable and self.position.fusable
         attn = ws.buffer("attention.out", (cap, self.q_width), self.ctx.dtype)[:T]
-        if ops.can_fuse_decode_attention(qkv, self.heads, self.kv_heads, self.head_dim, cache, step, attn):
-            # one token per sequence: rotation, append, attention and the combination of its
-            # splits are one launch
+        if fusable and ops.can_fuse_decode_attention(qkv, self.heads, self.kv_heads, self.head_dim, cache, step, attn):
+            # one token per sequence: rotation, append and attention are one launch
             ops.attention_decode_fused(qkv, table, rot, self.heads, self.kv_heads, self.head_dim, cache, step, attn,
                                        self.scale, self.window, append)
         else:

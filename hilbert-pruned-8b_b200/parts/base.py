@@ -19,7 +19,11 @@ What a part must provide:
   32-bit ``residual`` in place.
 * feed-forwards: ``forward(h, residual, step)``, adding likewise.
 * norms: ``forward(x, out, rows=None)``.
-* position encodings: ``prepare(step)`` once per step and whatever ``apply`` its mixer calls.
+* position encodings: ``rotation_table(step)`` when the encoding is a rotation of pairs of
+  head dimensions by position-dependent angles (the kernels then turn queries and keys
+  themselves), else ``apply(q, k, step)`` which turns them in place; see ``PositionEncoding``.
+* blocks (``parts/block.py``): ``ROLES``, ``named_parts()``, ``cache_need()``, ``state_need()``,
+  ``forward(x, step, cache, state, append)``.
 * ``graph_safe`` (class attribute, default True): whether ``forward`` only enqueues work on
   the current stream, so that a decode step can be captured in a CUDA graph.
 """
@@ -124,8 +128,30 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """How a mixer's queries and keys learn their positions.  A mixer uses one of two forms:
+
+    * ``rotation_table(step)`` returns ``(table, rotary_dim)``: ``table[t, i] = (cos a, sin a)``
+      in 32-bit, ``[tokens, rotary_dim / 2, 2]``, for the step's token ``t`` and the pair
+      ``(i, i + rotary_dim / 2)`` of every head; the attention kernels turn queries and keys by
+      it (dimensions from ``rotary_dim`` on stay).  ``fusable`` says whether a kernel that does
+      more than turning (decode attention that also appends and attends) may take the table;
+      a part sets it False to keep the rotation a step of its own.
+    * ``rotation_table`` returns None: the encoding is something else, and ``apply(q, k, step)``
+      changes ``q [tokens, heads, head_dim]`` and ``k [tokens, kv_heads, head_dim]`` (views of
+      the step's projections) in place before the keys are cached; no kernel rotates.
+
+    ``prepare(step)`` may compute what all layers of a step share into ``step.shared``."""
+
+    fusable = True
+
     def prepare(self, step) -> None:
         pass
+
+    def rotation_table(self, step):
+        return None
+
+    def apply(self, q, k, step) -> None:
+        raise NotImplementedError(f"{type(self).__name__} gives neither a rotation table nor apply()")
 
 
 class Registry:

@@ -67,7 +67,7 @@ class RotaryEmbedding(PositionEncoding):
         self.ctx.ops.rope_table(step.positions, self.inv_freq, table)
         step.shared[self._key] = table
 
-    def table(self, step) -> torch.Tensor:
-        """``[tokens, rot/2, 2]`` cosines and sines of this step's positions."""
+    def rotation_table(self, step):
+        """``([tokens, rot/2, 2] cosines and sines of this step's positions, rot)``."""
         self.prepare(step)
-        return step.shared[self._key]
+        return step.shared[self._key], self.rotary_dim

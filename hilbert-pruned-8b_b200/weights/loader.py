@@ -4,7 +4,11 @@ The table (full tensor name -> expected shape and kind) comes from the model's p
 Everything is checked before anything is copied, and all faults come in ONE error that
 lists missing tensors, unexpected tensors and wrong shapes (the reference stops at the
 first: ``weights: missing %s``, ``weights: %s has shape [a, b], expected [r, c]``,
-cleanroom-transformer/src/model.c:226-244,272-281).
+cleanroom-transformer/src/model.c:226-244,272-281).  A tensor that no part asks for is not a
+fault by itself: the reference never looks at what it does not bind (model.c:391-447), and
+checkpoints carry extras (``mtp.*``, vision towers, ``rotary_emb.inv_freq``).  Such names are
+still listed in the error when something else is wrong, where a misspelt name shows up as a
+missing and an unexpected tensor side by side; ``strict=True`` makes them a fault of their own.
 
 Dtype rule.  Serving precision (``bfloat16``): floating tensors stored in 16 bits are held
 as bfloat16 (float16 is converted), a tensor stored in 32-bit stays 32-bit, integer tables
@@ -52,9 +56,10 @@ class WeightError(ValueError):
 
 
 def check_table(available: Mapping[str, Tuple[str, Tuple[int, ...]]], table: Mapping[str, ParamSpec],
-                ignored: Iterable[str] = DEFAULT_IGNORED) -> None:
-    """Raises ``WeightError`` unless ``available`` (name -> (dtype tag, shape)) holds exactly
-    the table's tensors with the table's shapes."""
+                ignored: Iterable[str] = DEFAULT_IGNORED, strict: bool = False) -> List[str]:
+    """Raises ``WeightError`` unless ``available`` (name -> (dtype tag, shape)) holds the
+    table's tensors with the table's shapes; ``strict`` also refuses tensors the table does not
+    name (but for the ``ignored`` patterns).  Returns the unexpected names."""
     missing: List[str] = []
     wrong: List[Tuple[str, Tuple[int, ...], Tuple[int, ...]]] = []
     wrong_dtype: List[Tuple[str, str]] = []
@@ -80,8 +85,9 @@ def check_table(available: Mapping[str, Tuple[str, Tuple[int, ...]]], table: Map
     patterns = list(ignored)
     unexpected = [n for n in available
                   if n not in table and not any(fnmatch.fnmatchcase(n, p) for p in patterns)]
-    if missing or unexpected or wrong or wrong_dtype:
+    if missing or wrong or wrong_dtype or (strict and unexpected):
         raise WeightError(sorted(missing), sorted(unexpected), wrong, wrong_dtype)
+    return sorted(unexpected)
 
 
 def target_dtype(stored: torch.dtype, kind: str, precision: torch.dtype) -> torch.dtype:
@@ -95,12 +101,13 @@ def target_dtype(stored: torch.dtype, kind: str, precision: torch.dtype) -> torc
 
 
 def load_tensors(model_dir: str, table: Mapping[str, ParamSpec], precision: torch.dtype,
-                 device: torch.device, ignored: Iterable[str] = DEFAULT_IGNORED) -> Dict[str, torch.Tensor]:
+                 device: torch.device, ignored: Iterable[str] = DEFAULT_IGNORED,
+                 strict: bool = False) -> Dict[str, torch.Tensor]:
     """Checks the folder against ``table`` and returns the tensors on ``device``."""
     folder = SafetensorsFolder(model_dir)
     try:
         available = {n: (folder.entry(n).dtype, folder.entry(n).shape) for n in folder.names()}
-        check_table(available, table, ignored)
+        check_table(available, table, ignored, strict)
         out: Dict[str, torch.Tensor] = {}
         for name, spec in table.items():
             if name not in folder:

@@ -100,7 +100,7 @@ def test_round_trip_and_model_spec():
         m = spec.layers[0].mixer
         assert m.kind == "attention" and m.params["num_kv_heads"] == c.num_key_value_heads
         assert m.params["position"].params["theta"] == c.rope_theta
-        assert spec.layers[0].mixer_norm.params["eps"] == c.rms_norm_eps
+        assert spec.layers[0].part("mixer_norm").params["eps"] == c.rms_norm_eps
         assert spec.stop_token_ids == c.eos_token_ids
 
 

@@ -77,11 +77,12 @@ def test_rotary_part_matches_plain_frequencies_and_angles(ctx):
     assert (abs(rope.inv_freq_host - want) <= 1.2e-7 * want).all()
     pos = torch.tensor([0, 3, 200, 9000], dtype=torch.int32, device=DEV)
     step = types.SimpleNamespace(positions=pos, num_tokens=4, shared={})
-    table = rope.table(step)
+    table, rot = rope.rotation_table(step)
+    assert rot == 40 and rope.fusable
     ang = torch.from_numpy(rope.inv_freq_host)[None, :] * pos.cpu().float()[:, None]
     assert (table[..., 0].cpu().double() - torch.cos(ang.double())).abs().max() < 3e-7
     assert (table[..., 1].cpu().double() - torch.sin(ang.double())).abs().max() < 3e-7
-    assert rope.table(step) is table            # made once per step
+    assert rope.rotation_table(step)[0] is table            # made once per step
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -216,7 +217,7 @@ def _register_toy():
         def model_spec(self):
             s = self.base.model_spec()
             toy = PartSpec("toy_decay", {"hidden_size": self.base.hidden_size, "decay": self.decay})
-            layers = [dataclasses.replace(ls, mixer=toy, mixer_prefix="toy.") if i % 2 == 0 else ls
+            layers = [ls.with_part("mixer", toy, prefix="toy.") if i % 2 == 0 else ls
                       for i, ls in enumerate(s.layers)]
             return dataclasses.replace(s, architecture=self.architecture, layers=layers)
 
@@ -320,14 +321,14 @@ def _register_toy_routed():
             self.rotary_dim = int(spec.params["rotary_dim"])
             self.slope = float(spec.params["slope"])
 
-        def table(self, step):
-            """[tokens, rot/2, 2] cosines and sines: pair i turns by position * slope * (i + 1)."""
+        def rotation_table(self, step):
+            """([tokens, rot/2, 2] cosines and sines, rot): pair i turns by position * slope * (i + 1)."""
             key = f"toy_linear_rotary:{self.rotary_dim}:{self.slope}"
             if key not in step.shared:
                 freq = self.slope * torch.arange(1, self.rotary_dim // 2 + 1, dtype=torch.float32, device=step.positions.device)
                 ang = step.positions.float().unsqueeze(1) * freq.unsqueeze(0)
                 step.shared[key] = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
-            return step.shared[key]
+            return step.shared[key], self.rotary_dim
 
     class ToyRoutedConfig:
         architecture = "ToyRoutedForCausalLM"
@@ -351,9 +352,9 @@ def _register_toy_routed():
             layers = []
             for i, ls in enumerate(s.layers):
                 mixer = PartSpec(ls.mixer.kind, {**ls.mixer.params, "position": pos})
-                ls = dataclasses.replace(ls, mixer=mixer)
+                ls = ls.with_part("mixer", mixer)
                 if i % 2:
-                    ls = dataclasses.replace(ls, feed_forward=routed, feed_forward_prefix="routed.")
+                    ls = ls.with_part("feed_forward", routed, prefix="routed.")
                 layers.append(ls)
             return dataclasses.replace(s, architecture=self.architecture, layers=layers)
 
@@ -415,6 +416,149 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
         unregister_architecture(Cfg)
         FEED_FORWARDS.unregister("toy_top1")
         POSITION_ENCODINGS.unregister("toy_linear_rotary")
+
+
+# ------------------------------- a toy block with a post-norm, a position encoding that is no table
+def _register_toy_postnorm():
+    """A block of another shape (a norm BEHIND the mixer as well: ``x += post(mixer(pre(x)))``)
+    with a role the library's block does not have, and a position encoding that is no table of
+    half-split rotations (it turns the interleaved pairs (2i, 2i+1) itself).  Defined here,
+    registered, named by an architecture of their own; the library is not touched."""
+    from hilbert_pruned_8b_b200.config import LlamaConfig, PartSpec, register_architecture
+    from hilbert_pruned_8b_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block,
+                                              PositionEncoding)
+
+    @BLOCKS.register("toy_postnorm")
+    class ToyPostNormBlock(Block):
+        ROLES = {"mixer_norm": NORMS, "mixer": MIXERS, "mixer_post_norm": NORMS, "feed_forward_norm": NORMS,
+                 "feed_forward": FEED_FORWARDS}
+        graph_safe = False
+
+        def __init__(self, layer_spec, ctx):
+            super().__init__(layer_spec, ctx)
+            self.graph_safe = False         # torch operations that allocate
+
+        def forward(self, x, step, cache, state, append):
+            p = self.parts
+            h = torch.empty(x.shape, dtype=self.ctx.dtype, device=x.device)
+            p["mixer_norm"].forward(x, h)
+            mixed = torch.zeros_like(x)                  # the mixer ADDS its output: into zeros here
+            p["mixer"].forward(h, mixed, step, cache, state, append)
+            post = torch.empty_like(x)
+            p["mixer_post_norm"].forward(mixed, post)
+            x += post
+            p["feed_forward_norm"].forward(x, h)
+            p["feed_forward"].forward(h, x, step)
+
+    @POSITION_ENCODINGS.register("toy_interleaved")
+    class ToyInterleaved(PositionEncoding):
+        graph_safe = False
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.freq = float(spec.params["freq"])
+
+        def apply(self, q, k, step):
+            pos = step.positions.float()
+            for x in (q, k):
+                if x is None:
+                    continue
+                hd = x.shape[-1]
+                ang = pos[:, None] * (self.freq * torch.arange(1, hd // 2 + 1, device=x.device, dtype=torch.float32))[None, :]
+                cs, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                a, b = x[..., 0::2].float(), x[..., 1::2].float()
+                x[..., 0::2] = (a * cs - b * sn).to(x.dtype)
+                x[..., 1::2] = (b * cs + a * sn).to(x.dtype)
+
+    class ToyPostNormConfig:
+        architecture = "ToyPostNormForCausalLM"
+        model_type = "toy_postnorm"
+
+        def __init__(self, base, freq):
+            self.base, self.freq = base, freq
+
+        @classmethod
+        def from_dict(cls, root):
+            return cls(LlamaConfig.from_dict({**root, "architectures": ["LlamaForCausalLM"]}), root["toy_freq"])
+
+        def to_dict(self):
+            return {**self.base.to_dict(), "architectures": [self.architecture], "model_type": self.model_type,
+                    "toy_freq": self.freq}
+
+        def model_spec(self):
+            s = self.base.model_spec()
+            pos = PartSpec("toy_interleaved", {"freq": self.freq})
+            layers = []
+            for ls in s.layers:
+                ls = ls.with_block("toy_postnorm").with_part("mixer", PartSpec(ls.mixer.kind, {**ls.mixer.params, "position": pos}))
+                layers.append(ls.with_part("mixer_post_norm", ls.part("mixer_norm"), prefix="post_mixer_layernorm."))
+            return dataclasses.replace(s, architecture=self.architecture, layers=layers)
+
+    register_architecture(ToyPostNormConfig)
+    return ToyPostNormConfig
+
+
+class PlainToyPostNorm(pl.PlainLlama):
+    def __init__(self, folder, freq):
+        super().__init__(folder)
+        self.freq = freq
+
+    def turn(self, x, positions):
+        hd = x.shape[-1]
+        pos = torch.tensor(list(positions), dtype=torch.float32)
+        ang = (pos[:, None] * (np.float32(self.freq) * torch.arange(1, hd // 2 + 1, dtype=torch.float32))[None, :]).double()
+        cs, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = x.clone()
+        out[..., 0::2] = x[..., 0::2] * cs - x[..., 1::2] * sn
+        out[..., 1::2] = x[..., 1::2] * cs + x[..., 0::2] * sn
+        return out
+
+    def layer(self, x, i, positions):
+        c, w, p = self.cfg, self.w, f"{self.prefix}layers.{i}."
+        nh, nkv, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        T = x.shape[0]
+        h = pl.rms_norm(x, w[p + "input_layernorm.weight"], c["rms_norm_eps"])
+        q = self.turn(pl.linear(h, w[p + "self_attn.q_proj.weight"]).view(T, nh, hd), positions)
+        k = self.turn(pl.linear(h, w[p + "self_attn.k_proj.weight"]).view(T, nkv, hd), positions)
+        v = pl.linear(h, w[p + "self_attn.v_proj.weight"]).view(T, nkv, hd)
+        mixed = pl.linear(pl.attention(q, k, v).reshape(T, nh * hd), w[p + "self_attn.o_proj.weight"])
+        x = x + pl.rms_norm(mixed, w[p + "post_mixer_layernorm.weight"], c["rms_norm_eps"])
+        h = pl.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["rms_norm_eps"])
+        return x + pl.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"],
+                             self.rnd)
+
+
+def test_toy_block_with_a_post_norm_and_a_position_encoding_without_a_table(tmp_path):
+    require_gpu()
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.config import unregister_architecture
+    from hilbert_pruned_8b_b200.engine.step import Engine
+    from hilbert_pruned_8b_b200.parts import BLOCKS, POSITION_ENCODINGS
+    Cfg = _register_toy_postnorm()
+    try:
+        cfg = Cfg(hb.LlamaConfig.from_dict(TINY_B), 0.021)
+        folder = hb.weights.write_random_model(str(tmp_path / "postnorm"), cfg, seed=51, fan_in_scale=1.0, norm_std=0.05)
+        eng = Engine.from_folder(folder, "float32", max_tokens=1024)
+        table = eng.model.weight_table()
+        assert any(n.endswith("layers.2.post_mixer_layernorm.weight") for n in table)
+        assert not eng.model.graph_safe
+        v = TINY_B["vocab_size"]
+        reqs = {"p": tt.random_tokens(50, v, 930), "q": tt.random_tokens(21, v, 931), "r": tt.random_tokens(70, v, 932)}
+        ref = tt.plain_logits(PlainToyPostNorm(folder, 0.021), reqs)
+        for make in (tt.trace_whole, lambda r: tt.trace_tail(r, 16),
+                     lambda r: tt.trace_batches([{"p": (r["p"], 30), "q": (r["q"], 21)}, {"r": (r["r"], 5)}])):
+            steps, _ = make(reqs)
+            tt.compare(tt.run_in_process(eng, steps), ref, "float32", "toy post-norm")
+        assert min(eng.cache.pages_free()) == eng.cache.num_pages
+        # a part in a role the block does not have is refused by name
+        bad = cfg.model_spec()
+        bad = dataclasses.replace(bad, layers=[ls.with_block("prenorm") for ls in bad.layers])
+        with pytest.raises(ValueError, match="mixer_post_norm"):
+            Engine(bad, "float32", max_tokens=64)
+    finally:
+        unregister_architecture(Cfg)
+        BLOCKS.unregister("toy_postnorm")
+        POSITION_ENCODINGS.unregister("toy_interleaved")
 
 
 # --------------------------------------------------------------------------- the run order is data
@@ -479,7 +623,7 @@ def test_windowed_layers_give_pages_back_and_match_plain(model_folders, model, w
     from hilbert_pruned_8b_b200.weights import load_tensors
     folder = model_folders[model]
     spec = hb.load_config(folder).model_spec()
-    layers = [dataclasses.replace(ls, mixer=PartSpec("attention", {**ls.mixer.params, "window": window})) for ls in spec.layers]
+    layers = [ls.with_part("mixer", PartSpec("attention", {**ls.mixer.params, "window": window})) for ls in spec.layers]
     spec = dataclasses.replace(spec, layers=layers)
     eng = Engine(spec, dtype, max_tokens=64 * 12)
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16

@@ -50,6 +50,37 @@ def test_random_model_folder_loads_and_is_seeded(tmp_path):
     assert "lm_head.weight" not in t1
 
 
+def test_random_weights_are_a_function_of_seed_name_and_element():
+    """A tensor's values do not depend on which other tensors are drawn, in which order, or on
+    how the work is cut; the draw is a standard normal (mean, deviation, tails, Kolmogorov
+    distance); the tail's own logarithm agrees with the library's."""
+    import numpy as np
+    from hilbert_pruned_8b_b200.weights import random_init as ri
+    table = _table(TINY_B)
+    all_of_it = random_tensors(table, 7, CPU, std=0.02, norm_std=0.01)
+    name = "model.layers.1.mlp.down_proj.weight"
+    alone = random_tensors({name: table[name]}, 7, CPU, std=0.02, norm_std=0.01)
+    assert torch.equal(all_of_it[name], alone[name])
+    other_prefix = random_tensors({"x." + name: table[name]}, 7, CPU)
+    assert not torch.equal(other_prefix["x." + name], alone[name])
+    base = ri.stream_base(7, name)
+    whole = ri.standard_normals(base, 0, 100000)
+    assert np.array_equal(whole[777:999], ri.standard_normals(base, 777, 222))          # element i is element i
+    big = ri.normal_tensor_cpu((5000, 1000), 7, name, 1.0, 0.0, torch.float32).numpy().ravel()   # threaded chunks
+    assert np.array_equal(big[:100000], whole)
+    assert abs(big.mean()) < 2e-3 and abs(big.std() - 1.0) < 2e-3
+    for z, want in ((1.0, 0.158655), (2.0, 0.0227501), (3.0, 0.00134990), (4.0, 3.16712e-5)):
+        tol = 4.0 / (want * big.size) ** 0.5                  # four standard deviations of the count
+        assert abs((big > z).mean() / want - 1) < tol and abs((big < -z).mean() / want - 1) < tol
+    srt = np.sort(big[:200000].astype(np.float64))
+    cdf = 0.5 * (1.0 + np.vectorize(__import__("math").erf)(srt / np.sqrt(2.0)))
+    assert np.abs(cdf - (np.arange(1, srt.size + 1) - 0.5) / srt.size).max() < 0.004
+    p = np.float32(2.0) ** -np.arange(1, 34, dtype=np.float32) * np.float32(1.37)
+    assert np.abs(ri._log32(p) / np.log(p.astype(np.float64)) - 1).max() < 3e-7
+    norm = random_tensors({"n": table["model.norm.weight"]}, 7, CPU, norm_std=0.01, dtype=torch.float32)["n"]
+    assert abs(norm.mean().item() - 1.0) < 0.005 and 0.005 < norm.std().item() < 0.02
+
+
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     cfg = hb.LlamaConfig.from_dict(TINY_B)
     table = _table(TINY_B)
@@ -72,6 +103,23 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     text = str(e)
     assert "missing (2)" in text and "unexpected (1)" in text
     assert "model.layers.0.self_attn.q_proj.weight has shape [160, 161], expected [160, 160]" in text
+
+
+def test_extra_tensors_are_ignored_unless_strict(tmp_path):
+    """A tensor no part asks for is not a fault (the reference never looks at what it does not
+    bind, cleanroom-transformer/src/model.c:391-447); strict loading refuses it by name."""
+    cfg = hb.LlamaConfig.from_dict(TINY_A)
+    table = _table(TINY_A)
+    tensors = random_tensors(table, 1, CPU)
+    tensors["mtp.layers.0.extra.weight"] = torch.zeros(3, 3, dtype=torch.bfloat16)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    got = load_tensors(str(tmp_path), table, torch.bfloat16, CPU)
+    assert "mtp.layers.0.extra.weight" not in got and len(got) == len(table) - 1      # the tied head is optional
+    with pytest.raises(WeightError) as ei:
+        load_tensors(str(tmp_path), table, torch.bfloat16, CPU, strict=True)
+    assert ei.value.unexpected == ["mtp.layers.0.extra.weight"] and not ei.value.missing
 
 
 def test_dtype_rules(tmp_path):
