@@ -28,6 +28,8 @@ class LLM:
     @classmethod
     def load(cls, model: str, dtype: str = "bfloat16", max_tokens: int = 4096, device: int = 0,
              max_batch: int = 64, **kw) -> "LLM":
+        """Further keywords go to the engine: ``max_sequence_tokens`` (the most one sequence may
+        hold; default: the whole cache), ``max_step_tokens``, ``max_sequences``, ``strict_weights``."""
         return cls(Engine.from_folder(model, dtype, max_tokens=max_tokens, device=f"cuda:{device}", **kw), max_batch)
 
     @classmethod
@@ -53,15 +55,21 @@ class LLM:
 
     def logits(self, tokens: Sequence[int], ids: Optional[Sequence[int]] = None, split: int = 0) -> torch.Tensor:
         """Logits at the last position of ``tokens`` (all of the vocabulary, or the given ids),
-        as the reference's ``logits`` command reads them; ``split`` N runs the first N tokens in
-        a step of their own (cleanroom-transformer/src/main.c:351-387)."""
+        as the reference's ``logits`` command reads them.  ``split`` N does what the reference's
+        ``--split N`` does (cleanroom-transformer/src/main.c:363-370): the first N tokens in a
+        step of their own, a snapshot, the rest, a restore, and the rest once more; the logits
+        of that second run are returned, so a rewind that left anything behind would show."""
         eng = self.engine
         seq = eng.open_sequence()
         try:
             toks = [int(t) for t in tokens]
             if 0 < split < len(toks):
                 eng.step_chunked([StepEntry(seq, toks[:split], [])])
-                toks = toks[split:]
+                snap = eng.snapshot(seq)
+                rest = toks[split:]
+                eng.step_chunked([StepEntry(seq, rest, [len(rest) - 1])])
+                eng.restore(seq, snap)
+                toks = rest
             out = eng.step_chunked([StepEntry(seq, toks, [len(toks) - 1])])[0].clone()
         finally:
             eng.close_sequence(seq)

@@ -55,6 +55,15 @@ class Sequence:
     pages_version: int = 0      # counts the changes of `pages`: who keeps a copy compares this
 
 
+@dataclass
+class Snapshot:
+    """A sequence's length and fixed-size state at some moment (``CacheManager.snapshot``)."""
+
+    seq_id: int
+    length: int
+    state: Dict[int, torch.Tensor]
+
+
 class CacheGroup:
     def __init__(self, need: CacheNeed, entries: List[int], num_pages: int, device, dtype,
                  allocate: bool = True):
@@ -138,6 +147,17 @@ class CacheManager:
                 need[gi] += max(0, pages_for(new_len) - have)
         return need
 
+    def check_room(self, seqs_and_lengths: List[Tuple[Sequence, int]]) -> None:
+        """Raises ``CacheFull`` if the pages are not there for each sequence to grow to its new
+        length; reserves nothing.  A group with a window may get by with fewer (it gives pages
+        back as the sequence grows): for such a group this is the worst case."""
+        need = self._pages_needed(seqs_and_lengths)
+        for gi, g in enumerate(self.groups):
+            if g.need.window is None and need[gi] > g.pool.num_free:
+                raise CacheFull(
+                    f"cache: the call needs {need[gi]} more pages of {PAGE_TOKENS} tokens, "
+                    f"{g.pool.num_free} of {g.pool.size} are free (max_tokens {self.max_tokens})")
+
     def reserve(self, seqs_and_lengths: List[Tuple[Sequence, int]]) -> None:
         """Makes room for each sequence to grow to its new length; all or nothing."""
         for seq, new_len in seqs_and_lengths:
@@ -184,22 +204,48 @@ class CacheManager:
         seq.length = new_len
 
     def truncate(self, seq: Sequence, length: int) -> None:
-        """Rewinds a sequence: later keys and values are forgotten (the reference's restore,
-        cpu_backend.c:279-292).  Fixed-size state cannot be rewound this way."""
+        """Rewinds a sequence: later keys and values are forgotten, their pages given back (the
+        reference's restore is a position reset, rows beyond it are overwritten later:
+        cpu_backend.c:279-292).  Fixed-size state cannot be rewound this way: it needs the copy
+        that ``snapshot`` takes."""
+        if self.state and length != seq.length:
+            raise ValueError("cache: a sequence with fixed-size state cannot be rewound by truncation "
+                             "(take a snapshot and restore it)")
+        self._forget_after(seq, length)
+
+    def _forget_after(self, seq: Sequence, length: int) -> None:
+        if not seq.open:
+            raise ValueError(f"cache: sequence {seq.seq_id} is closed")
         if length > seq.length or length < 0:
             raise ValueError("cache: truncate needs 0 <= length <= current length")
-        if self.state and length != seq.length:
-            raise ValueError("cache: a sequence with fixed-size state cannot be rewound by truncation")
         keep = pages_for(length)
         for gi, g in enumerate(self.groups):
             w = g.need.window
             if w is not None and any(p is None for p in seq.pages[gi][max(0, (length - w)) // PAGE_TOKENS:keep]):
                 raise ValueError("cache: pages inside the rewound window were already given back")
+        for gi, g in enumerate(self.groups):
             tail = seq.pages[gi][keep:]
             g.pool.free([p for p in tail if p is not None])
             del seq.pages[gi][keep:]
         seq.pages_version += 1
         seq.length = length
+
+    def snapshot(self, seq: Sequence) -> "Snapshot":
+        """Remembers where a sequence stands: its length and a copy of its fixed-size state (the
+        reference's snapshot copies its other layer kind's state and notes the position,
+        cpu_backend.c:265-277).  Keys and values are not copied: a restore forgets the later ones."""
+        if not seq.open:
+            raise ValueError(f"cache: sequence {seq.seq_id} is closed")
+        return Snapshot(seq.seq_id, seq.length, {e: t[seq.state_slot].clone() for e, t in self.state.items()})
+
+    def restore(self, seq: Sequence, snap: "Snapshot") -> None:
+        """Takes a sequence back to a snapshot of itself: later keys and values are forgotten,
+        the fixed-size state is the snapshot's again."""
+        if snap.seq_id != seq.seq_id:
+            raise ValueError(f"cache: the snapshot is of sequence {snap.seq_id}, not of {seq.seq_id}")
+        self._forget_after(seq, snap.length)
+        for e, t in self.state.items():
+            t[seq.state_slot].copy_(snap.state[e])
 
     # ------------------------------------------------------------------ views
     def group_of(self, entry: int) -> int:

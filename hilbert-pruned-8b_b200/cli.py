@@ -7,7 +7,7 @@ names where it has them (cleanroom-transformer/src/main.c:11-50,66-129: ``--mode
 commands:
   generate  tokens for prompts   --input rows.jsonl --output results.jsonl | --tokens "1 2 3"
                                  [--max-new-tokens N] [--temperature T] [--seed S] [--stop-ids "7 9"] [--batch N]
-  logits    raw logits           --tokens "1 2 3" [--ids "4 5"] [--split N]
+  logits    raw logits           --tokens "1 2 3" [--ids "4 5"] [--split N]   (N: prefix, snapshot, rest, restore, rest)
   shapes    the weight table as JSON (config only, no GPU)
   random    write a model folder --config config.json --output DIR [--seed S] [--std X] [--norm-std X]
   selftest  a tiny random model: token by token against whole prompts, on the GPU
@@ -36,6 +36,11 @@ def _parser() -> argparse.ArgumentParser:
                     help="model precision; changing it can change the tokens")
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--max-tokens", type=int, default=4096, help="context: tokens the cache holds")
+    ap.add_argument("--max-sequence-tokens", type=int, default=None,
+                    help="most tokens of one sequence (default: --max-tokens; generation also stops at the "
+                         "model's max_position_embeddings)")
+    ap.add_argument("--strict-weights", action="store_true",
+                    help="tensors in the folder that the model does not read are an error")
     ap.add_argument("--input", help="JSON lines: {\"id\":..., \"tokens\":[...], \"max_new_tokens\":..., \"temperature\":..., \"seed\":...}")
     ap.add_argument("--output", help="JSON lines, one per row; must not exist yet")
     ap.add_argument("--tokens", help="one prompt as token ids")
@@ -85,7 +90,8 @@ def main(argv=None) -> int:
     if a.command == "logits":
         if not a.tokens:
             ap.error("logits needs --tokens")
-        llm = LLM.load(a.model, a.dtype, a.max_tokens, a.device)
+        llm = LLM.load(a.model, a.dtype, a.max_tokens, a.device, max_sequence_tokens=a.max_sequence_tokens,
+                       strict_weights=a.strict_weights)
         out = llm.logits(_ids(a.tokens), _ids(a.ids) if a.ids else None, a.split)
         print(" ".join(repr(float(x)) for x in out.tolist()))
         return 0
@@ -106,7 +112,8 @@ def main(argv=None) -> int:
             dest = open(a.output, "x")
         except FileExistsError:
             ap.error("Output must be new")
-    llm = LLM.load(a.model, a.dtype, a.max_tokens, a.device, max_batch=a.batch)
+    llm = LLM.load(a.model, a.dtype, a.max_tokens, a.device, max_batch=a.batch,
+                   max_sequence_tokens=a.max_sequence_tokens, strict_weights=a.strict_weights)
     reqs = [GenerationRequest([int(t) for t in r["tokens"]], int(r.get("max_new_tokens", a.max_new_tokens)),
                               SamplingParams(float(r.get("temperature", a.temperature)), int(r.get("seed", a.seed))),
                               r.get("stop_token_ids", stop), i) for i, r in enumerate(rows)]
@@ -129,7 +136,7 @@ def run(argv=None) -> int:
     from .weights import SafetensorsError, WeightError
     try:
         return main(argv)
-    except (ConfigError, WeightError, SafetensorsError, ValueError, RuntimeError) as e:
+    except (ConfigError, WeightError, SafetensorsError, ValueError, RuntimeError) as e:     # KernelError is a RuntimeError
         print(f"error: {e}", file=sys.stderr)
         return 1
 

@@ -29,6 +29,7 @@
 // the positions come from a copy that finished before the step's first kernel), the wait
 // happens before the first request of that page, or after the prologue.  -1: the caller
 // has waited already.  `after_wait` runs right after the wait (the place to write that page).
+// `status`, `batch_row`: where a page number outside the cache is noted (common.cuh).
 // `patch_page` (>= 0): when that page has arrived, row `patch_row` of its key and value tiles is
 // overwritten with k_new / v_new (HD values each, in shared memory): the new token's key and
 // value, for a page that was requested before they existed.
@@ -37,7 +38,8 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
                                                   const int* __restrict__ pt, int n_pages, int nkv, int g, int lo,
                                                   int len, int p_begin, int p_end, float scale_log2e, uint8_t* smem,
                                                   F&& after_prologue, int fresh_page, W&& after_wait, int patch_page = -1,
-                                                  int patch_row = 0, const bf16* k_new = nullptr, const bf16* v_new = nullptr) {
+                                                  int patch_row = 0, const bf16* k_new = nullptr, const bf16* v_new = nullptr,
+                                                  int* status = nullptr, int batch_row = 0) {
     constexpr int ROW_BYTES = HD * 2;
     constexpr int TILE_BYTES = HB_PAGE_TOKENS * ROW_BYTES;        // one page of K (or V) of one kv head
     constexpr int CHUNKS = ROW_BYTES / 16;
@@ -46,8 +48,13 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     auto load_page = [&](int stage, int page_idx) {
         if (page_idx < p_end) {
+            // every page of [p_begin, p_end) holds a key the query sees: one that is missing from the
+            // table or outside the cache is a fault of the host's bookkeeping (noted, not trapped)
             int page = pt[page_idx];
-            if (page < 0 || page >= n_pages) page = 0;      // never read outside the cache
+            if (page < 0 || page >= n_pages) {
+                if (tid == 0) hb_note(status, HB_STATUS_PAGE, 1 + batch_row);
+                page = 0;                                   // never read outside the cache
+            }
             const uint8_t* ksrc = (const uint8_t*)(kc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
             const uint8_t* vsrc = (const uint8_t*)(vc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
             const uint32_t kdst = smem_base + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
@@ -251,8 +258,10 @@ __device__ __forceinline__ void combine_by_last_split(int b, int g, int G, int S
 // equal shares of THIS sequence's pages, not of the longest sequence's or of the page table's
 // width, so that every split has work whatever the length (a sequence a little above half the
 // table's width would leave half the splits empty otherwise).
-__device__ __forceinline__ void split_pages(int z, int S, int lo, int len, int& p_begin, int& p_end, int& per_split) {
-    const int first = lo / HB_PAGE_TOKENS, last = (len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS;
+// `pt_width` bounds the pages: a position beyond the page table reads nothing outside it.
+__device__ __forceinline__ void split_pages(int z, int S, int lo, int len, int pt_width, int& p_begin, int& p_end,
+                                            int& per_split) {
+    const int first = lo / HB_PAGE_TOKENS, last = min((len + HB_PAGE_TOKENS - 1) / HB_PAGE_TOKENS, pt_width);
     per_split = max(1, (last - first + S - 1) / S);
     p_begin = first + z * per_split;
     p_end = min(p_begin + per_split, last);
@@ -265,7 +274,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                    const int* __restrict__ page_table, int pt_width, const int* __restrict__ positions,
                    float* part_o, float* part_ml, int nh, int nkv, float scale_log2e,
-                   int window, int n_pages, int* counters, bf16* out, long long out_stride) {
+                   int window, int n_pages, int* counters, bf16* out, long long out_stride, int* status) {
     __shared__ int is_last;
     __shared__ float w_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];
     __shared__ float l_split[COMBINE ? 16 * AD_MAX_SPLITS : 1];
@@ -280,7 +289,7 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
     const int len = positions[b] + 1;
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;
     int p_begin, p_end, pages_per_split;
-    split_pages(z, S, lo, len, p_begin, p_end, pages_per_split);
+    split_pages(z, S, lo, len, pt_width, p_begin, p_end, pages_per_split);
     const int* pt = page_table + (size_t)b * pt_width;
 
     if (p_begin >= p_end) {                       // nothing to read: an empty partial
@@ -318,7 +327,8 @@ attn_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* _
             qf[ks][2] = r0 < G ? __ldcg(q0 + ks * 8 + 4) : 0u;
             qf[ks][3] = r0 + 8 < G ? __ldcg(q1 + ks * 8 + 4) : 0u;
         }
-    }, (len - 1) / HB_PAGE_TOKENS, [] {});
+    }, (len - 1) / HB_PAGE_TOKENS, [] {}, -1, 0, nullptr, nullptr, status, b);
+    if (tid == 0 && len > pt_width * HB_PAGE_TOKENS) hb_note(status, HB_STATUS_PAGE, 1 + b);   // a position beyond the table
     const float* so = reinterpret_cast<const float*>(smem);
     const float* sm = so + 4 * 16 * HD;
     const float* sl = sm + 4 * 16;
@@ -364,7 +374,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                          bf16* kc, bf16* vc, const int* __restrict__ page_table, int pt_width,
                          const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
                          int* __restrict__ counters, bf16* __restrict__ out, long long out_stride, int nh, int nkv,
-                         float scale_log2e, int window, int n_pages, int append) {
+                         float scale_log2e, int window, int n_pages, int append, int* status) {
     pdl_trigger();
     constexpr int KSTEPS = HD / 16;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -379,7 +389,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
     const int pos = positions[b], len = pos + 1;
     const int lo = (window > 0 && len - window > 0) ? len - window : 0;
     int p_begin, p_end, pages_per_split;
-    split_pages(z, S, lo, len, p_begin, p_end, pages_per_split);
+    split_pages(z, S, lo, len, pt_width, p_begin, p_end, pages_per_split);
     const int* pt = page_table + (size_t)b * pt_width;
     // what the kernels in front wrote (projections, table) is read after the wait only, through
     // pointers that the compiler cannot take for memory that never changes
@@ -413,8 +423,9 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
         if (tid < HD) vx = vn[tid];
     };
     auto append_new = [&]() {
-        const int page = pt[pos / HB_PAGE_TOKENS];
-        const bool in_cache = page >= 0 && page < n_pages;   // the host reserved the page; never write outside the cache
+        const int page = pos / HB_PAGE_TOKENS < pt_width ? pt[pos / HB_PAGE_TOKENS] : -1;
+        const bool in_cache = page >= 0 && page < n_pages;   // the host reserved the page: else a fault of its bookkeeping
+        if (!in_cache && tid == 0) hb_note(status, HB_STATUS_PAGE, 1 + b);    // never write outside the cache
         const size_t off = in_cache ? cache_offset(page, g, pos, nkv, HD) : 0;
         if (tid < half) {
             float y1, y2;
@@ -486,7 +497,12 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, long long qkv_stride, con
                 qf[ks][2] = *reinterpret_cast<const uint32_t*>(q_rot + r0 * HD + ks * 16 + c + 8);
                 qf[ks][3] = *reinterpret_cast<const uint32_t*>(q_rot + (r0 + 8) * HD + ks * 16 + c + 8);
             }
-        }, 1 << 30, waited, owner ? pos / HB_PAGE_TOKENS : -1, pos % HB_PAGE_TOKENS, kv_new, kv_new + HD);
+            // Before the wait only pages that no kernel of this step writes may be requested.  A layer
+            // that appends writes the new token's row itself (and patches its copy); one that reads
+            // another layer's cache finds that row written earlier in this step, so the new token's
+            // page is requested after the wait.
+        }, append ? (1 << 30) : pos / HB_PAGE_TOKENS, waited, owner ? pos / HB_PAGE_TOKENS : -1, pos % HB_PAGE_TOKENS, kv_new,
+           kv_new + HD, status, b);
         const float* so = reinterpret_cast<const float*>(smem);
         const float* sm = so + 4 * 16 * HD;
         const float* sl = sm + 4 * 16;
@@ -579,11 +595,12 @@ template <int HD, bool COMBINE>
 static int launch_decode_splits(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
                                 int pt_width, const int* positions, float* part_o, float* part_ml, int* counters, void* out,
                                 long long out_stride, int batch, int nh, int nkv, float scale, int window, int splits,
-                                int n_pages, cudaStream_t s) {
+                                int n_pages, int* status, cudaStream_t s) {
     constexpr int PIPE = AD_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
     constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
-    static bool attr_set = false;
+    static bool attr_done[HB_MAX_DEVICES] = {};
+    bool& attr_set = attr_done[hb_device_slot()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, COMBINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("attention_decode: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
@@ -591,7 +608,7 @@ static int launch_decode_splits(const void* q, long long q_stride, const void* k
     }
     hb_launch(attn_decode_kernel<HD, COMBINE>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)q, q_stride,
               (const bf16*)kc, (const bf16*)vc, page_table, pt_width, positions, part_o, part_ml, nh, nkv, scale * AD_LOG2E, window,
-              n_pages, counters, (bf16*)out, out_stride);
+              n_pages, counters, (bf16*)out, out_stride, status);
     return hb_check_launch("attention_decode");
 }
 
@@ -599,14 +616,14 @@ template <int HD>
 static int launch_decode(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
                          int pt_width, const int* positions, float* scratch, int* counters, void* out, long long out_stride,
                          int batch, int nh, int nkv, float scale, int window, int splits, int n_pages,
-                         cudaStream_t s) {
+                         int* status, cudaStream_t s) {
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)batch * nh * splits * HD;
     if (counters != nullptr)
         return launch_decode_splits<HD, true>(q, q_stride, kc, vc, page_table, pt_width, positions, part_o, part_ml, counters, out,
-                                              out_stride, batch, nh, nkv, scale, window, splits, n_pages, s);
+                                              out_stride, batch, nh, nkv, scale, window, splits, n_pages, status, s);
     if (launch_decode_splits<HD, false>(q, q_stride, kc, vc, page_table, pt_width, positions, part_o, part_ml, nullptr, out,
-                                        out_stride, batch, nh, nkv, scale, window, splits, n_pages, s))
+                                        out_stride, batch, nh, nkv, scale, window, splits, n_pages, status, s))
         return 1;
     dim3 cgrid(batch, nh);
     hb_launch(attn_decode_combine_kernel<bf16>, dim3(cgrid), dim3(HD), 0, s, part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
@@ -620,12 +637,15 @@ static int launch_decode(const void* q, long long q_stride, const void* kc, cons
 static int attention_decode_any(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                 const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
                                 void* out, long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim,
-                                float scale, int window, int splits, int max_pages, int n_pages, void* stream) {
+                                float scale, int window, int splits, int max_pages, int n_pages, int* status,
+                                void* stream) {
     if (batch == 0) return 0;
     HB_REQUIRE(hb_attention_decode_supported(n_heads, n_kv_heads, head_dim),
                "attention_decode: head size %d with %d heads over %d kv heads is not built (64 or 128, groups up to 16)",
                head_dim, n_heads, n_kv_heads);
     HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && scratch != nullptr, "attention_decode: bad sizes");
+    HB_REQUIRE(pt_width >= 1 && max_pages <= pt_width, "attention_decode: %d pages per sequence do not fit a page table of width %d",
+               max_pages, pt_width);
     HB_REQUIRE(batch <= 65535 && n_kv_heads <= 65535, "attention_decode: batch or kv heads too large for one launch");
     HB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q & 3) == 0, "attention_decode: queries must be 4-byte aligned");
     HB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "attention_decode: cache must be 16-byte aligned");
@@ -635,17 +655,17 @@ static int attention_decode_any(const void* q, long long q_stride, const void* k
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 128)
         return launch_decode<128>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out,
-                                  out_stride, batch, n_heads, n_kv_heads, scale, window, splits, n_pages, s);
+                                  out_stride, batch, n_heads, n_kv_heads, scale, window, splits, n_pages, status, s);
     return launch_decode<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out, out_stride,
-                             batch, n_heads, n_kv_heads, scale, window, splits, n_pages, s);
+                             batch, n_heads, n_kv_heads, scale, window, splits, n_pages, status, s);
 }
 
 extern "C" int hb_attention_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                    const int* page_table, int pt_width, const int* positions, float* scratch, void* out,
                                    long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim, float scale,
-                                   int window, int splits, int max_pages, int n_pages, void* stream) {
+                                   int window, int splits, int max_pages, int n_pages, int* status, void* stream) {
     return attention_decode_any(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, nullptr, out, out_stride,
-                                batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
+                                batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, status, stream);
 }
 
 // The same in ONE launch: the last split of a (sequence, kv head) to finish combines the
@@ -654,10 +674,10 @@ extern "C" int hb_attention_decode_combined(const void* q, long long q_stride, c
                                             const int* page_table, int pt_width, const int* positions, float* scratch,
                                             int* counters, void* out, long long out_stride, int batch, int n_heads,
                                             int n_kv_heads, int head_dim, float scale, int window, int splits, int max_pages,
-                                            int n_pages, void* stream) {
+                                            int n_pages, int* status, void* stream) {
     HB_REQUIRE(counters != nullptr, "attention_decode_combined: no counters");
     return attention_decode_any(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, counters, out, out_stride,
-                                batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
+                                batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, status, stream);
 }
 
 #define AD_DEEP_STAGES 6        // when every CTA has an SM of its own: five pages in flight instead of two
@@ -666,12 +686,13 @@ template <int HD, bool COMBINE, int STAGES>
 static int launch_decode_fused_stages(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
                                       const int* page_table, int pt_width, const int* positions, float* part_o, float* part_ml,
                                       int* counters, void* out, long long out_stride, int batch, int nh, int nkv, float scale,
-                                      int window, int splits, int n_pages, int append, cudaStream_t s) {
+                                      int window, int splits, int n_pages, int append, int* status, cudaStream_t s) {
     constexpr int PIPE = STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
     constexpr int MERGE = (4 * 16 * HD + 2 * 4 * 16) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
     static_assert(SMEM + 8 * 1024 <= 227 * 1024, "page pipeline does not fit shared memory");
-    static bool attr_set = false;
+    static bool attr_done[HB_MAX_DEVICES] = {};
+    bool& attr_set = attr_done[hb_device_slot()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<HD, COMBINE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("attention_decode_fused: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
@@ -679,12 +700,13 @@ static int launch_decode_fused_stages(const void* qkv, long long stride, const f
     }
     hb_launch(attn_decode_fused_kernel<HD, COMBINE, STAGES>, dim3(splits, nkv, batch), dim3(AD_THREADS), SMEM, s, (const bf16*)qkv, stride,
               (const float2*)table, rot, (bf16*)kc, (bf16*)vc, page_table, pt_width, positions, part_o, part_ml, counters,
-              (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, n_pages, append);
+              (bf16*)out, out_stride, nh, nkv, scale * AD_LOG2E, window, n_pages, append, status);
     return hb_check_launch("attention_decode_fused");
 }
 
 static int decode_sm_count() {
-    static int n = 0;
+    static int count[HB_MAX_DEVICES] = {};
+    int& n = count[hb_device_slot()];
     if (n == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
@@ -699,14 +721,14 @@ template <int HD, bool COMBINE>
 static int launch_decode_fused_splits(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
                                       const int* page_table, int pt_width, const int* positions, float* part_o, float* part_ml,
                                       int* counters, void* out, long long out_stride, int batch, int nh, int nkv, float scale,
-                                      int window, int splits, int n_pages, int append, cudaStream_t s) {
+                                      int window, int splits, int n_pages, int append, int* status, cudaStream_t s) {
     if ((long long)splits * nkv * batch <= decode_sm_count())
         return launch_decode_fused_stages<HD, COMBINE, AD_DEEP_STAGES>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions,
                                                                        part_o, part_ml, counters, out, out_stride, batch, nh, nkv,
-                                                                       scale, window, splits, n_pages, append, s);
+                                                                       scale, window, splits, n_pages, append, status, s);
     return launch_decode_fused_stages<HD, COMBINE, AD_STAGES>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o,
                                                               part_ml, counters, out, out_stride, batch, nh, nkv, scale, window,
-                                                              splits, n_pages, append, s);
+                                                              splits, n_pages, append, status, s);
 }
 
 template <int HD>
@@ -739,16 +761,16 @@ template <int HD>
 static int launch_decode_fused(const void* qkv, long long stride, const float* table, int rot, void* kc, void* vc,
                                const int* page_table, int pt_width, const int* positions, float* scratch, int* counters,
                                void* out, long long out_stride, int batch, int nh, int nkv, float scale, int window,
-                               int splits, int n_pages, int append, cudaStream_t s) {
+                               int splits, int n_pages, int append, int* status, cudaStream_t s) {
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)batch * nh * splits * HD;
     if (counters != nullptr || splits == 1)
         return launch_decode_fused_splits<HD, true>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o,
                                                     part_ml, counters, out, out_stride, batch, nh, nkv, scale, window, splits,
-                                                    n_pages, append, s);
+                                                    n_pages, append, status, s);
     if (launch_decode_fused_splits<HD, false>(qkv, stride, table, rot, kc, vc, page_table, pt_width, positions, part_o, part_ml,
                                               nullptr, out, out_stride, batch, nh, nkv, scale, window, splits,
-                                              n_pages, append, s))
+                                              n_pages, append, status, s))
         return 1;
     hb_launch(attn_decode_combine_kernel<bf16>, dim3(batch, nh), dim3(HD), 0, s, part_o, part_ml, (bf16*)out, out_stride, nh, HD, splits);
     return hb_check_launch("attention_decode_combine");
@@ -765,12 +787,14 @@ extern "C" int hb_attention_decode_fused(const void* qkv, long long stride, cons
                                          void* v_cache, const int* page_table, int pt_width, const int* positions,
                                          float* scratch, int* counters, void* out, long long out_stride, int batch,
                                          int n_heads, int n_kv_heads, int head_dim, float scale, int window, int splits,
-                                         int max_pages, int n_pages, int append, void* stream) {
+                                         int max_pages, int n_pages, int append, int* status, void* stream) {
     if (batch == 0) return 0;
     HB_REQUIRE(hb_attention_decode_supported(n_heads, n_kv_heads, head_dim),
                "attention_decode_fused: head size %d with %d heads over %d kv heads is not built (64 or 128, groups up to 16)",
                head_dim, n_heads, n_kv_heads);
     HB_REQUIRE(batch > 0 && splits >= 1 && max_pages >= 1 && scratch, "attention_decode_fused: bad sizes");
+    HB_REQUIRE(pt_width >= 1 && max_pages <= pt_width, "attention_decode_fused: %d pages per sequence do not fit a page table of width %d",
+               max_pages, pt_width);
     HB_REQUIRE(counters == nullptr || splits <= AD_MAX_SPLITS, "attention_decode_fused: at most %d splits when the last one combines, got %d",
                AD_MAX_SPLITS, splits);
     HB_REQUIRE(batch <= 65535 && n_kv_heads <= 65535, "attention_decode_fused: batch or kv heads too large for one launch");
@@ -782,10 +806,10 @@ extern "C" int hb_attention_decode_fused(const void* qkv, long long stride, cons
     if (head_dim == 128)
         return launch_decode_fused<128>(qkv, stride, table, rot, k_cache, v_cache, page_table, pt_width, positions, scratch,
                                         counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits,
-                                        n_pages, append, s);
+                                        n_pages, append, status, s);
     return launch_decode_fused<64>(qkv, stride, table, rot, k_cache, v_cache, page_table, pt_width, positions, scratch,
                                    counters, out, out_stride, batch, n_heads, n_kv_heads, scale, window, splits, n_pages,
-                                   append, s);
+                                   append, status, s);
 }
 
 // ------------------------------------------------------------------ no-allocation entry point
@@ -834,5 +858,5 @@ extern "C" int hb_attention_decode_noalloc(const void* q, long long q_stride, co
     float* scratch = nullptr;
     if (noalloc_scratch_address(&scratch)) return 1;
     return hb_attention_decode(q, q_stride, k_cache, v_cache, page_table, pt_width, positions, scratch, out, out_stride,
-                               batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, stream);
+                               batch, n_heads, n_kv_heads, head_dim, scale, window, splits, max_pages, n_pages, nullptr, stream);
 }

@@ -18,7 +18,8 @@ __global__ void __launch_bounds__(AG_THREADS)
 attention_general_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __restrict__ k_cache,
                          const TC* __restrict__ v_cache, const int* __restrict__ page_table, int pt_width,
                          const int* __restrict__ tok_seq, const int* __restrict__ positions, TO* __restrict__ out,
-                         long long out_stride, int nh, int nkv, int hd, float scale, int window) {
+                         long long out_stride, int nh, int nkv, int hd, float scale, int window, int n_pages,
+                         int* status) {
     pdl_trigger();
     pdl_wait();
     q = pdl_fresh(q);
@@ -47,7 +48,9 @@ attention_general_kernel(const TQ* __restrict__ q, long long q_stride, const TC*
         const int first_page = s0 / HB_PAGE_TOKENS;
         if (tid < AG_THREADS / HB_PAGE_TOKENS + 1) {
             const int pg = first_page + tid;
-            pages[tid] = (pg < pt_width) ? pt[pg] : -1;
+            int page = (pg < pt_width) ? pt[pg] : -1;
+            if (page >= n_pages) page = -1;                     // never read outside the cache
+            pages[tid] = page;
         }
         __syncthreads();
         const int s = s0 + tid;
@@ -55,6 +58,8 @@ attention_general_kernel(const TQ* __restrict__ q, long long q_stride, const TC*
         float sc = -INFINITY;
         if (valid) {
             const int page = pages[s / HB_PAGE_TOKENS - first_page];
+            // a key this query sees on a page the table does not hold: a fault of the host's bookkeeping
+            if (page < 0) hb_note(status, HB_STATUS_PAGE, 1 + tok_seq[t]);
             if (page >= 0) {
                 const TC* kr = k_cache + cache_offset(page, g, s, nkv, hd);
                 float dot = 0.0f;
@@ -102,9 +107,9 @@ extern "C" int hb_attention_general(const void* q, int q_dtype, long long q_stri
                                     const void* v_cache, int cache_dtype, const int* page_table, int pt_width,
                                     const int* tok_seq, const int* positions, void* out, int out_dtype,
                                     long long out_stride, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                    float scale, int window, void* stream) {
+                                    float scale, int window, int n_pages, int* status, void* stream) {
     if (n_tokens == 0) return 0;
-    HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0, "attention: bad sizes");
+    HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0 && n_pages > 0, "attention: bad sizes");
     HB_REQUIRE(n_heads % n_kv_heads == 0, "attention: %d heads are no multiple of %d kv heads", n_heads, n_kv_heads);
     HB_REQUIRE(head_dim <= AG_MAX_HD, "attention: head size %d is larger than %d", head_dim, AG_MAX_HD);
     HB_REQUIRE(n_heads <= 65535, "attention: too many heads");
@@ -113,7 +118,7 @@ extern "C" int hb_attention_general(const void* q, int q_dtype, long long q_stri
 #define HB_AG_LAUNCH(TQ, TC, TO)                                                                                      \
     hb_launch(attention_general_kernel<TQ, TC, TO>, dim3(grid), dim3(AG_THREADS), 0, s,                                                  \
         (const TQ*)q, q_stride, (const TC*)k_cache, (const TC*)v_cache, page_table, pt_width, tok_seq, positions,     \
-        (TO*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window)
+        (TO*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window, n_pages, status)
     if (q_dtype == HB_F32 && cache_dtype == HB_F32 && out_dtype == HB_F32) HB_AG_LAUNCH(float, float, float);
     else if (q_dtype == HB_BF16 && cache_dtype == HB_BF16 && out_dtype == HB_BF16) HB_AG_LAUNCH(bf16, bf16, bf16);
     else return hb_fail("attention: unsupported dtypes q %d cache %d out %d", q_dtype, cache_dtype, out_dtype);

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(AP_THREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                     const int* __restrict__ page_table, int pt_width, const int* __restrict__ seq_start,
                     const int* __restrict__ seq_pos0, bf16* __restrict__ out, long long out_stride, int n_seqs, int nh,
-                    int nkv, float scale_log2e, int window, int n_pages) {
+                    int nkv, float scale_log2e, int window, int n_pages, int* status) {
     pdl_trigger();
     pdl_wait();
     q = pdl_fresh(q);
@@ -82,8 +82,13 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     auto load_page = [&](int stage, int page_idx) {
         if (page_idx < p_end) {
-            int page = pt[page_idx];
-            if (page < 0 || page >= n_pages) page = 0;
+            // every page of [p_begin, p_end) holds a key that a row of this CTA sees: one that is
+            // missing or outside the cache is a fault of the host's bookkeeping
+            int page = page_idx < pt_width ? pt[page_idx] : -1;
+            if (page < 0 || page >= n_pages) {
+                if (tid == 0) hb_note(status, HB_STATUS_PAGE, 1 + b);
+                page = 0;                                       // never read outside the cache
+            }
             const uint8_t* ksrc = (const uint8_t*)(kc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
             const uint8_t* vsrc = (const uint8_t*)(vc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
             const uint32_t kdst = smem_base + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
@@ -214,9 +219,11 @@ extern "C" int hb_attention_prefill_supported(int n_heads, int n_kv_heads, int h
 template <int HD>
 static int launch_prefill(const void* q, long long q_stride, const void* kc, const void* vc, const int* page_table,
                           int pt_width, const int* seq_start, const int* seq_pos0, void* out, long long out_stride,
-                          int n_seqs, int q_blocks, int nh, int nkv, float scale, int window, int n_pages, cudaStream_t s) {
+                          int n_seqs, int q_blocks, int nh, int nkv, float scale, int window, int n_pages, int* status,
+                          cudaStream_t s) {
     constexpr int SMEM = AP_STAGES * 2 * HB_PAGE_TOKENS * HD * 2;
-    static bool attr_set = false;
+    static bool attr_done[HB_MAX_DEVICES] = {};
+    bool& attr_set = attr_done[hb_device_slot()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("attention_prefill: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
@@ -225,7 +232,7 @@ static int launch_prefill(const void* q, long long q_stride, const void* kc, con
     dim3 grid(nh, q_blocks);
     hb_launch(attn_prefill_kernel<HD>, dim3(grid), dim3(AP_THREADS), SMEM, s, (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, page_table,
                                                            pt_width, seq_start, seq_pos0, (bf16*)out, out_stride, n_seqs, nh, nkv,
-                                                           scale * AP_LOG2E, window, n_pages);
+                                                           scale * AP_LOG2E, window, n_pages, status);
     return hb_check_launch("attention_prefill");
 }
 
@@ -235,7 +242,7 @@ static int launch_prefill(const void* q, long long q_stride, const void* kc, con
 extern "C" int hb_attention_prefill(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                     const int* page_table, int pt_width, const int* seq_start, const int* seq_pos0,
                                     void* out, long long out_stride, int n_seqs, int q_blocks, int n_heads, int n_kv_heads,
-                                    int head_dim, float scale, int window, int n_pages, void* stream) {
+                                    int head_dim, float scale, int window, int n_pages, int* status, void* stream) {
     if (n_seqs == 0 || q_blocks == 0) return 0;
     HB_REQUIRE(hb_attention_prefill_supported(n_heads, n_kv_heads, head_dim),
                "attention_prefill: head size %d with %d heads over %d kv heads is not built (64 or 128)", head_dim, n_heads,
@@ -247,7 +254,7 @@ extern "C" int hb_attention_prefill(const void* q, long long q_stride, const voi
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 128)
         return launch_prefill<128>(q, q_stride, k_cache, v_cache, page_table, pt_width, seq_start, seq_pos0, out, out_stride,
-                                   n_seqs, q_blocks, n_heads, n_kv_heads, scale, window, n_pages, s);
+                                   n_seqs, q_blocks, n_heads, n_kv_heads, scale, window, n_pages, status, s);
     return launch_prefill<64>(q, q_stride, k_cache, v_cache, page_table, pt_width, seq_start, seq_pos0, out, out_stride, n_seqs,
-                              q_blocks, n_heads, n_kv_heads, scale, window, n_pages, s);
+                              q_blocks, n_heads, n_kv_heads, scale, window, n_pages, status, s);
 }

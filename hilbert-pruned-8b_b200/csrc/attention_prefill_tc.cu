@@ -198,7 +198,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int pg = 0; pg < 2; pg++) {
                     const int pi = (jt0 + it) * 2 + pg;
                     int page = pi < pt_width ? pt[pi] : -1;
-                    if (page < 0 || page >= n_pages) page = 0;      // masked keys; never read outside the cache
+                    if (page < 0 || page >= n_pages) {
+                        // a tile's second page may lie behind the sequence's end (its keys are masked);
+                        // a page between the oldest key the first row sees and the last row's own key
+                        // must exist: the host's bookkeeping is at fault.  `error_flag` points at the
+                        // status words (common.cuh)
+                        if (page >= n_pages || (pi >= lo_cta / HB_PAGE_TOKENS && pi <= last_pos / HB_PAGE_TOKENS))
+                            hb_note(error_flag, HB_STATUS_PAGE, 1 + b);
+                        page = 0;                                   // never read outside the cache
+                    }
                     const int row = (page * nkv + g) * HB_PAGE_TOKENS;
                     for (int half = 0; half < HALVES; half++)
                         tma_load_2d(dst + half * FA_HALF_BYTES + pg * (FA_HALF_BYTES / 2), map, bar, half * 64, row);

@@ -22,6 +22,20 @@ int hb_check_launch(const char* what);
 
 typedef __nv_bfloat16 bf16;
 
+// Device status words: an int32[HB_STATUS_WORDS] of the caller that the host reads where it
+// waits anyway.  A kernel that meets a fault traps nothing: it notes the FIRST fault of its
+// kind (a non-zero code), carries on with a safe value (a clamped page, a skipped write), and
+// the host raises once it has read the words.  A null pointer switches the notes off.
+//   [HB_STATUS_WAIT]       a bounded wait of a tensor-core kernel ran out (the code says which)
+//   [HB_STATUS_NONFINITE]  a row of logits handed to a sampler was not finite (1 + row)
+//   [HB_STATUS_PAGE]       a page number that attention or the cache append needed was outside
+//                          the cache, or missing from the page table (1 + sequence's row in the batch)
+//   [HB_STATUS_TOKEN]      a token id outside the vocabulary reached the embedding (1 + token's row)
+enum { HB_STATUS_WAIT = 0, HB_STATUS_NONFINITE = 1, HB_STATUS_PAGE = 2, HB_STATUS_TOKEN = 3, HB_STATUS_WORDS = 4 };
+__device__ __forceinline__ void hb_note(int* status, int word, int code) {
+    if (status != nullptr) atomicCAS(status + word, 0, code);
+}
+
 // Programmatic dependent launch.  Every kernel of the library is launched with the
 // "programmatic stream serialization" attribute, so it may be scheduled while the kernel
 // before it in the stream is still running; it calls pdl_wait() before it touches anything
@@ -136,6 +150,15 @@ __device__ __forceinline__ T* pdl_fresh(T* p) {
 }
 
 bool hb_pdl_enabled();
+
+// One-time set-up that belongs to a device (shared-memory opt-ins, SM counts) is kept per
+// device: `static bool done[HB_MAX_DEVICES]` indexed by the current device.
+#define HB_MAX_DEVICES 64
+static inline int hb_device_slot() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= HB_MAX_DEVICES) d = 0;
+    return d;
+}
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t hb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -9,26 +9,29 @@
 // x[t,:] = float(E[token[t],:])   (cpu_backend.c:236; cuda_backend.cu:66-70)
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out,
-                             int hidden, int vocab) {
+                             int hidden, int vocab, int* status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     int tok = tokens[t];
-    if (tok < 0 || tok >= vocab) tok = 0;  // the host checked the range; never read outside the table
+    if (tok < 0 || tok >= vocab) {         // the host checks what it knows; tokens a sampler left on the device it cannot
+        if (threadIdx.x == 0) hb_note(status, HB_STATUS_TOKEN, 1 + t);
+        tok = 0;                           // never read outside the table
+    }
     const TW* row = table + (size_t)tok * hidden;
     float* o = out + (size_t)t * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
 }
 
 extern "C" int hb_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int hidden,
-                        int vocab, void* stream) {
+                        int vocab, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == HB_BF16)
-        hb_launch(embed_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, out, hidden, vocab);
+        hb_launch(embed_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, out, hidden, vocab, status);
     else if (table_dtype == HB_F32)
-        hb_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, out, hidden, vocab);
+        hb_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, out, hidden, vocab, status);
     else
         return hb_fail("embed: unsupported table dtype %d", table_dtype);
     return hb_check_launch("embed");
@@ -208,7 +211,7 @@ __global__ void __launch_bounds__(256)
 rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot, int nh,
                       int nkv, int hd, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                       const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
-                      const int* __restrict__ positions, int n_pages, int append) {
+                      const int* __restrict__ positions, int n_pages, int append, int* status) {
     pdl_trigger();
     const int t = blockIdx.x;
     const int half = rot >> 1;
@@ -218,7 +221,7 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
     int pos = 0, page = -1;
     if (appends) {
         pos = positions[t];
-        page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
+        page = pos / HB_PAGE_TOKENS < pt_width ? page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS] : -1;
     }
     pdl_wait();
     table = pdl_fresh(table);          // written by the rope table kernel of this step
@@ -239,7 +242,10 @@ rope_kv_append_kernel(T* __restrict__ qkv, long long qkv_stride, const float2* _
         }
         return;
     }
-    if (page < 0 || page >= n_pages) return;   // the host reserved the pages; never write outside the cache
+    if (page < 0 || page >= n_pages) {         // the host reserved the pages: a fault of its bookkeeping
+        if (threadIdx.x == 0) hb_note(status, HB_STATUS_PAGE, 1 + tok_seq[t]);
+        return;                                // never write outside the cache
+    }
     const T* krow = row + (size_t)nh * hd;
     const T* vrow = krow + (size_t)nkv * hd;
     for (int idx = threadIdx.x; idx < nkv * half; idx += blockDim.x) {
@@ -284,7 +290,7 @@ __global__ void __launch_bounds__(256)
 rope_kv_append_vec_kernel(bf16* __restrict__ qkv, long long qkv_stride, const float2* __restrict__ table, int rot, int nh,
                           int nkv, int hd, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                           const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
-                          const int* __restrict__ positions, int n_pages, int append) {
+                          const int* __restrict__ positions, int n_pages, int append, int* status) {
     pdl_trigger();
     pdl_wait();
     table = pdl_fresh(table);
@@ -295,8 +301,11 @@ rope_kv_append_vec_kernel(bf16* __restrict__ qkv, long long qkv_stride, const fl
     int page = -1, pos = 0;
     if (append) {
         pos = positions[t];
-        page = page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS];
-        if (page < 0 || page >= n_pages) page = -1;            // the host reserved the pages; never write outside the cache
+        page = pos / HB_PAGE_TOKENS < pt_width ? page_table[(size_t)tok_seq[t] * pt_width + pos / HB_PAGE_TOKENS] : -1;
+        if (page < 0 || page >= n_pages) {                     // the host reserved the pages: a fault of its bookkeeping
+            if (threadIdx.x == 0) hb_note(status, HB_STATUS_PAGE, 1 + tok_seq[t]);
+            page = -1;                                         // never write outside the cache
+        }
     }
     const int q_tasks = nh * hv;
     const int k_tasks = page >= 0 ? nkv * hv : 0;
@@ -337,7 +346,8 @@ rope_kv_append_vec_kernel(bf16* __restrict__ qkv, long long qkv_stride, const fl
 extern "C" int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride, const float* table, int rot,
                                  int n_heads, int n_kv_heads, int head_dim, void* k_cache, void* v_cache,
                                  int cache_dtype, const int* page_table, int pt_width, const int* tok_seq,
-                                 const int* positions, int n_tokens, int append, int n_pages, void* stream) {
+                                 const int* positions, int n_tokens, int append, int n_pages, int* status,
+                                 void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && head_dim > 0, "rope_kv_append: bad sizes");
     HB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0, "rope_kv_append: rotary size %d does not fit head size %d",
@@ -357,17 +367,17 @@ extern "C" int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride,
         ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0) {
         hb_launch(rope_kv_append_vec_kernel, dim3(n_tokens), dim3(256), 0, s, (bf16*)qkv, qkv_stride, tab, rot, n_heads,
                   n_kv_heads, head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table, pt_width, tok_seq, positions, n_pages,
-                  append);
+                  append, status);
         return hb_check_launch("rope_kv_append");
     }
     if (qkv_dtype == HB_BF16 && cache_dtype == HB_BF16)
         hb_launch(rope_kv_append_kernel<bf16, bf16>, dim3(n_tokens, groups), dim3(threads), 0, s, (bf16*)qkv, qkv_stride, tab, rot,
                   n_heads, n_kv_heads, head_dim, (bf16*)k_cache, (bf16*)v_cache, page_table, pt_width, tok_seq, positions,
-                  n_pages, append);
+                  n_pages, append, status);
     else if (qkv_dtype == HB_F32 && cache_dtype == HB_F32)
         hb_launch(rope_kv_append_kernel<float, float>, dim3(n_tokens, groups), dim3(threads), 0, s, (float*)qkv, qkv_stride, tab, rot,
                   n_heads, n_kv_heads, head_dim, (float*)k_cache, (float*)v_cache, page_table, pt_width, tok_seq, positions,
-                  n_pages, append);
+                  n_pages, append, status);
     else
         return hb_fail("rope_kv_append: unsupported dtypes qkv %d cache %d", qkv_dtype, cache_dtype);
     return hb_check_launch("rope_kv_append");

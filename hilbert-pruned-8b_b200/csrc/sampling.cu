@@ -27,10 +27,12 @@ __device__ __forceinline__ float uniform_from(long long seed, long long request,
     return (float)(z >> 40) * (1.0f / 16777216.0f);
 }
 
+// Also reports (to every thread) whether the row holds a value that is not finite.
 __device__ __forceinline__ void argmax_row(const float* __restrict__ row, int vocab, int* out_idx, float* out_max,
-                                           float* sval, int* sidx) {
+                                           float* sval, int* sidx, bool* out_nonfinite) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
+    bool bad = false;                      // x - x is 0 for a finite x, NaN for an infinity or a NaN
     if ((((uintptr_t)row) & 15) == 0) {
         // 16-byte loads, four in flight per thread: one block has to pull a whole row
         const float4* r4 = reinterpret_cast<const float4*>(row);
@@ -47,21 +49,27 @@ __device__ __forceinline__ void argmax_row(const float* __restrict__ row, int vo
                 const int base = (i0 + u * blockDim.x) * 4;
                 const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
-                for (int k = 0; k < 4; k++)
+                for (int k = 0; k < 4; k++) {
+                    if (i0 + u * blockDim.x < n4) bad |= (e[k] - e[k]) != 0.0f;      // not the padding of a short tail
                     if (e[k] > best || (e[k] == best && base + k < bi)) { best = e[k]; bi = base + k; }
+                }
             }
         }
         for (int i = (n4 << 2) + threadIdx.x; i < vocab; i += blockDim.x) {
             const float v = row[i];
+            bad |= (v - v) != 0.0f;
             if (v > best || (v == best && i < bi)) { best = v; bi = i; }
         }
     } else {
         for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
             const float v = row[i];
+            bad |= (v - v) != 0.0f;
             if (v > best || (v == best && i < bi)) { best = v; bi = i; }
         }
     }
+    *out_nonfinite = __syncthreads_or(bad ? 1 : 0) != 0;
     // a NaN never compares greater: a row of NaNs yields index 0x7fffffff, mapped to 0 below
+    // (a valid token for whatever runs next; the status word tells the host not to use it)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -89,7 +97,7 @@ __device__ __forceinline__ void argmax_row(const float* __restrict__ row, int vo
 }
 
 __global__ void __launch_bounds__(SM_THREADS)
-argmax_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ out, int vocab) {
+argmax_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ out, int vocab, int* status) {
     pdl_trigger();
     pdl_wait();
     logits = pdl_fresh(logits);
@@ -97,14 +105,19 @@ argmax_kernel(const float* __restrict__ logits, long long stride, int* __restric
     __shared__ int sidx[33];
     int idx;
     float mx;
-    argmax_row(logits + (size_t)blockIdx.x * stride, vocab, &idx, &mx, sval, sidx);
-    if (threadIdx.x == 0) out[blockIdx.x] = idx;
+    bool nonfinite;
+    argmax_row(logits + (size_t)blockIdx.x * stride, vocab, &idx, &mx, sval, sidx, &nonfinite);
+    if (threadIdx.x == 0) {
+        out[blockIdx.x] = idx;
+        // the reference fails a row whose logits are not finite (engine.c:29-31)
+        if (nonfinite) hb_note(status, HB_STATUS_NONFINITE, 1 + (int)blockIdx.x);
+    }
 }
 
 __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(const float* __restrict__ logits, long long stride, const float* __restrict__ temperature,
               const long long* __restrict__ seeds, const long long* __restrict__ request_ids,
-              const long long* __restrict__ steps, int* __restrict__ out, int vocab) {
+              const long long* __restrict__ steps, int* __restrict__ out, int vocab, int* status) {
     pdl_trigger();
     pdl_wait();
     logits = pdl_fresh(logits);
@@ -116,7 +129,15 @@ sample_kernel(const float* __restrict__ logits, long long stride, const float* _
     const float* row = logits + (size_t)r * stride;
     int amax;
     float mx;
-    argmax_row(row, vocab, &amax, &mx, sval, sidx);
+    bool nonfinite;
+    argmax_row(row, vocab, &amax, &mx, sval, sidx, &nonfinite);
+    if (nonfinite) {                            // engine.c:29-31: such a row is an error, not a draw
+        if (tid == 0) {
+            out[r] = amax;
+            hb_note(status, HB_STATUS_NONFINITE, 1 + r);
+        }
+        return;
+    }
     const float temp = temperature[r];
     if (!(temp > 0.0f)) {
         if (tid == 0) out[r] = amax;
@@ -156,19 +177,19 @@ sample_kernel(const float* __restrict__ logits, long long stride, const float* _
     if (tid == 0) out[r] = (chosen == 0x7fffffff) ? amax : chosen;  // rounding left no interval: the mode
 }
 
-extern "C" int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, void* stream) {
+extern "C" int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, int* status, void* stream) {
     if (n_rows == 0) return 0;
     HB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
-    hb_launch(argmax_kernel, dim3(n_rows), dim3(SM_THREADS), 0, (cudaStream_t)stream, logits, stride, out, vocab);
+    hb_launch(argmax_kernel, dim3(n_rows), dim3(SM_THREADS), 0, (cudaStream_t)stream, logits, stride, out, vocab, status);
     return hb_check_launch("argmax");
 }
 
 extern "C" int hb_sample(const float* logits, long long stride, const float* temperature, const long long* seeds,
                          const long long* request_ids, const long long* steps, int* out, int n_rows, int vocab,
-                         void* stream) {
+                         int* status, void* stream) {
     if (n_rows == 0) return 0;
     HB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "sample: bad sizes");
     hb_launch(sample_kernel, dim3(n_rows), dim3(SM_THREADS), 0, (cudaStream_t)stream, logits, stride, temperature, seeds, request_ids,
-                                                                   steps, out, vocab);
+                                                                   steps, out, vocab, status);
     return hb_check_launch("sample");
 }

@@ -95,7 +95,11 @@ class Generator:
         return pages_for(min(len(req.prompt) + req.max_new_tokens, self._context()))
 
     def _context(self) -> int:
-        return self.engine.cache.tokens_capacity()
+        """The most tokens a request's sequence may hold: the engine's limit for one sequence
+        (and the checkpoint's stated maximum position), not the size of the page pool, which
+        bounds what a whole batch holds and is the admission rule's business."""
+        limit = getattr(self.engine, "generation_limit", None)
+        return int(limit) if limit else self.engine.cache.tokens_capacity()
 
     def generate(self, requests: Sequence[GenerationRequest]) -> List[GenerationResult]:
         reqs = list(requests)
@@ -138,6 +142,8 @@ class Generator:
                        for i in order]
             logits = eng.step_chunked(entries) if hasattr(eng, "step_chunked") else eng.step(entries)
             toks = self._sample(logits, [live[i] for i in order], step_no=0)
+            if hasattr(eng, "check_status"):
+                eng.check_status()              # what the sampler noted (non-finite logits); the tokens were read anyway
             self._sync()
             self.stats.prefill_seconds += time.perf_counter() - t0
             self.stats.prefill_tokens += sum(len(live[i]["req"].prompt) for i in order)
@@ -170,8 +176,7 @@ class Generator:
             if flying is not None and self._same_batch_goes_on(flying, live):
                 order = flying["order"]
                 entries = [StepEntry(live[i]["seq"], [0], [0]) for i in order]
-                logits = eng.step(entries, device_tokens=flying["tokens"])
-                nxt = self._launch_sampling(logits, order, live, step_no)
+                nxt = self._step_and_sample(entries, order, live, step_no, flying["tokens"])
                 self._land(flying, live, results)
                 flying = nxt
             else:
@@ -183,8 +188,7 @@ class Generator:
                     break
                 order = list(live)
                 entries = [StepEntry(live[i]["seq"], [live[i]["next"]], [0]) for i in order]
-                logits = eng.step(entries)
-                flying = self._launch_sampling(logits, order, live, step_no)
+                flying = self._step_and_sample(entries, order, live, step_no, None)
                 if not ahead or not flying["on_device"]:
                     self._land(flying, live, results)
                     flying = None
@@ -192,24 +196,46 @@ class Generator:
             self.stats.decode_seconds += time.perf_counter() - t0
             step_no += 1
 
-    def _launch_sampling(self, logits, order, live, step_no: int) -> dict:
-        """Samples a step's tokens and starts their copy to the host; the record of a step whose
-        tokens have not been read."""
+    def _step_and_sample(self, entries, order, live, step_no: int, device_tokens) -> dict:
+        """One decode step and its sampling.  When every sequence of the step is greedy and the
+        engine can take the largest logit itself (``samples_greedy``), that is part of the step
+        (of its captured graph), not a launch of its own behind it."""
+        eng = self.engine
         states = [live[i] for i in order]
-        toks = self.sampler.sample(logits, [s["req"].sampling.temperature for s in states],
-                                   [s["req"].sampling.seed for s in states], [s["rid"] for s in states],
-                                   [step_no] * len(states))
+        kw = {} if device_tokens is None else {"device_tokens": device_tokens}
+        if getattr(eng, "samples_greedy", False) and all(s["req"].sampling.temperature == 0.0 for s in states):
+            eng.step(entries, greedy=True, **kw)
+            return self._launch_sampling(None, order, live, step_no, eng.greedy_tokens)
+        return self._launch_sampling(eng.step(entries, **kw), order, live, step_no)
+
+    def _launch_sampling(self, logits, order, live, step_no: int, toks=None) -> dict:
+        """Samples a step's tokens (unless the step took them itself: ``toks``) and starts their
+        copy to the host, together with the device status words if the engine has some; the
+        record of a step whose tokens have not been read."""
+        states = [live[i] for i in order]
+        if toks is None:
+            toks = self.sampler.sample(logits, [s["req"].sampling.temperature for s in states],
+                                       [s["req"].sampling.seed for s in states], [s["rid"] for s in states],
+                                       [step_no] * len(states))
         # the sequences' lengths as of this step: a later step may have grown them when this is read
-        rec = {"order": order, "tokens": toks, "on_device": False, "host": None, "event": None,
+        rec = {"order": order, "tokens": toks, "on_device": False, "host": None, "event": None, "status": None,
                "lengths": {i: live[i]["seq"].length for i in order}}
         if hasattr(toks, "is_cuda"):                   # a tensor: the next step can take it as it is
             import torch
             if toks.is_cuda:
-                host = self._host_tokens(len(order))
-                host.copy_(toks, non_blocking=True)
+                n = len(order)
+                status = self.engine.status_tensor() if hasattr(self.engine, "status_tensor") else None
+                words = 0 if status is None else status.numel()
+                host = self._host_tokens(n + words)
+                host[:n].copy_(toks, non_blocking=True)
+                if words:
+                    # what the kernels noted up to and including this step's sampling, read when
+                    # the tokens are read: no wait of its own
+                    host[n:].copy_(status, non_blocking=True)
+                    rec["status"] = host[n:]
                 ev = torch.cuda.Event()
                 ev.record(torch.cuda.current_stream(toks.device))
-                rec.update(on_device=True, host=host, event=ev)
+                rec.update(on_device=True, host=host[:n], event=ev)
             else:
                 rec.update(on_device=True, host=toks.clone())
         return rec
@@ -219,7 +245,7 @@ class Generator:
         import torch
         bufs = getattr(self, "_token_buffers", None)
         if bufs is None or bufs[0].numel() < n:
-            bufs = self._token_buffers = [torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+            bufs = self._token_buffers = [torch.empty(max(n, 72), dtype=torch.int32, pin_memory=True) for _ in range(2)]
             self._token_turn = 0
         self._token_turn ^= 1
         return bufs[self._token_turn][:n]
@@ -246,6 +272,12 @@ class Generator:
         if flying["on_device"]:
             if flying["event"] is not None:
                 flying["event"].synchronize()
+            if flying.get("status") is not None:
+                words = flying["status"].tolist()
+                if any(words):
+                    # a kernel noted a fault (a wait that ran out, non-finite logits, a bad page or
+                    # token number): the tokens are not to be trusted, the call ends here
+                    self.engine.raise_on_status(words)
             toks = flying["host"].tolist()
         else:
             toks = [int(t) for t in (toks.tolist() if hasattr(toks, "tolist") else toks)]

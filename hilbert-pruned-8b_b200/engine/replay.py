@@ -65,5 +65,9 @@ def main(argv=None) -> int:
     if args.max_tokens < 1:
         ap.error("--max-tokens must be positive")
     from .step import Engine
-    engine = Engine.from_folder(args.model, args.dtype, max_tokens=args.max_tokens, device=f"cuda:{args.device}")
-    return replay(engine, sys.stdin, args.out, sys.stdout)
+    try:
+        engine = Engine.from_folder(args.model, args.dtype, max_tokens=args.max_tokens, device=f"cuda:{args.device}")
+        return replay(engine, sys.stdin, args.out, sys.stdout)
+    except (ValueError, RuntimeError) as e:        # configuration, weights, a refused step, a fault a kernel noted
+        print(f"error: {e}", file=sys.stderr)
+        return 1

@@ -25,12 +25,12 @@ _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_floa
 _SIGNATURES = {
     "hb_device_info": [_c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "hb_timeline_set": [_c_ptr, _c_ptr, _c_int, _c_int],
-    "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_rmsnorm": [_c_ptr, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_silu_mul": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
     "hb_rope_table": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_rope_kv_append": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
-                          _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+                          _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_gemm_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
                         _c_int, _c_ptr],
     "hb_gemm_tc": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -38,21 +38,21 @@ _SIGNATURES = {
     "hb_gemm_tc2": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int,
                     _c_ptr],
     "hb_attention_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
-                             _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr],
+                             _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_decode": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
-                            _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                            _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_decode_combined": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int,
-                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_decode_fused": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                   _c_ll, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                  _c_ptr],
+                                  _c_ptr, _c_ptr],
     "hb_attention_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
-                             _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr],
+                             _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_prefill_tc": [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_random_normal": [_c_ptr, _c_int, _c_ll, ctypes.c_ulonglong, _c_float, _c_float, _c_ptr],
-    "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
-    "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
 }
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -181,8 +181,11 @@ class Ops:
         self.use_pair_gemm = True      # many-token products on CTA pairs (cta_group::2)
         # weights as contiguous tiles (PackedWeight); HILBERT_B200_PACK=0 keeps them row-major
         self.use_packed_weights = os.environ.get("HILBERT_B200_PACK", "1") != "0"
-        # device status word the tensor-core kernels set when one of their bounded waits ran out
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # device status words (csrc/common.cuh): a kernel that meets a fault notes the first one of
+        # its kind and carries on with a safe value; the host reads the words where it waits anyway
+        # (check_errors, or copied back beside a step's sampled tokens) and raises
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.error_flag = self.status[:1]      # word 0: a bounded wait of a tensor-core kernel ran out
         # split-K scratch: float32 partial tiles and one counter per output tile (kept zero)
         self._splitk_partials = torch.empty(8 << 20, dtype=torch.float32, device=self.device)
         self._splitk_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
@@ -198,7 +201,9 @@ class Ops:
         # their page in shared memory).  Inside a replayed graph at batch 8 / 8192 tokens it takes
         # 43.2 us where rotation + attention take 3.4 + 41.0 us; alternating runs on one GPU, a step
         # of 8 layers: 1310 against 1312 us, at batch 1 1046 against 1047 us, 1B sizes 613 against
-        # 616 us.  One launch less, the time of the hand-over between kernels stays.
+        # 616 us.  One launch less, the time of the hand-over between kernels stays.  Whether a
+        # model's attention uses it is the part's choice (the mixer's `fuse_decode`, its position
+        # encoding's `fusable`); this switch only takes the kernel away (tests compare both ways).
         self.fuse_decode_attention = True
         # Split-K decode attention whose last split combines the splits, instead of a second
         # kernel.  Off: at batch 8 / 8192 tokens a step of 8 layers takes 1319 us against 1313 us, at
@@ -257,7 +262,7 @@ class Ops:
         if table.shape[1] != H or tokens.numel() != T:
             raise KernelError("embed: shapes do not agree")
         self._call("hb_embed", tokens.data_ptr(), table.data_ptr(), _code(table), out.data_ptr(), T, H,
-                   table.shape[0], self._stream())
+                   table.shape[0], self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def rmsnorm(self, x, weight, eps: float, offset: float, out, rows=None) -> None:
@@ -318,15 +323,47 @@ class Ops:
         self._call("hb_rope_kv_append", qkv.data_ptr(), _code(qkv), _rows(qkv, "qkv"),
                    table.data_ptr() if rot else None, rot, heads, kv_heads, head_dim, cache.k.data_ptr(),
                    cache.v.data_ptr(), _code(cache.k), pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(),
-                   step.positions.data_ptr(), T, 1 if append else 0, cache.k.shape[0], self._stream())
+                   step.positions.data_ptr(), T, 1 if append else 0, cache.k.shape[0], self.status.data_ptr(),
+                   self._stream())
         self.launches += 1
 
+    STATUS_WORDS = 4
+
+    @staticmethod
+    def status_message(words) -> Optional[str]:
+        """What the status words say, or None if all are zero."""
+        w = [int(x) for x in words]
+        if not any(w):
+            return None
+        parts = []
+        if w[0]:
+            parts.append(f"a tensor-core kernel gave up a bounded wait (code {w[0]}); its results are invalid")
+        if w[1]:
+            parts.append(f"non-finite logits at row {w[1] - 1} of a step (the reference fails such a row too)")
+        if w[2]:
+            parts.append(f"a page number outside the cache, or a missing page, for sequence {w[2] - 1} of a step: "
+                         "the cache's bookkeeping is at fault")
+        if w[3]:
+            parts.append(f"a token id outside the vocabulary at row {w[3] - 1} of a step")
+        return "; ".join(parts)
+
+    def raise_on_status(self, words) -> None:
+        """Raises ``KernelError`` for non-zero status words that were read already (a host copy),
+        after clearing the device's words and the split-K counters a kernel that gave up may have
+        left non-zero."""
+        msg = self.status_message(words)
+        if msg is not None:
+            self.reset_status()
+            raise KernelError(msg)
+
+    def reset_status(self) -> None:
+        self.status.zero_()
+        self._splitk_counters.zero_()
+        self._decode_counters.zero_()
+
     def check_errors(self) -> None:
-        """Reads the device status word (this synchronises) and raises if a kernel gave up a wait."""
-        code = int(self.error_flag.item())
-        if code:
-            self.error_flag.zero_()
-            raise KernelError(f"a tensor-core kernel gave up a bounded wait (code {code}); its results are invalid")
+        """Reads the device status words (this synchronises) and raises if a kernel noted a fault."""
+        self.raise_on_status(self.status.tolist())
 
     # ------------------------------------------------------------------ matrix products
     def pack_weight(self, w: torch.Tensor, swiglu: bool = False):
@@ -456,7 +493,7 @@ class Ops:
                    self._decode_counters.data_ptr() if self.combine_in_attention else None,
                    out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,
                    head_dim, float(scale), int(window) if window else 0, n_splits, max_pages, cache.k.shape[0],
-                   1 if append else 0, self._stream())
+                   1 if append else 0, self.status.data_ptr(), self._stream())
         self.launches += 1 if (n_splits == 1 or self.combine_in_attention) else 2
 
     def attention(self, qkv, heads: int, kv_heads: int, head_dim: int, cache, step, out, scale: float,
@@ -489,18 +526,20 @@ class Ops:
                            cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.positions.data_ptr(),
                            self._decode_scratch.data_ptr(), self._decode_counters.data_ptr(), out.data_ptr(),
                            _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale), win, n_splits, max_pages,
-                           cache.k.shape[0], self._stream())
+                           cache.k.shape[0], self.status.data_ptr(), self._stream())
                 self.launches += 1
                 return
             self._call("hb_attention_decode", qkv.data_ptr(), _rows(qkv, "attention queries"), cache.k.data_ptr(),
                        cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.positions.data_ptr(),
                        self._decode_scratch.data_ptr(), out.data_ptr(), _rows(out, "attention output"), T, heads, kv_heads,
-                       head_dim, float(scale), win, n_splits, max_pages, cache.k.shape[0], self._stream())
+                       head_dim, float(scale), win, n_splits, max_pages, cache.k.shape[0], self.status.data_ptr(),
+                       self._stream())
             self.launches += 2
             return
         if (fast and self.use_tcgen05_attention and self.lib.hb_attention_prefill_tc_supported(heads, kv_heads, head_dim)
                 and qkv.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and _rows(qkv, "attention queries") % 8 == 0
-                and _rows(out, "attention output") % 8 == 0):
+                and _rows(out, "attention output") % 8 == 0
+                and sum((n + 127) // 128 for n in step.host_new) <= 65535):
             q_blocks = sum((n + 127) // 128 for n in step.host_new)
             self._call("hb_attention_prefill_tc", qkv.data_ptr(), _rows(qkv, "attention queries"), T, cache.k.data_ptr(),
                        cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(),
@@ -508,18 +547,20 @@ class Ops:
                        float(scale), win, cache.k.shape[0], self.error_flag.data_ptr(), self._stream())
             self.launches += 1
             return
-        if fast and self.lib.hb_attention_prefill_supported(heads, kv_heads, head_dim):
+        if (fast and self.lib.hb_attention_prefill_supported(heads, kv_heads, head_dim)
+                and sum((n + 63) // 64 for n in step.host_new) <= 65535):
             q_blocks = sum((n + 63) // 64 for n in step.host_new)
             self._call("hb_attention_prefill", qkv.data_ptr(), _rows(qkv, "attention queries"), cache.k.data_ptr(),
                        cache.v.data_ptr(), pt.data_ptr(), pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(),
                        out.data_ptr(), _rows(out, "attention output"), step.num_seqs, q_blocks, heads, kv_heads, head_dim,
-                       float(scale), win, cache.k.shape[0], self._stream())
+                       float(scale), win, cache.k.shape[0], self.status.data_ptr(), self._stream())
             self.launches += 1
             return
         self._call("hb_attention_general", qkv.data_ptr(), _code(qkv), _rows(qkv, "attention queries"),
                    cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k), pt.data_ptr(), pt.shape[1],
                    step.tok_seq.data_ptr(), step.positions.data_ptr(), out.data_ptr(), _code(out),
-                   _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale), win, self._stream())
+                   _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale), win, cache.k.shape[0],
+                   self.status.data_ptr(), self._stream())
         self.launches += 1
 
     # ------------------------------------------------------------------ random weights
@@ -539,7 +580,7 @@ class Ops:
         if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() != logits.shape[0]:
             raise KernelError("argmax: float32 logits and one int32 per row expected")
         self._call("hb_argmax", logits.data_ptr(), _rows(logits, "logits"), out.data_ptr(), logits.shape[0],
-                   logits.shape[1], self._stream())
+                   logits.shape[1], self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def sample(self, logits, temperature, seeds, request_ids, steps, out) -> None:
@@ -551,5 +592,6 @@ class Ops:
             raise KernelError("sample: float32 logits/temperature, int64 seeds/requests/steps, int32 output, "
                               "one of each per row expected")
         self._call("hb_sample", logits.data_ptr(), _rows(logits, "logits"), temperature.data_ptr(), seeds.data_ptr(),
-                   request_ids.data_ptr(), steps.data_ptr(), out.data_ptr(), n, logits.shape[1], self._stream())
+                   request_ids.data_ptr(), steps.data_ptr(), out.data_ptr(), n, logits.shape[1], self.status.data_ptr(),
+                   self._stream())
         self.launches += 1

@@ -113,6 +113,49 @@ def test_truncate_rewinds_a_sequence():
     m.close(s)
 
 
+def test_snapshot_and_restore_rewind_keys_and_fixed_size_state():
+    """Truncation alone cannot rewind fixed-size state; a snapshot carries a copy of it, and a
+    restore gives the later pages back and puts the copy in place."""
+    m = _manager(max_tokens=512, state=True)
+    s, other = m.open(), m.open()
+    m.reserve([(s, 70)])
+    m.commit(s, 70)
+    m.state_view(1)[s.state_slot].fill_(3.0)
+    snap = m.snapshot(s)
+    m.reserve([(s, 200)])
+    m.commit(s, 200)
+    m.state_view(1)[s.state_slot].fill_(9.0)
+    version = s.pages_version
+    with pytest.raises(ValueError, match="fixed-size state"):
+        m.truncate(s, 70)
+    with pytest.raises(ValueError, match="snapshot is of sequence"):
+        m.restore(other, snap)
+    m.restore(s, snap)
+    assert s.length == 70 and [len(p) for p in s.pages] == [2, 2] and s.pages_version > version
+    assert torch.all(m.state_view(1)[s.state_slot] == 3.0)
+    assert m.pages_free() == [6, 6]
+    m.restore(s, snap)                                 # a snapshot can be gone back to again
+    m.reserve([(s, 130)])
+    m.commit(s, 130)
+    m.restore(s, snap)
+    assert s.length == 70 and m.pages_free() == [6, 6]
+    m.close(s)
+    m.close(other)
+    with pytest.raises(ValueError, match="closed"):
+        m.restore(s, snap)
+    assert m.pages_free() == [8, 8] and m.slots.num_held == 0
+
+
+def test_check_room_reserves_nothing():
+    m = _manager(max_tokens=64 * 4)
+    s = m.open()
+    m.check_room([(s, 256)])
+    with pytest.raises(CacheFull, match="needs 5 more pages"):
+        m.check_room([(s, 257)])
+    assert m.pages_free() == [4, 4] and s.pages == [[], []]
+    m.close(s)
+
+
 def test_random_traffic_never_loses_a_page():
     rng = random.Random(0)
     m = _manager(max_tokens=64 * 40, window=100, state=True)

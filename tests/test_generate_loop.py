@@ -146,6 +146,82 @@ def test_context_limit_and_bad_requests():
     assert eng.cache.slots.num_held == 0
 
 
+def test_a_request_ends_at_its_own_limit_while_the_pool_has_pages():
+    """The context of a request is the engine's limit for ONE sequence (and the model's stated
+    maximum position), not the size of the page pool: admission counts pages up to that limit."""
+    eng = FakeEngine(max_tokens=64 * 16)
+    eng.generation_limit = 100
+    gen = Generator(eng, FakeSampler(), max_batch=8)
+    reqs = [GenerationRequest([3] * 90, max_new_tokens=50, stop_token_ids=[]),
+            GenerationRequest([4] * 10, max_new_tokens=20, stop_token_ids=[])]
+    res = gen.generate(reqs)
+    assert res[0].finish_reason == "context" and len(res[0].tokens) == 11     # 90 + 10 fed = 100, the 11th cannot be fed
+    assert res[1].finish_reason == "length" and len(res[1].tokens) == 20
+    assert eng.peak_pages <= 2 + 1 and min(eng.cache.pages_free()) == 16       # costs were counted up to the limit
+    with pytest.raises(ValueError, match="prompt tokens, context is 100"):
+        gen.generate([GenerationRequest([1] * 101)])
+    ahead = AheadEngine(max_tokens=64 * 16)
+    ahead.generation_limit = 100
+    res2 = Generator(ahead, FakeSampler(), max_batch=8).generate(reqs)
+    assert [(r.tokens, r.finish_reason) for r in res2] == [(r.tokens, r.finish_reason) for r in res]
+
+
+class NotingEngine(AheadEngine):
+    """An engine with device status words (here host memory): the loop copies them beside each
+    step's tokens and stops the call when one is set."""
+
+    def __init__(self, fail_at_step):
+        super().__init__(256)
+        self.words = torch.zeros(4, dtype=torch.int32)
+        self.fail_at_step, self.decode_steps = fail_at_step, 0
+        self.raised = None
+
+    def status_tensor(self):
+        return self.words
+
+    def step(self, entries, device_tokens=None):
+        out = super().step(entries, device_tokens)
+        if all(len(e.tokens) == 1 for e in entries):
+            self.decode_steps += 1
+            if self.decode_steps == self.fail_at_step:
+                self.words[1] = 3            # what a sampler notes for non-finite logits in row 2
+        return out
+
+    def raise_on_status(self, words):
+        self.raised = list(words)
+        self.words.zero_()
+        raise RuntimeError(f"status {list(words)}")
+
+
+def test_a_status_word_set_on_the_device_stops_generation(monkeypatch):
+    """The loop reads the status words with the step's tokens; a non-zero word raises through
+    the engine, the sequences are closed and every page comes back."""
+    import hilbert_pruned_8b_b200.engine.generate as g
+
+    eng = NotingEngine(fail_at_step=3)
+    gen = Generator(eng, FakeSampler(), max_batch=4)
+    # the fake sampler's tokens are host tensors: take the path of device tensors by hand
+    calls = {"n": 0}
+    real = Generator._launch_sampling
+
+    def launch(self, logits, order, live, step_no, toks=None):
+        rec = real(self, logits, order, live, step_no, toks)
+        rec["status"] = eng.status_tensor().clone()
+        calls["n"] += 1
+        return rec
+
+    monkeypatch.setattr(g.Generator, "_launch_sampling", launch)
+    reqs = [GenerationRequest([3, 4, 5], max_new_tokens=30, stop_token_ids=[]),
+            GenerationRequest([7], max_new_tokens=30, stop_token_ids=[])]
+    with pytest.raises(RuntimeError, match="status"):
+        gen.generate(reqs)
+    assert eng.raised == [0, 3, 0, 0] and calls["n"] >= 3
+    assert eng.cache.slots.num_held == 0 and min(eng.cache.pages_free()) == eng.cache.num_pages
+    # the next call starts clean
+    eng.fail_at_step = -1
+    assert len(gen.generate(reqs)) == 2
+
+
 def test_default_stop_ids_come_from_the_model():
     eng = FakeEngine()
     eng.stop_token_ids = [6]
