@@ -10,7 +10,8 @@ steps; ``e2e`` is the same through the library's generation loop with host token
 (pinned host memory -> device every step, sampled tokens device -> host every step).
 ``prefill`` times one 2048-token prompt; ``roofline`` relates the decode step to the HBM
 bandwidth it needs (every weight once + the live sequences' cache); ``points`` adds decoding
-at batch 1 and 64.  Weights (15 GB) exceed L2 (126 MB), so every step reads them from HBM.
+at batch 1 and 64, prefill at 512, 8192 and 32768 tokens, and steady decoding at the 3B and 1B
+shapes (batch 16 and 64) with the fraction of the HBM peak each reaches.  Weights (15 GB) exceed L2 (126 MB), so every step reads them from HBM.
 The caches of the decode benchmark are filled with random keys and values instead of being
 prefilled; a decode step's work does not depend on their values.
 """
@@ -138,8 +139,7 @@ def time_decode(llm, batch, steps, warmup, length, sampler=None):
     vocab = eng.vocab_size
     toks = torch.randint(0, vocab, (steps + warmup, batch), generator=gen).tolist()
     for w in range(warmup):
-        lg = eng.step([StepEntry(s, [toks[w][b]], [0]) for b, s in enumerate(seqs)])
-        llm.sampler.greedy(lg)
+        eng.step([StepEntry(s, [toks[w][b]], [0]) for b, s in enumerate(seqs)], greedy=True)
     torch.cuda.synchronize()
     launches0 = eng.ctx.ops.launches
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -148,10 +148,11 @@ def time_decode(llm, batch, steps, warmup, length, sampler=None):
         clocks.start()
     start.record()
     for k in range(steps):
-        lg = eng.step([StepEntry(s, [toks[warmup + k][b]], [0]) for b, s in enumerate(seqs)])
-        llm.sampler.greedy(lg)
+        # the greedy pick is the last kernel of the step's captured graph
+        eng.step([StepEntry(s, [toks[warmup + k][b]], [0]) for b, s in enumerate(seqs)], greedy=True)
     end.record()
     torch.cuda.synchronize()
+    eng.check_status()                 # a kernel that noted a fault makes the number worthless: raise
     ms = start.elapsed_time(end) / steps
     clock_info = clocks.stop() if clocks else None
     launches = eng.ctx.ops.launches - launches0
@@ -183,10 +184,11 @@ def time_e2e(llm, batch, steps, warmup, length):
     _run_steps(gen, live, results, steps)
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    eng.check_status()
     for s in seqs:
         eng.close_sequence(s)
     h2d = _step_meta_bytes(eng, batch, length)
-    return batch * steps / dt, h2d, batch * 4
+    return batch * steps / dt, h2d, batch * 4 + 16      # the tokens and the four status words
 
 
 def _run_steps(gen, live, results, n):
@@ -214,6 +216,28 @@ def _step_meta_bytes(eng, batch, length):
     from hilbert_pruned_8b_b200.cache import pages_for
     per_seq = 3 + 4 + pages_for(length) * max(1, len(eng.cache.groups))
     return 4 * (batch * per_seq + 8)
+
+
+def other_shape_point(name, steps, pk):
+    """Steady decoding at the 3B / 1B shapes with their workloads' batch and a cache length in the
+    middle of what that workload reaches: tokens/s, ms per step, GB/s and the fraction of the HBM
+    peak, as flat keys for `points`."""
+    import torch
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.api import LLM
+    cfg_dict, label, batch, lo, hi, new_tokens = WORKLOADS[name]
+    length = (lo + hi) // 2 + new_tokens // 2
+    cfg = hb.LlamaConfig.from_dict(cfg_dict)
+    llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=batch * ((length + 127) // 64 * 64), device=0,
+                     max_batch=batch, max_step_tokens=256)
+    fill_cache_random(llm)
+    ms, _, step_bytes, _ = time_decode(llm, batch, steps, 3, length)
+    del llm
+    torch.cuda.empty_cache()
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    key = f"decode_{name}_b{batch}"
+    return {key: round(batch / (ms * 1e-3), 1), key + "_ms": round(ms, 4), key + "_gbs": round(gbs, 1),
+            key + "_frac": round(gbs / pk["hbm_gbs"], 4), key + "_ctx": length}
 
 
 def time_prefill(llm, tokens, repeats=3, warmup=2):
@@ -429,8 +453,19 @@ def main() -> int:
     points = {}
     if not a.skip_points:
         for b in (1, 64):
-            pms, _, _, _ = time_decode(llm, b, max(4, a.steps // 2), 3, CONTEXT)
+            pms, _, pbytes, _ = time_decode(llm, b, max(4, a.steps // 2), 3, CONTEXT)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+            points[f"decode_b{b}_frac"] = round(pbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        # prefill at other lengths (cut into steps of 2048 tokens): tokens/s
+        for t in (512, 8192, 32768):
+            pms = time_prefill(llm, t, repeats=2, warmup=1)
+            points[f"prefill_t{t}"] = round(t / (pms * 1e-3), 1)
+            points[f"prefill_t{t}_frac"] = round(prefill_flops(cfg_dict, layers, t) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+        del llm
+        torch.cuda.empty_cache()
+        # decoding at the 3B and 1B shapes (their workloads' batch sizes)
+        for name in ("3b", "1b"):
+            points.update(other_shape_point(name, max(8, a.steps), pk))
     achieved = step_bytes / (ms * 1e-3) / 1e9
     value = a.batch / (ms * 1e-3)
     line = {

@@ -57,13 +57,21 @@ def read_config(model_dir: str) -> dict:
     return c
 
 
-def read_weights(model_dir: str) -> Dict[str, torch.Tensor]:
-    """Every tensor of model.safetensors widened exactly to float64 (ct/src/model.c:259-270,291-307)."""
+class Widening(dict):
+    """Tensors as stored; reading one widens it exactly to float64 (ct/src/model.c:259-270,291-307).
+    Widening on use keeps a vocabulary-sized table at its stored size until it is needed."""
+
+    def __getitem__(self, key):
+        return super().__getitem__(key).to(F64)
+
+
+def read_weights(model_dir: str, device: str = "cpu") -> Dict[str, torch.Tensor]:
+    """Every tensor of model.safetensors; reads come back as float64."""
     from safetensors import safe_open
-    out = {}
+    out = Widening()
     with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt") as f:
         for k in f.keys():
-            out[k] = f.get_tensor(k).to(F64)
+            out[k] = f.get_tensor(k).to(device)
     return out
 
 
@@ -91,7 +99,7 @@ def rope_inv_freq(rotary_dim: int, theta: float, llama3: Optional[dict]) -> np.n
 
 def embed(tokens: Sequence[int], table: torch.Tensor) -> torch.Tensor:
     """x[t] = E[token[t]], no scaling (ct/src/cpu_backend.c:236)."""
-    return table[torch.as_tensor(list(tokens), dtype=torch.long)].clone()
+    return table[torch.as_tensor(list(tokens), dtype=torch.long, device=table.device)].clone()
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, offset: float = 0.0) -> torch.Tensor:
@@ -112,7 +120,7 @@ def rope(x: torch.Tensor, positions: Sequence[int], inv_freq: np.ndarray, rotary
     half = rotary_dim // 2
     p = np.asarray(list(positions), dtype=np.float32)[:, None]
     ang = (inv_freq[None, :].astype(np.float32) * p).astype(np.float32)  # float32 product, as the reference
-    ang = torch.from_numpy(ang.astype(np.float64))
+    ang = torch.from_numpy(ang.astype(np.float64)).to(x.device)
     cs, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     out = x.clone()
     x1, x2 = x[..., :half], x[..., half:rotary_dim]
@@ -130,11 +138,11 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optiona
     nkv = k.shape[1]
     group = nh // nkv
     scale = 1.0 / math.sqrt(float(hd))
-    out = torch.zeros(T, nh, hd, dtype=q.dtype)
+    out = torch.zeros(T, nh, hd, dtype=q.dtype, device=q.device)
     for j in range(nh):
         g = j // group
         sc = (q[:, j, :] @ k[:, g, :].t()) * scale                      # [T, T]
-        t_idx = torch.arange(T)
+        t_idx = torch.arange(T, device=q.device)
         mask = t_idx[None, :] > t_idx[:, None]
         if window is not None:
             mask = mask | (t_idx[None, :] < (t_idx[:, None] - window + 1))
@@ -159,9 +167,13 @@ def swiglu(h: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Tensor
 
 # --------------------------------------------------------------------------- the model
 class PlainLlama:
-    def __init__(self, model_dir: str, round_to: Optional[torch.dtype] = None, window: Optional[int] = None):
+    def __init__(self, model_dir: str, round_to: Optional[torch.dtype] = None, window: Optional[int] = None,
+                 device: str = "cpu"):
+        """``device``: where torch does the arithmetic.  The CPU by default; the models with a full
+        vocabulary and real layer widths run the same float64 operations on the GPU, where they
+        take seconds instead of minutes."""
         self.cfg = read_config(model_dir)
-        self.w = read_weights(model_dir)
+        self.w = read_weights(model_dir, device)
         self.prefix = "model.language_model." if "model.language_model.embed_tokens.weight" in self.w else "model."
         self.inv_freq = rope_inv_freq(self.cfg["rotary_dim"], self.cfg["rope_theta"], self.cfg["llama3"])
         self.round_to = round_to
@@ -189,11 +201,22 @@ class PlainLlama:
         return x
 
     def hidden(self, tokens: Sequence[int]) -> torch.Tensor:
-        x = embed(tokens, self.w[self.prefix + "embed_tokens.weight"])
+        table = dict.__getitem__(self.w, self.prefix + "embed_tokens.weight")      # rows are widened after the gather
+        x = embed(tokens, table).to(F64)
         positions = list(range(len(tokens)))
         for i in range(self.cfg["num_hidden_layers"]):
             x = self.layer(x, i, positions)
         return x
+
+    def logits_at(self, tokens: Sequence[int], places: Sequence[int]) -> torch.Tensor:
+        """Logits at the given positions only: [len(places), vocab] float64."""
+        x = self.hidden(tokens)[torch.as_tensor(list(places), dtype=torch.long, device=self.hidden_device())]
+        h = self.rnd(rms_norm(x, self.w[self.prefix + "norm.weight"], self.cfg["rms_norm_eps"]))
+        head = self.w[self.prefix + "embed_tokens.weight"] if self.cfg["tied"] else self.w["lm_head.weight"]
+        return linear(h, head)
+
+    def hidden_device(self):
+        return dict.__getitem__(self.w, self.prefix + "norm.weight").device
 
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:
         """Logits at every position of one whole sequence: [T, vocab] float64.  The reference

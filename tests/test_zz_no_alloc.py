@@ -18,7 +18,7 @@ def _lib():
     lib = ctypes.CDLL(build.library_path())
     P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
     lib.hb_last_error.restype = ctypes.c_char_p
-    lib.hb_attention_decode.argtypes = [P, L, P, P, P, I, P, P, P, L, I, I, I, I, F, I, I, I, I, P]
+    lib.hb_attention_decode.argtypes = [P, L, P, P, P, I, P, P, P, L, I, I, I, I, F, I, I, I, I, P, P]
     lib.hb_attention_decode_noalloc.argtypes = [P, L, P, P, P, I, P, P, L, I, I, I, I, F, I, I, I, I, P]
     lib.hb_attention_decode_scratch_floats.argtypes = [I, I, I, I]
     lib.hb_attention_decode_scratch_floats.restype = L
@@ -54,7 +54,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         want = torch.zeros(batch, nh * hd, device=DEV, dtype=torch.bfloat16)
         rc = lib.hb_attention_decode(q.data_ptr(), nh * hd, k.data_ptr(), v.data_ptr(), table.data_ptr(), width,
                                      positions.data_ptr(), scratch.data_ptr(), want.data_ptr(), nh * hd, batch, nh, nkv, hd,
-                                     scale, 0, splits, width, 24, stream)
+                                     scale, 0, splits, width, 24, None, stream)
         assert rc == 0, lib.hb_last_error()
         got = torch.full_like(want, 7.0)
         rc = lib.hb_attention_decode_noalloc(q.data_ptr(), nh * hd, k.data_ptr(), v.data_ptr(), table.data_ptr(), width,
@@ -86,3 +86,28 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
     assert rc != 0
     msg = lib.hb_last_error().decode()
     assert "scratch floats" in msg and "built-in area" in msg
+
+
+def test_no_alloc_entry_point_reads_nothing_beyond_the_page_table():
+    """A position that lies beyond what the page table covers (a caller's mistake): the kernel
+    reads the pages the table has and nothing past its end; more pages per sequence than the
+    table is wide are refused before anything runs."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    lib = _lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    nh, nkv, hd, splits = 8, 2, 128, 2
+    q, k, v, table, positions, width = _case(3, 2, nh, nkv, hd, [100, 40], 24)
+    table = table[:, :2].contiguous()                       # two pages per sequence, then the next row starts
+    positions = torch.tensor([500, 39], dtype=torch.int32, device=DEV)      # 500 is far beyond 2 * 64
+    got = torch.full((2, nh * hd), 7.0, device=DEV, dtype=torch.bfloat16)
+    rc = lib.hb_attention_decode_noalloc(q.data_ptr(), nh * hd, k.data_ptr(), v.data_ptr(), table.data_ptr(), 2,
+                                         positions.data_ptr(), got.data_ptr(), nh * hd, 2, nh, nkv, hd, 0.1, 0, splits, 2, 24,
+                                         stream)
+    assert rc == 0, lib.hb_last_error()
+    torch.cuda.synchronize()
+    assert torch.isfinite(got.float()).all()
+    rc = lib.hb_attention_decode_noalloc(q.data_ptr(), nh * hd, k.data_ptr(), v.data_ptr(), table.data_ptr(), 2,
+                                         positions.data_ptr(), got.data_ptr(), nh * hd, 2, nh, nkv, hd, 0.1, 0, splits, 8, 24,
+                                         stream)
+    assert rc != 0 and "page table of width 2" in lib.hb_last_error().decode()

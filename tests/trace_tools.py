@@ -42,15 +42,18 @@ def trace_tail(requests, tail=32):
     return steps, max(round64(len(t)) for t in requests.values())
 
 
-def trace_batches(batches):
+def trace_batches(batches, want_all=True):
     """`batches`: list of {id: (tokens, prompt_len)}.  A batch's prompts start together in one
     step, then every live request feeds one token per step; a request ends when its tokens
-    are used up, the shorter ones earlier.  Batches follow one another, so slots are reused."""
+    are used up, the shorter ones earlier.  Batches follow one another, so slots are reused.
+    Logits are wanted at every position, or (`want_all` False) at each prompt's last position
+    and at every position after it."""
     steps, peak = [], 0
     for batch in batches:
         peak = max(peak, sum(round64(len(t)) for t, _ in batch.values()))
         fed = {rid: p for rid, (t, p) in batch.items()}
-        entries = [{"id": rid, "tokens": t[:p], "want": list(range(p))} for rid, (t, p) in batch.items()]
+        entries = [{"id": rid, "tokens": t[:p], "want": list(range(p)) if want_all else [p - 1]}
+                   for rid, (t, p) in batch.items()]
         ends = [rid for rid, (t, p) in batch.items() if p == len(t)]
         steps.append({"step": len(steps), "entries": entries, "end": ends})
         live = [rid for rid in batch if rid not in ends]
