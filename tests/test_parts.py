@@ -466,7 +466,7 @@ def _register_toy_postnorm():
                 hd = x.shape[-1]
                 ang = pos[:, None] * (self.freq * torch.arange(1, hd // 2 + 1, device=x.device, dtype=torch.float32))[None, :]
                 cs, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
-                a, b = x[..., 0::2].float(), x[..., 1::2].float()
+                a, b = x[..., 0::2].to(torch.float32, copy=True), x[..., 1::2].to(torch.float32, copy=True)
                 x[..., 0::2] = (a * cs - b * sn).to(x.dtype)
                 x[..., 1::2] = (b * cs + a * sn).to(x.dtype)
 
