@@ -394,6 +394,88 @@ def timeline_table(llm, batch, context, steps=8):
     return 0
 
 
+NO_DECODE = ("decode tokens/s: the reference generates nothing (no decode loop, no sampler: "
+             "cleanroom-transformer/README.md:7-10; its Python package only scores answer options of text rows "
+             "through transformers and needs a tokenizer and a hub revision)")
+
+
+def reference_arm(a) -> int:
+    """The UNMODIFIED reference on the same box, for the one part of the metric it can measure: the
+    warm 2048-token prefill that its own ``selftest`` command times and prints
+    (cleanroom-transformer/src/cuda_backend.cu:1449-1457).  The binary is the reference's CUDA
+    build, made by its own Makefile with its stock flags (``make cuda``: sm_86 code plus
+    compute_86 PTX, which the driver compiles for this GPU) under ``baseline/_ref/ct/``; the model
+    folder is the 8B-shaped random model of the default arm (same seed, same bits), written to a
+    temporary folder.  It has no decode loop, so ``value`` (decode tokens/s) stays unavailable."""
+    import re
+    import shutil
+    import tempfile
+    ct = os.path.join(ROOT, "baseline", "_ref", "ct")
+    binary = os.path.join(ct, "build", "cleanroom-transformer-cuda")
+    line = {"impl": "reference", "unavailable": NO_DECODE}
+    if a.gpus != 1:
+        print(json.dumps(line))
+        return 0
+    if not os.path.isfile(binary) and os.path.isfile(os.path.join(ct, "Makefile")):
+        subprocess.run(["make", "-C", ct, "cuda", "CC=/usr/bin/gcc"], capture_output=True, text=True)
+    if not os.path.isfile(binary):
+        line["prefill"] = {"unavailable": "the reference's CUDA build is not installed under baseline/_ref/ct "
+                                          "(copy cleanroom-transformer/ there and run `make cuda CC=/usr/bin/gcc`)"}
+        print(json.dumps(line))
+        return 0
+    import torch
+    import hilbert_pruned_8b_b200 as hb
+    cfg_dict = dict(MODEL_8B)
+    layers = a.layers or cfg_dict["num_hidden_layers"]
+    cfg_dict["num_hidden_layers"] = layers
+    folder = tempfile.mkdtemp(prefix="hilbert_b200_reference_model_")
+    try:
+        t0 = time.time()
+        hb.weights.write_random_model(folder, hb.LlamaConfig.from_dict(cfg_dict), seed=0, device="cuda:0")
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        write_s = time.time() - t0
+        env = dict(os.environ)
+        env["LD_LIBRARY_PATH"] = os.pathsep.join(filter(None, [env.get("LD_LIBRARY_PATH"), "/usr/local/cuda/lib64"]))
+        clocks = ClockSampler()
+        clocks.start()
+        t0 = time.time()
+        try:
+            res = subprocess.run([binary, "selftest", "--tokens", "2", "--model", folder], capture_output=True, text=True,
+                                 env=env, timeout=1500)
+            out, err, rc = res.stdout, res.stderr, res.returncode
+        except subprocess.TimeoutExpired as e:
+            out, err, rc = (e.stdout or b"").decode("utf-8", "replace") if isinstance(e.stdout, bytes) else (e.stdout or ""), \
+                "selftest did not end within 1500 s", 124
+        run_s = time.time() - t0
+        clock_info = clocks.stop()
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    m = re.search(r"cuda prefill (\d+) tokens: ([0-9.]+) ms \(([0-9.]+) tokens/s\)", out)
+    pk, pk_src = peaks()
+    if m:
+        tokens, ms = int(m.group(1)), float(m.group(2))
+        line["prefill"] = {"value": round(tokens / (ms * 1e-3), 1), "tokens": tokens, "ms": round(ms, 3),
+                           "frac": round(prefill_flops(cfg_dict, layers, tokens) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                           "timer": "the reference's own: host clock around its second (warm) prefill, device synchronised"}
+    else:
+        tail = (err.strip().splitlines() or out.strip().splitlines() or ["no output"])[-1]
+        line["prefill"] = {"unavailable": f"the reference's selftest printed no prefill time (exit code {rc}): {tail[:300]}"}
+    checks = [l.strip() for l in out.splitlines() if l.strip().endswith(("ok", "FAIL")) and "cuda vs cpu" in l]
+    line.update({
+        "metric": "prefill tok/s @ 2048 tokens (Llama-3.1-8B-shaped, random weights), the reference's own selftest timer",
+        "unit": "tokens/s", "n_gpus": 1, "steps": 1, "warmup": 1, "dtype": "bf16 weights and GEMM inputs, float32 activations and cache",
+        "data": "synthetic: random weights (the default arm's seed), the selftest's own token ids",
+        "config": {"model": "llama-3.1-8b-shaped", "layers": layers, "layers_in_config": MODEL_8B["num_hidden_layers"],
+                   "hidden": cfg_dict["hidden_size"], "vocab": cfg_dict["vocab_size"], "prefill_tokens": PREFILL_TOKENS,
+                   "command": "cleanroom-transformer-cuda selftest --tokens 2 --model DIR", "build": "make cuda (stock flags: sm_86 + compute_86 PTX)",
+                   "peaks": pk_src},
+        "selftest_exit_code": rc, "selftest_checks": checks[:4], "model_write_s": round(write_s, 1), "selftest_s": round(run_s, 1),
+        "clocks": clock_info})
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -412,12 +494,7 @@ def main() -> int:
     if a.timeline:
         os.environ["HILBERT_B200_TIMELINE"] = "1"      # before the kernel library is looked for
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the installed reference package (semif-score) only scores answer options of text rows "
-                          "through transformers and needs a tokenizer and a hub revision; neither it nor the reference's "
-                          "C engine generates tokens (no decode loop or sampler: cleanroom-transformer/README.md:7-10), "
-                          "so it has no decode tokens/s to measure"}))
-        return 0
+        return reference_arm(a)
     if a.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported by this single-GPU library")
         return 2

@@ -194,13 +194,16 @@ def random_tensors(table: Mapping[str, ParamSpec], seed: int, device: torch.devi
 
 
 def write_random_model(model_dir: str, config, seed: int, std: float = 0.02, norm_std: float = 0.0,
-                       dtype: torch.dtype = torch.bfloat16, fan_in_scale: Optional[float] = None) -> str:
-    """Writes ``model_dir/config.json`` and ``model_dir/model.safetensors`` for ``config``."""
+                       dtype: torch.dtype = torch.bfloat16, fan_in_scale: Optional[float] = None,
+                       device="cpu") -> str:
+    """Writes ``model_dir/config.json`` and ``model_dir/model.safetensors`` for ``config``.
+    ``device``: where the values are drawn (a CUDA device is much faster for a large model; the
+    file is the same, bit for bit)."""
     from ..engine.model import weight_table  # the table is the model's, not the writer's
     os.makedirs(model_dir, exist_ok=True)
     spec = config.model_spec()
     table = weight_table(spec, prefix=spec.weight_prefixes[-1])
-    tensors = random_tensors(table, seed, torch.device("cpu"), std, norm_std, dtype, fan_in_scale)
+    tensors = random_tensors(table, seed, torch.device(device), std, norm_std, dtype, fan_in_scale)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config.to_dict(), f, indent=1)
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors)
