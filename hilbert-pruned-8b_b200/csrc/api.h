@@ -37,30 +37,6 @@ int hb_gemm_tc_resident_clusters(int mode, int size);
 int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,
                int M, int N, int K, int mode, int up_row0, int schedule, float* partials, long long partials_capacity,
                int* tile_counters, long long counters_capacity, int* error_flag, int packed, void* stream);
-// One operation of a chain (hb_gemm_chain): a product with the operands and epilogue of
-// hb_gemm_tc, or an RMSNorm with the arguments of hb_rmsnorm.
-typedef struct {
-    int type;                 // 0: product, 1: RMSNorm
-    int M, N, K, mode, up_row0, packed;          // product: out[M, N] (op)= a[M, K] w[N, K]^T
-    const void* a;
-    long long lda;
-    const void* w;
-    long long ldw, w_rows;
-    void* out;
-    long long ldc;
-    const float* x;           // norm: nout[r] = norm(x[rows ? rows[r] : r]) for r < n_rows
-    const float* weight;
-    float eps, offset;
-    void* nout;
-    int out_dtype;
-    const int* rows;
-    int n_rows, hidden;
-} HbChainOp;
-int hb_gemm_chain_max_ops(void);
-int hb_gemm_chain_max_rows(void);
-int hb_gemm_chain_scratch(const HbChainOp* ops, int n_ops, long long* floats, long long* counters);
-int hb_gemm_chain(const HbChainOp* ops, int n_ops, float* partials, long long partials_capacity, int* counters,
-                  long long counters_capacity, int* barrier, int* status, void* stream);
 int hb_gemm_tc2_wanted(int M, int N, int K);
 int hb_gemm_tc2_resident_pairs(int mode);
 int hb_gemm_tc2(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,

@@ -38,10 +38,6 @@ class DecoderModel:
         self.final_norm = NORMS.build(spec.final_norm, ctx)
         self.head = HEADS.build(spec.head, ctx)
         self.prefix = spec.weight_prefixes[-1]
-        # every part and arrangement reaches device memory through the kernel library alone: its
-        # launches may be collected into chains
-        self.kernel_only = (all(getattr(part, "kernel_only", False) for _, part in self.named_parts())
-                            and all(getattr(b, "kernel_only", False) for b in self.blocks))
         self.graph_safe = (all(getattr(part, "graph_safe", True) for _, part in self.named_parts())
                            and all(getattr(b, "graph_safe", True) for b in self.blocks))
 
@@ -125,12 +121,6 @@ class DecoderModel:
     def forward(self, step, cache) -> Optional[torch.Tensor]:
         """Runs the step's tokens through the decoder; returns ``[wanted, vocab]`` 32-bit
         logits (None when nothing is wanted)."""
-        if self.kernel_only and hasattr(self.ctx.ops, "chaining"):
-            with self.ctx.ops.chaining():
-                return self._forward(step, cache)
-        return self._forward(step, cache)
-
-    def _forward(self, step, cache) -> Optional[torch.Tensor]:
         ws, cap, T = self.ctx.workspace, self.ctx.max_step_tokens, step.num_tokens
         H, V = self.spec.hidden_size, self.spec.vocab_size
         x = ws.buffer("model.x", (cap, H), torch.float32)[:T]

@@ -22,14 +22,6 @@ from .plan import decode_splits
 
 _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
 
-class _ChainOp(ctypes.Structure):
-    """``HbChainOp`` of csrc/api.h: one operation of a chain."""
-    _fields_ = [("type", _c_int), ("M", _c_int), ("N", _c_int), ("K", _c_int), ("mode", _c_int), ("up_row0", _c_int),
-                ("packed", _c_int), ("a", _c_ptr), ("lda", _c_ll), ("w", _c_ptr), ("ldw", _c_ll), ("w_rows", _c_ll),
-                ("out", _c_ptr), ("ldc", _c_ll), ("x", _c_ptr), ("weight", _c_ptr), ("eps", _c_float), ("offset", _c_float),
-                ("nout", _c_ptr), ("out_dtype", _c_int), ("rows", _c_ptr), ("n_rows", _c_int), ("hidden", _c_int)]
-
-
 _SIGNATURES = {
     "hb_device_info": [_c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "hb_timeline_set": [_c_ptr, _c_ptr, _c_int, _c_int],
@@ -58,8 +50,6 @@ _SIGNATURES = {
                              _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_prefill_tc": [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
-    "hb_gemm_chain": [ctypes.POINTER(_ChainOp), _c_int, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr],
-    "hb_gemm_chain_scratch": [ctypes.POINTER(_ChainOp), _c_int, ctypes.POINTER(_c_ll), ctypes.POINTER(_c_ll)],
     "hb_random_normal": [_c_ptr, _c_int, _c_ll, ctypes.c_ulonglong, _c_float, _c_float, _c_ptr],
     "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -86,8 +76,6 @@ def load_library():
             fn.argtypes = args
             fn.restype = _c_int
         lib.hb_gemm_tc_token_tile.argtypes, lib.hb_gemm_tc_token_tile.restype = [_c_int], _c_int
-        lib.hb_gemm_chain_max_ops.argtypes, lib.hb_gemm_chain_max_ops.restype = [], _c_int
-        lib.hb_gemm_chain_max_rows.argtypes, lib.hb_gemm_chain_max_rows.restype = [], _c_int
         lib.hb_gemm_tc_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int, _c_int]
         lib.hb_gemm_tc_scratch_floats.restype = _c_ll
         lib.hb_gemm_tc_tiles.argtypes, lib.hb_gemm_tc_tiles.restype = [_c_int, _c_int, _c_int], _c_ll
@@ -180,7 +168,6 @@ class Ops:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device is available; the library has no CPU path")
         self.lib = load_library()
-        self._chain = []                # operations collected for a chain (see chaining())
         self.call_log = None  # a list: the name of every library call is appended (diagnostics)
         major, minor, sms = _c_int(), _c_int(), _c_int()
         idx = self.device.index if self.device.index is not None else torch.cuda.current_device()
@@ -205,16 +192,6 @@ class Ops:
         # split-K decode attention scratch: partial outputs with their maxima and sums
         self._decode_scratch = torch.empty(4 << 20, dtype=torch.float32, device=self.device)
         self._decode_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
-        # Chains (csrc/gemm_chain.cu): inside ``with ops.chaining():`` few-token products and norms
-        # are not launched one by one but collected, and everything collected runs as ONE persistent
-        # launch when an operation of another kind comes (or the block ends).  HILBERT_B200_CHAIN=0
-        # switches the collecting off.
-        self.use_chain = os.environ.get("HILBERT_B200_CHAIN", "1") != "0"
-        self._chain_depth = 0           # _chain holds (_ChainOp, tensors kept alive, stand-alone launch)
-        self._chain_barrier = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._chain_max_ops = self.lib.hb_gemm_chain_max_ops()
-        self._chain_max_rows = self.lib.hb_gemm_chain_max_rows()
-        self.chain_launches = 0
         self._retired = []              # outgrown scratch, kept alive for graphs that captured it
         self._splits_cache = {}
         self.use_tcgen05_attention = True   # head size 128 prefill on tcgen05 (else the mma.sync kernel)
@@ -237,64 +214,11 @@ class Ops:
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
-        if self._chain:
-            self.flush()                # an operation of another kind: what was collected runs first
         rc = getattr(self.lib, name)(*args)
         if rc != 0:
             raise KernelError(self.lib.hb_last_error().decode("utf-8", "replace"))
         if self.call_log is not None:
             self.call_log.append(name)
-
-    # ------------------------------------------------------------------ chains
-    def chaining(self):
-        """Context in which few-token products and norms are collected into chains.  Only for code
-        that touches device memory through this object alone: a torch operation on a tensor that a
-        collected operation has yet to write would read it too early (``flush()`` first)."""
-        ops = self
-
-        class _Chaining:
-            def __enter__(self):
-                ops._chain_depth += 1
-
-            def __exit__(self, *exc):
-                ops._chain_depth -= 1
-                if ops._chain_depth == 0:
-                    ops.flush()
-                return False
-        return _Chaining()
-
-    def _collect(self, op: "_ChainOp", keep, launch) -> None:
-        products = sum(1 for o, _, _ in self._chain if o.type == 0)
-        if len(self._chain) >= self._chain_max_ops or (op.type == 0 and products >= 4):
-            self.flush()
-        self._chain.append((op, keep, launch))
-
-    def _chains_now(self, rows: int) -> bool:
-        return self._chain_depth > 0 and self.use_chain and 1 <= rows <= self._chain_max_rows
-
-    def flush(self) -> None:
-        """Launches what was collected: one operation as its own kernel, several as one chain."""
-        chain, self._chain = self._chain, []
-        if not chain:
-            return
-        if len(chain) == 1:
-            chain[0][2]()
-            return
-        n = len(chain)
-        arr = (_ChainOp * n)(*[c[0] for c in chain])
-        floats, counters = _c_ll(), _c_ll()
-        self._call("hb_gemm_chain_scratch", arr, n, ctypes.byref(floats), ctypes.byref(counters))
-        if floats.value > self._splitk_partials.numel():
-            self._retired.append(self._splitk_partials)     # a captured graph may still write there
-            self._splitk_partials = torch.empty(floats.value, dtype=torch.float32, device=self.device)
-        if counters.value > self._splitk_counters.numel():
-            self._retired.append(self._splitk_counters)
-            self._splitk_counters = torch.zeros(counters.value, dtype=torch.int32, device=self.device)
-        self._call("hb_gemm_chain", arr, n, self._splitk_partials.data_ptr(), self._splitk_partials.numel(),
-                   self._splitk_counters.data_ptr(), self._splitk_counters.numel(), self._chain_barrier.data_ptr(),
-                   self.status.data_ptr(), self._stream())
-        self.launches += 1
-        self.chain_launches += 1
 
     # ------------------------------------------------------------------ timeline
     def timeline_begin(self, capacity: int = 1 << 16, events: bool = False) -> None:
@@ -358,20 +282,9 @@ class Ops:
             if rows.dtype != torch.int32 or rows.numel() != n:
                 raise KernelError("rmsnorm: rows must be int32, one per output row")
             rp = rows.data_ptr()
-        code = _code(out)
-
-        def launch():
-            self._call("hb_rmsnorm", x.data_ptr(), weight.data_ptr(), float(eps), float(offset), out.data_ptr(), code,
-                       rp, n, H, self._stream())
-            self.launches += 1
-
-        if (self._chains_now(n) and H % 4 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
-                and out.data_ptr() % 16 == 0):
-            op = _ChainOp(type=1, x=x.data_ptr(), weight=weight.data_ptr(), eps=float(eps), offset=float(offset),
-                          nout=out.data_ptr(), out_dtype=code, rows=rp, n_rows=n, hidden=H)
-            self._collect(op, (x, weight, out, rows), launch)
-            return
-        launch()
+        self._call("hb_rmsnorm", x.data_ptr(), weight.data_ptr(), float(eps), float(offset), out.data_ptr(), _code(out),
+                   rp, n, H, self._stream())
+        self.launches += 1
 
     def silu_mul(self, gate_up, out) -> None:
         self._dev(gate_up, out)
@@ -447,7 +360,6 @@ class Ops:
         self.status.zero_()
         self._splitk_counters.zero_()
         self._decode_counters.zero_()
-        self._chain_barrier.zero_()
 
     def check_errors(self) -> None:
         """Reads the device status words (this synchronises) and raises if a kernel noted a fault."""
@@ -472,18 +384,6 @@ class Ops:
     SCHEDULES = {None: 0, "auto": 0, "tiles": 1, "stream_k": 2, "cut_first": 3}
 
     def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None) -> None:
-        M, K = a.shape
-        packed = 1 if isinstance(w, PackedWeight) else 0
-        ldw = 64 if packed else _rows(w, "linear weight")
-        if schedule is None and self._chains_now(M):
-            op = _ChainOp(type=0, M=M, N=N, K=K, mode=mode, up_row0=up_row0, packed=packed, a=a.data_ptr(),
-                          lda=_rows(a, "linear input"), w=w.data_ptr(), ldw=ldw, w_rows=w.shape[0], out=out.data_ptr(),
-                          ldc=_rows(out, "linear output"))
-            self._collect(op, (a, w, out), lambda: self._gemm_tc_now(a, w, out, mode, N, up_row0, None))
-            return
-        self._gemm_tc_now(a, w, out, mode, N, up_row0, schedule)
-
-    def _gemm_tc_now(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None) -> None:
         M, K = a.shape
         packed = 1 if isinstance(w, PackedWeight) else 0
         ldw = 64 if packed else _rows(w, "linear weight")

@@ -34,7 +34,6 @@ class Attention(Mixer):
         pos = p.get("position")
         self.position = ctx.shared_part(POSITION_ENCODINGS, pos) if pos is not None else None
         self.graph_safe = getattr(self.position, "graph_safe", True)      # a step is as capturable as its parts
-        self.kernel_only = self.position is None or bool(getattr(self.position, "kernel_only", False))
         # whether decode steps may run the kernel that rotates, appends and attends in one launch
         # (the part decides; the kernel library only says whether it can)
         self.fuse_decode = bool(p.get("fuse_decode", True))

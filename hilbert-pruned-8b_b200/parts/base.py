@@ -24,8 +24,6 @@ What a part must provide:
   themselves), else ``apply(q, k, step)`` which turns them in place; see ``PositionEncoding``.
 * blocks (``parts/block.py``): ``ROLES``, ``named_parts()``, ``cache_need()``, ``state_need()``,
   ``forward(x, step, cache, state, append)``.
-* ``kernel_only`` (class attribute, default False): the part reaches device memory through
-  ``ctx.ops`` alone, so the kernel library may hold back and fuse its launches.
 * ``graph_safe`` (class attribute, default True): whether ``forward`` only enqueues work on
   the current stream, so that a decode step can be captured in a CUDA graph.
 """
@@ -90,11 +88,6 @@ class Part:
     # False for a part whose forward reads device values on the host or allocates: the engine
     # then runs its decode steps eagerly instead of replaying a captured CUDA graph
     graph_safe = True
-    # True for a part whose forward touches device memory through the kernel library (``ctx.ops``)
-    # ONLY: no torch operation reads or writes its inputs, outputs or the residual.  The library
-    # may then hold back and fuse launches (``Ops.chaining``); a model whose parts all say so runs
-    # its few-token steps that way.  The default is the safe one.
-    kernel_only = False
 
     def __init__(self, spec: PartSpec, ctx: BuildContext):
         self.spec = spec

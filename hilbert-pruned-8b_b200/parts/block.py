@@ -19,8 +19,6 @@ class Block:
     """Base of the arrangements: builds the parts that ``ROLES`` names from the layer's spec."""
 
     ROLES: Dict[str, Registry] = {}
-    # whether this arrangement's own forward reaches device memory through ctx.ops alone (see Part.kernel_only)
-    kernel_only_arrangement = False
 
     def __init__(self, layer_spec, ctx):
         self.spec = layer_spec
@@ -31,7 +29,6 @@ class Block:
                              f"{layer_spec.prefix!r} (its roles: {', '.join(self.ROLES)})")
         self.parts = {role: registry.build(layer_spec.part(role), ctx) for role, registry in self.ROLES.items()}
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.parts.values())
-        self.kernel_only = self.kernel_only_arrangement and all(getattr(p, "kernel_only", False) for p in self.parts.values())
 
     def named_parts(self) -> List[Tuple[str, object]]:
         """(name prefix below the layer's prefix, part) for every part that may own weights."""
@@ -53,7 +50,6 @@ class Block:
 @BLOCKS.register("prenorm")
 class PreNormBlock(Block):
     ROLES = {"mixer_norm": NORMS, "mixer": MIXERS, "feed_forward_norm": NORMS, "feed_forward": FEED_FORWARDS}
-    kernel_only_arrangement = True
 
     def __init__(self, layer_spec, ctx):
         super().__init__(layer_spec, ctx)

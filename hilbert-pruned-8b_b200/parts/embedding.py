@@ -15,8 +15,6 @@ from .base import EMBEDDINGS, HEADS, ParamSpec, Part
 
 @EMBEDDINGS.register("embedding")
 class TokenEmbedding(Part):
-    kernel_only = True
-
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.vocab = int(spec.params["vocab_size"])
@@ -35,8 +33,6 @@ class TokenEmbedding(Part):
 
 @HEADS.register("lm_head")
 class LMHead(Part):
-    kernel_only = True
-
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.vocab = int(spec.params["vocab_size"])

@@ -16,8 +16,6 @@ from .base import NORMS, Norm, ParamSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    kernel_only = True
-
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.size = int(spec.params["size"])

@@ -42,8 +42,6 @@ def rotary_inv_freq(rotary_dim: int, theta: float, llama3=None) -> np.ndarray:
 
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEmbedding(PositionEncoding):
-    kernel_only = True
-
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.head_dim = int(spec.params["head_dim"])

@@ -15,8 +15,6 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    kernel_only = True
-
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         self.hidden = int(spec.params["hidden_size"])

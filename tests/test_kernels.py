@@ -655,99 +655,3 @@ def test_temperature_sampling_follows_the_cdf(ops, vocab):
     assert torch.equal(out, again)
     ops.sample(lg, torch.tensor(temps, device=DEV), seeds, reqs, steps + 1, again)
     assert not torch.equal(out, again)
-
-
-# --------------------------------------------------------------------------------- chains
-@pytest.mark.parametrize("M,H,I,N2,packed", [(8, 512, 1024, 384, True), (1, 256, 320, 100, False), (16, 4096, 14336, 6144, True),
-                                              (17, 2048, 8192, 2560, True), (40, 320, 448, 200, False), (64, 3072, 8192, 5120, True),
-                                              (5, 96, 208, 300, False), (64, 4096, 14336, 128256, True)])
-def test_chain_of_products_and_norms(ops, M, H, I, N2, packed):
-    """What a decoder layer queues between two attentions (output projection into the residual,
-    norm, gate/up with SiLU, down into the residual, norm, a product that stores) as ONE
-    persistent launch, against the same operations launched one by one and against float64;
-    twice in a row (the barrier and the tile counters must come back to zero); the last product
-    stores 32-bit (the head) or bfloat16 (q/k/v)."""
-    from hilbert_pruned_8b_b200.engine.workspace import Workspace
-    torch.manual_seed(100 + M)
-    ws = Workspace(torch.device(DEV))
-    pk = (lambda w, **kw: ops.pack_weight(w, **kw)) if packed else (lambda w, **kw: w)
-    attn = _bf(torch.randn(M, H, device=DEV))
-    x0 = torch.randn(M, H, device=DEV)
-    w_o = _bf(torch.randn(H, H, device=DEV) / math.sqrt(H))
-    w_gu = _bf(torch.randn(2 * I, H, device=DEV) / math.sqrt(H))
-    w_d = _bf(torch.randn(H, I, device=DEV) / math.sqrt(I))
-    w_2 = _bf(torch.randn(N2, H, device=DEV) / math.sqrt(H))
-    g1, g2 = 1 + 0.1 * torch.randn(H, device=DEV), 1 + 0.1 * torch.randn(H, device=DEV)
-    p_o, p_gu, p_d, p_2 = pk(w_o), pk(w_gu, swiglu=True), pk(w_d), pk(w_2)
-
-    def run(out_dtype):
-        x = x0.clone()
-        h = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
-        act = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
-        out = torch.full((M, N2), 7.0, device=DEV, dtype=out_dtype)
-        with ops.chaining():
-            ops.linear(attn, p_o, x, accumulate=True)
-            ops.rmsnorm(x, g1, 1e-5, 0.0, h)
-            ops.linear_swiglu(h, p_gu, act, ws, M)
-            ops.linear(act, p_d, x, accumulate=True)
-            ops.rmsnorm(x, g2, 1e-5, 0.0, h)
-            ops.linear(h, p_2, out)
-        ops.check_errors()
-        return x, out
-
-    rnd = lambda t: t.to(torch.bfloat16).double()
-    xd = x0.double() + attn.double() @ w_o.double().t()
-    hd = rnd(xd / torch.sqrt((xd ** 2).mean(-1, keepdim=True) + 1e-5) * g1.double())
-    gg, uu = hd @ w_gu[:I].double().t(), hd @ w_gu[I:].double().t()
-    xd = xd + rnd(gg / (1 + torch.exp(-gg)) * uu) @ w_d.double().t()
-    hd = rnd(xd / torch.sqrt((xd ** 2).mean(-1, keepdim=True) + 1e-5) * g2.double())
-    ref = hd @ w_2.double().t()
-    for out_dtype in (torch.float32, torch.bfloat16):
-        ops.use_chain = True
-        before = ops.chain_launches
-        x_c, out_c = run(out_dtype)
-        x_c2, out_c2 = run(out_dtype)
-        chained = ops.chain_launches - before
-        ops.use_chain = False
-        try:
-            x_s, out_s = run(out_dtype)
-        finally:
-            ops.use_chain = True
-        uses_tc = H % 8 == 0 and I % 8 == 0 and (I % 64 == 0 or not packed)
-        assert chained == (2 if uses_tc else 0) or not uses_tc
-        assert torch.equal(x_c, x_c2) and torch.equal(out_c, out_c2)                 # the sum order is fixed
-        assert int(ops._chain_barrier.item()) == 0 and int(ops._splitk_counters.abs().sum()) == 0
-        assert _rel(x_c, xd) < 2e-3 and _rel(x_c, x_s) < 2e-3
-        tol = 2e-2
-        assert _rel(out_c, ref) < tol and _rel(out_s, ref) < tol and _rel(out_c, out_s) < tol
-    assert ops.status.tolist() == [0, 0, 0, 0]
-
-
-def test_chain_of_a_norm_and_a_product_and_gathered_rows(ops):
-    """The shortest chains: a norm and a product (a model's first layer), and a norm that gathers
-    rows (the final norm on the wanted rows) in front of the head's product."""
-    torch.manual_seed(9)
-    T, H, N = 23, 1024, 2000
-    x = torch.randn(T, H, device=DEV) * 2
-    g = 1 + 0.1 * torch.randn(H, device=DEV)
-    w = _bf(torch.randn(N, H, device=DEV) / math.sqrt(H))
-    rows = torch.tensor([22, 0, 7, 7, 3], dtype=torch.int32, device=DEV)
-    for sel in (None, rows):
-        n = T if sel is None else sel.numel()
-        src = x if sel is None else x[sel.long()]
-        hd = (src.double() / torch.sqrt((src.double() ** 2).mean(-1, keepdim=True) + 1e-6) * g.double()).to(torch.bfloat16).double()
-        ref = hd @ w.double().t()
-        h = torch.empty(n, H, device=DEV, dtype=torch.bfloat16)
-        out = torch.empty(n, N, device=DEV)
-        before = ops.chain_launches
-        with ops.chaining():
-            ops.rmsnorm(x, g, 1e-6, 0.0, h, sel)
-            ops.linear(h, w, out)
-        ops.check_errors()
-        assert ops.chain_launches == before + 1
-        assert _rel(h, hd) < 2 ** -8 and _rel(out, ref) < 2e-2
-    # one operation alone is launched as its own kernel; an operation of another kind flushes
-    before = ops.chain_launches
-    with ops.chaining():
-        ops.rmsnorm(x, g, 1e-6, 0.0, torch.empty(T, H, device=DEV, dtype=torch.bfloat16))
-    assert ops.chain_launches == before
