@@ -46,13 +46,14 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
     constexpr int KSTEPS = HD / 16;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    bool bad_page = false;
     auto load_page = [&](int stage, int page_idx) {
         if (page_idx < p_end) {
             // every page of [p_begin, p_end) holds a key the query sees: one that is missing from the
             // table or outside the cache is a fault of the host's bookkeeping (noted, not trapped)
             int page = pt[page_idx];
             if (page < 0 || page >= n_pages) {
-                if (tid == 0) hb_note(status, HB_STATUS_PAGE, 1 + batch_row);
+                bad_page = true;                            // noted once, behind the loop
                 page = 0;                                   // never read outside the cache
             }
             const uint8_t* ksrc = (const uint8_t*)(kc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
@@ -169,6 +170,7 @@ __device__ __forceinline__ void decode_split_core(uint32_t (&qf)[HD / 16][4], co
     }
     cp_async_wait<0>();
     __syncthreads();
+    if (bad_page && tid == 0) hb_note(status, HB_STATUS_PAGE, 1 + batch_row);
 
     // merge the four warps (each saw a quarter of every page) and write the split's partial
 #pragma unroll

@@ -80,13 +80,14 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     const int w_lo = (window > 0 && w_first - window + 1 > 0) ? w_first - window + 1 : 0;
 
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    bool bad_page = false;
     auto load_page = [&](int stage, int page_idx) {
         if (page_idx < p_end) {
             // every page of [p_begin, p_end) holds a key that a row of this CTA sees: one that is
             // missing or outside the cache is a fault of the host's bookkeeping
             int page = page_idx < pt_width ? pt[page_idx] : -1;
             if (page < 0 || page >= n_pages) {
-                if (tid == 0) hb_note(status, HB_STATUS_PAGE, 1 + b);
+                bad_page = true;                                // noted once, behind the loop
                 page = 0;                                       // never read outside the cache
             }
             const uint8_t* ksrc = (const uint8_t*)(kc + ((size_t)page * nkv + g) * HB_PAGE_TOKENS * HD);
@@ -192,6 +193,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
         }
     }
     cp_async_wait<0>();
+    if (bad_page && tid == 0) hb_note(status, HB_STATUS_PAGE, 1 + b);
 
 #pragma unroll
     for (int h = 0; h < 2; h++) {
