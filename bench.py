@@ -484,6 +484,9 @@ def main() -> int:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16",
+                    help="float32: the true 32-bit path (FP32-pipe products, general attention), a line of its own; "
+                         "give --layers to keep it short")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=("8b", "3b", "1b"), default="8b",
                     help="8b: the default line; 3b, 1b: the generation workloads at those shapes (--steps = repeats)")
@@ -512,10 +515,13 @@ def main() -> int:
     cfg_dict["num_hidden_layers"] = layers
     cfg = hb.LlamaConfig.from_dict(cfg_dict)
     pk, pk_src = peaks()
+    fp32 = a.dtype == "float32"
+    if fp32:
+        a.skip_points = True            # the other points are about the serving precision
     max_batch = 64 if not a.skip_points else a.batch
     max_tokens = max_batch * CONTEXT
     t_build = time.time()
-    llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, device=0, max_batch=max_batch,
+    llm = LLM.random(cfg, seed=0, dtype=a.dtype, max_tokens=max_tokens, device=0, max_batch=max_batch,
                      max_step_tokens=PREFILL_TOKENS)
     fill_cache_random(llm)
     torch.cuda.synchronize()
@@ -545,11 +551,15 @@ def main() -> int:
             points.update(other_shape_point(name, max(8, a.steps), pk))
     achieved = step_bytes / (ms * 1e-3) / 1e9
     value = a.batch / (ms * 1e-3)
+    # the 32-bit path runs on the FP32 pipe: its prefill fraction is of that pipe's nominal peak
+    # (148 SMs x 128 lanes x 2 flop x 1.965 GHz), not of the tensor cores'
+    flop_peak = 148 * 128 * 2 * 1.965e9 if fp32 else pk["bf16_tflops"] * 1e12
     line = {
-        "metric": "decode tok/s @ batch 8, context 8192 (Llama-3.1-8B-shaped, random weights)",
+        "metric": f"decode tok/s @ batch {a.batch}, context 8192 (Llama-3.1-8B-shaped, random weights)"
+                  + (", true 32-bit path" if fp32 else ""),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache contents",
+        "dtype": "fp32" if fp32 else "bf16", "data": "synthetic: random weights, random token ids, random cache contents",
         "impl": "ours",
         "config": {"model": "llama-3.1-8b-shaped", "layers": layers, "layers_in_config": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
@@ -560,7 +570,7 @@ def main() -> int:
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(prefill_ms, 3), "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "ms": round(prefill_ms, 3), "frac": round(pf / (prefill_ms * 1e-3) / flop_peak, 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,

@@ -15,8 +15,9 @@ int hb_device_info(int device, int* sm_major, int* sm_minor, int* sm_count);
 
 // `status` (here and below): the caller's int32[4] status words (common.cuh: a bounded wait that
 // ran out, non-finite logits, a bad page number, a bad token id), or null.
+// `packed`: the table is stored as contiguous 128 x 64 tiles (the layout of hb_gemm_tc's packed weights)
 int hb_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int hidden,
-             int vocab, int* status, void* stream);
+             int vocab, int packed, int* status, void* stream);
 int hb_rmsnorm(const float* x, const float* weight, float eps, float offset, void* out, int out_dtype,
                const int* rows, int n_rows, int hidden, void* stream);
 int hb_silu_mul(const void* gate_up, int in_dtype, long long in_stride, void* out, int out_dtype,

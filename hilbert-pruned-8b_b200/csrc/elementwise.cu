@@ -7,9 +7,12 @@
 
 // ---------------------------------------------------------------------------------- embed
 // x[t,:] = float(E[token[t],:])   (cpu_backend.c:236; cuda_backend.cu:66-70)
+// `kbt` > 0: the table is stored as the tensor-core products store a weight (contiguous tiles
+// of 128 rows x 64 columns, the tiles of a 128-row band one after another along the columns,
+// kbt of them): a tied output head and the embedding then share ONE copy of the table.
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out,
-                             int hidden, int vocab, int* status) {
+                             int hidden, int vocab, int kbt, int* status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -18,20 +21,26 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
         if (threadIdx.x == 0) hb_note(status, HB_STATUS_TOKEN, 1 + t);
         tok = 0;                           // never read outside the table
     }
-    const TW* row = table + (size_t)tok * hidden;
     float* o = out + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+    if (kbt > 0) {
+        const TW* band = table + ((size_t)(tok >> 7) * kbt * 128 + (tok & 127)) * 64;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(band[(size_t)(i >> 6) * (128 * 64) + (i & 63)]);
+    } else {
+        const TW* row = table + (size_t)tok * hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+    }
 }
 
 extern "C" int hb_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int hidden,
-                        int vocab, int* status, void* stream) {
+                        int vocab, int packed, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
+    const int kbt = packed ? (hidden + 63) / 64 : 0;
     if (table_dtype == HB_BF16)
-        hb_launch(embed_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, out, hidden, vocab, status);
+        hb_launch(embed_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, out, hidden, vocab, kbt, status);
     else if (table_dtype == HB_F32)
-        hb_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, out, hidden, vocab, status);
+        hb_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, out, hidden, vocab, kbt, status);
     else
         return hb_fail("embed: unsupported table dtype %d", table_dtype);
     return hb_check_launch("embed");

@@ -73,7 +73,9 @@ class DecoderModel:
                     local[p.name] = tensors[full]
             part.bind(local)
         if getattr(self.head, "tied", False):
-            self.head.tie(self.embedding.weight)
+            stored = self.head.tie(self.embedding.weight)
+            if stored is not None and stored is not self.embedding.weight and hasattr(self.embedding, "share"):
+                self.embedding.share(stored)       # one copy of the table for both
 
     def first_weight_name(self) -> str:
         return self.spec.embedding_prefix + self.embedding.params()[0].name

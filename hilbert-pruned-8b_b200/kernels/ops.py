@@ -25,7 +25,7 @@ _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_floa
 _SIGNATURES = {
     "hb_device_info": [_c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "hb_timeline_set": [_c_ptr, _c_ptr, _c_int, _c_int],
-    "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_rmsnorm": [_c_ptr, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_silu_mul": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
     "hb_rope_table": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -254,15 +254,17 @@ class Ops:
 
     # ------------------------------------------------------------------ elementwise
     def embed(self, tokens, table, out) -> None:
-        self._dev(tokens, table, out)
+        """``out[t] = table[tokens[t]]`` widened to 32-bit; ``table`` row-major or a PackedWeight."""
+        packed = isinstance(table, PackedWeight)
+        self._dev(tokens, table.data if packed else table, out)
         if tokens.dtype != torch.int32 or out.dtype != torch.float32 or not out.is_contiguous() \
-                or not table.is_contiguous():
+                or not (packed or table.is_contiguous()):
             raise KernelError("embed: tokens int32, contiguous table, contiguous float32 output expected")
         T, H = out.shape
         if table.shape[1] != H or tokens.numel() != T:
             raise KernelError("embed: shapes do not agree")
         self._call("hb_embed", tokens.data_ptr(), table.data_ptr(), _code(table), out.data_ptr(), T, H,
-                   table.shape[0], self.status.data_ptr(), self._stream())
+                   table.shape[0], 1 if packed else 0, self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def rmsnorm(self, x, weight, eps: float, offset: float, out, rows=None) -> None:

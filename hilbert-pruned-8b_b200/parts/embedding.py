@@ -27,6 +27,11 @@ class TokenEmbedding(Part):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
 
+    def share(self, stored) -> None:
+        """Reads the table from ``stored`` from now on (the same values in the layout a tied head
+        keeps them in), so that one copy serves both; the row-major copy is let go."""
+        self.weight = stored
+
     def forward(self, tokens, out) -> None:
         self.ctx.ops.embed(tokens, self.weight, out)
 
@@ -48,9 +53,11 @@ class LMHead(Part):
         if not self.tied:
             self.weight = self.ctx.ops.pack_weight(tensors["weight"].contiguous())
 
-    def tie(self, embedding_weight: torch.Tensor) -> None:
-        # the table is gathered from by rows; the head reads its own copy, stored as tiles
+    def tie(self, embedding_weight: torch.Tensor):
+        """The head reads the embedding table; returns the form it keeps it in (tiles, where the
+        tensor-core product can read them), which the embedding can gather from as well."""
         self.weight = self.ctx.ops.pack_weight(embedding_weight)
+        return self.weight
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -52,18 +52,30 @@ def option_scores(logits: Sequence[float]) -> List[float]:
 
 
 class Sampler:
-    """Device-side sampler over ``[rows, vocab]`` float32 logits."""
+    """Device-side sampler over ``[rows, vocab]`` float32 logits.  The per-row parameters of a
+    temperature step travel in one copy from a small ring of pinned host buffers (a buffer is
+    written again only after the copy that read it has finished), so a step allocates nothing."""
+
+    RING = 4
 
     def __init__(self, ops, device, max_rows: int = 1024):
         self.ops = ops
         self.device = torch.device(device)
-        self.max_rows = max_rows
-        self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
+        self.max_rows = 0
+        self._turn = 0
+        self._grow(max_rows)
 
     def _grow(self, n: int) -> None:
-        if n > self.max_rows:
-            self.max_rows = n
-            self._out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if n <= self.max_rows:
+            return
+        self.max_rows = n
+        pin = self.device.type == "cuda"
+        self._out = torch.empty(n, dtype=torch.int32, device=self.device)
+        # rows of the parameter block: temperatures (float32, at the row's start), seeds, requests, steps
+        self._dev = torch.empty((4, n), dtype=torch.int64, device=self.device)
+        self._host = [torch.zeros((4, n), dtype=torch.int64, pin_memory=pin) for _ in range(self.RING)]
+        self._host_np = [h.numpy() for h in self._host]
+        self._events = [None] * self.RING
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
         n = logits.shape[0]
@@ -76,14 +88,27 @@ class Sampler:
                request_ids: Sequence[int], steps: Sequence[int]) -> torch.Tensor:
         """One token per row; rows with temperature 0 are greedy.  Returns int32 on the device
         (scratch: overwritten by the next call)."""
+        import numpy as np
         n = logits.shape[0]
         self._grow(n)
         out = self._out[:n]
         if all(t == 0.0 for t in temperatures):
             self.ops.argmax(logits, out)
             return out
-        temp = torch.tensor(list(temperatures), dtype=torch.float32).to(self.device, non_blocking=True)
-        meta = torch.tensor([[s - (1 << 64) if s >= (1 << 63) else s for s in seeds], list(request_ids), list(steps)],
-                            dtype=torch.int64).to(self.device, non_blocking=True)
-        self.ops.sample(logits, temp, meta[0], meta[1], meta[2], out)
+        r = self._turn
+        self._turn = (r + 1) % self.RING
+        if self._events[r] is not None:
+            self._events[r].synchronize()
+        a = self._host_np[r]
+        a[0].view(np.float32)[:n] = np.asarray(temperatures, dtype=np.float32)      # the row's first n floats
+        a[1, :n] = [s - (1 << 64) if s >= (1 << 63) else s for s in seeds]
+        a[2, :n] = request_ids
+        a[3, :n] = steps
+        self._dev[:, :n].copy_(self._host[r][:, :n], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = self._events[r] or torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._events[r] = ev
+        temp = self._dev[0].view(torch.float32)[:n]
+        self.ops.sample(logits, temp, self._dev[1, :n], self._dev[2, :n], self._dev[3, :n], out)
         return out

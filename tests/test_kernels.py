@@ -37,6 +37,14 @@ def test_embed(ops, dtype):
     out = torch.empty(5, 72, device=DEV)
     ops.embed(toks, table, out)
     assert torch.equal(out, table[toks.long()].float())
+    if dtype == torch.bfloat16:
+        # the same rows from the table stored as tiles (what a tied head keeps): one copy serves both
+        for rows, cols in ((301, 72), (1000, 200), (128, 64)):
+            t2 = torch.randn(rows, cols, device=DEV).to(dtype)
+            ids = torch.tensor([0, rows - 1, 127 % rows, 128 % rows, 5], dtype=torch.int32, device=DEV)
+            o2 = torch.empty(5, cols, device=DEV)
+            ops.embed(ids, ops.pack_weight(t2), o2)
+            assert torch.equal(o2, t2[ids.long()].float())
 
 
 @pytest.mark.parametrize("hidden,eps,offset", [(72, 1e-5, 0.0), (1000, 1e-6, 1.0), (4096, 1e-5, 0.0)])

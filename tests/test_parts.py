@@ -156,7 +156,10 @@ def test_feed_forward_embedding_and_head_parts(ctx, dtype):
     assert torch.equal(x, table[[300, 0, 7, 7]].float())
     head = HEADS.build(PartSpec("lm_head", {"vocab_size": 301, "hidden_size": 72, "tied": True}), c)
     assert head.params()[0].optional and head.params()[0].absolute
-    head.tie(emb.weight)
+    stored = head.tie(emb.weight)
+    emb.share(stored)                                   # one copy of the table serves both
+    emb.forward(torch.tensor([300, 0, 7, 7], dtype=torch.int32, device=DEV), x)
+    assert torch.equal(x, table[[300, 0, 7, 7]].float())
     hn = torch.randn(4, 72, device=DEV).to(dtype)
     logits = torch.empty(4, 301, device=DEV)
     head.forward(hn, logits)
