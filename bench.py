@@ -349,8 +349,7 @@ def timeline_table(llm, batch, context, steps=8):
     seqs = open_filled(llm, batch, context - steps - 8)
 
     def one(k):
-        lg = eng.step([StepEntry(s, [(7 * k + b) % 1000], [0]) for b, s in enumerate(seqs)])
-        llm.sampler.greedy(lg)
+        eng.step([StepEntry(s, [(7 * k + b) % 1000], [0]) for b, s in enumerate(seqs)], greedy=True)
 
     ops.call_log = []
     one(0)                                   # the first step runs eagerly: its calls name the kernels
@@ -484,6 +483,9 @@ def main() -> int:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--shape", choices=("8b", "3b", "1b"), default="8b",
+                    help="layer sizes of the steady-decode line and of --timeline (default: the 8B shape of the contract)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each sequence's cache holds while decoding")
     ap.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16",
                     help="float32: the true 32-bit path (FP32-pipe products, general attention), a line of its own; "
                          "give --layers to keep it short")
@@ -509,7 +511,9 @@ def main() -> int:
     import hilbert_pruned_8b_b200 as hb
     from hilbert_pruned_8b_b200.api import LLM
 
-    cfg_dict = dict(MODEL_8B)
+    cfg_dict = dict({"8b": MODEL_8B, "3b": MODEL_3B, "1b": MODEL_1B}[a.shape])
+    shape_name = {"8b": "llama-3.1-8b-shaped", "3b": "llama-3.2-3b-shaped", "1b": "llama-3.2-1b-shaped"}[a.shape]
+    context = a.context
     full_layers = cfg_dict["num_hidden_layers"]
     layers = a.layers or full_layers
     cfg_dict["num_hidden_layers"] = layers
@@ -519,7 +523,7 @@ def main() -> int:
     if fp32:
         a.skip_points = True            # the other points are about the serving precision
     max_batch = 64 if not a.skip_points else a.batch
-    max_tokens = max_batch * CONTEXT
+    max_tokens = max(max_batch * ((context + 127) // 64 * 64), 64 * 1024 if not a.skip_points else 0, PREFILL_TOKENS)
     t_build = time.time()
     llm = LLM.random(cfg, seed=0, dtype=a.dtype, max_tokens=max_tokens, device=0, max_batch=max_batch,
                      max_step_tokens=PREFILL_TOKENS)
@@ -528,15 +532,15 @@ def main() -> int:
     build_s = time.time() - t_build
 
     if a.timeline:
-        return timeline_table(llm, a.batch, CONTEXT)
+        return timeline_table(llm, a.batch, context)
     prefill_ms = time_prefill(llm, PREFILL_TOKENS)
     pf = prefill_flops(cfg_dict, layers, PREFILL_TOKENS)
-    ms, launches, step_bytes, clocks = time_decode(llm, a.batch, a.steps, a.warmup, CONTEXT, ClockSampler())
-    e2e, h2d, d2h = time_e2e(llm, a.batch, a.steps, a.warmup, CONTEXT)
+    ms, launches, step_bytes, clocks = time_decode(llm, a.batch, a.steps, a.warmup, context, ClockSampler())
+    e2e, h2d, d2h = time_e2e(llm, a.batch, a.steps, a.warmup, context)
     points = {}
     if not a.skip_points:
         for b in (1, 64):
-            pms, _, pbytes, _ = time_decode(llm, b, max(4, a.steps // 2), 3, CONTEXT)
+            pms, _, pbytes, _ = time_decode(llm, b, max(4, a.steps // 2), 3, context)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
             points[f"decode_b{b}_frac"] = round(pbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         # prefill at other lengths (cut into steps of 2048 tokens): tokens/s
@@ -555,16 +559,16 @@ def main() -> int:
     # (148 SMs x 128 lanes x 2 flop x 1.965 GHz), not of the tensor cores'
     flop_peak = 148 * 128 * 2 * 1.965e9 if fp32 else pk["bf16_tflops"] * 1e12
     line = {
-        "metric": f"decode tok/s @ batch {a.batch}, context 8192 (Llama-3.1-8B-shaped, random weights)"
-                  + (", true 32-bit path" if fp32 else ""),
+        "metric": f"decode tok/s @ batch {a.batch}, context {context} ({shape_name.replace('llama', 'Llama').replace('b-shaped', 'B-shaped')}, "
+                  "random weights)" + (", true 32-bit path" if fp32 else ""),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32" if fp32 else "bf16", "data": "synthetic: random weights, random token ids, random cache contents",
         "impl": "ours",
-        "config": {"model": "llama-3.1-8b-shaped", "layers": layers, "layers_in_config": full_layers,
+        "config": {"model": shape_name, "layers": layers, "layers_in_config": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "global_batch": a.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
+                   "global_batch": a.batch, "seq_len": context, "prefill_tokens": PREFILL_TOKENS,
                    "parallelism": "single-gpu", "l2": "weights (15 GB) exceed L2; every step reads them from HBM",
                    "peaks": pk_src, "hbm_gbs_peak": pk["hbm_gbs"], "bf16_tflops_peak": pk["bf16_tflops"]},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

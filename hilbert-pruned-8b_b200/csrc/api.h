@@ -77,7 +77,8 @@ int hb_attention_prefill_tc(const void* q, long long q_stride, long long n_token
 // out[i] = mean + stdev * N(0, 1): element i of the counter-based stream `base`
 int hb_random_normal(void* out, int out_dtype, long long n, unsigned long long base, float stdev, float mean,
                      void* stream);
-int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, int* status, void* stream);
+int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, int parts, void* scratch,
+              int* counters, int* status, void* stream);
 int hb_sample(const float* logits, long long stride, const float* temperature, const long long* seeds,
               const long long* request_ids, const long long* steps, int* out, int n_rows, int vocab, int* status,
               void* stream);

@@ -96,21 +96,51 @@ __device__ __forceinline__ void argmax_row(const float* __restrict__ row, int vo
     *out_max = sval[32];
 }
 
+// Greedy pick.  A row of a vocabulary-sized logit vector is half a megabyte: one block per row
+// leaves most SMs idle for a small batch, so a row is cut into `parts` ranges (grid: parts x
+// rows).  Each block leaves (maximum, index) of its range in scratch; the last block of a row to
+// finish (a counter per row, left at zero) takes the best of them, lowest index on ties.
 __global__ void __launch_bounds__(SM_THREADS)
-argmax_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ out, int vocab, int* status) {
+argmax_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ out, int vocab, int chunk,
+              float* part_val, int* part_idx, int* counters, int* status) {
     pdl_trigger();
     pdl_wait();
     logits = pdl_fresh(logits);
     __shared__ float sval[33];
     __shared__ int sidx[33];
-    int idx;
-    float mx;
-    bool nonfinite;
-    argmax_row(logits + (size_t)blockIdx.x * stride, vocab, &idx, &mx, sval, sidx, &nonfinite);
+    __shared__ int is_last;
+    const int part = blockIdx.x, parts = gridDim.x, r = blockIdx.y;
+    const int begin = min(part * chunk, vocab), n = min(chunk, vocab - begin);
+    int idx = 0;
+    float mx = -INFINITY;
+    bool nonfinite = false;
+    if (n > 0) argmax_row(logits + (size_t)r * stride + begin, n, &idx, &mx, sval, sidx, &nonfinite);
+    idx += begin;
+    // the reference fails a row whose logits are not finite (engine.c:29-31)
+    if (threadIdx.x == 0 && nonfinite) hb_note(status, HB_STATUS_NONFINITE, 1 + r);
+    if (parts == 1) {
+        if (threadIdx.x == 0) out[r] = idx;
+        return;
+    }
     if (threadIdx.x == 0) {
-        out[blockIdx.x] = idx;
-        // the reference fails a row whose logits are not finite (engine.c:29-31)
-        if (nonfinite) hb_note(status, HB_STATUS_NONFINITE, 1 + (int)blockIdx.x);
+        part_val[(size_t)r * parts + part] = n > 0 ? mx : -INFINITY;
+        part_idx[(size_t)r * parts + part] = idx;
+        __threadfence();
+        const int prev = atomicAdd(counters + r, 1);
+        is_last = prev == parts - 1;
+        if (is_last) counters[r] = 0;                  // ready for the next launch
+    }
+    __syncthreads();
+    if (is_last && threadIdx.x == 0) {
+        __threadfence();
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int p = 0; p < parts; p++) {              // ranges in index order: the first maximum wins a tie
+            const float v = __ldcg(part_val + (size_t)r * parts + p);
+            const int i = __ldcg(part_idx + (size_t)r * parts + p);
+            if (v > best) { best = v; bi = i; }
+        }
+        out[r] = bi == 0x7fffffff ? 0 : bi;
     }
 }
 
@@ -177,10 +207,20 @@ sample_kernel(const float* __restrict__ logits, long long stride, const float* _
     if (tid == 0) out[r] = (chosen == 0x7fffffff) ? amax : chosen;  // rounding left no interval: the mode
 }
 
-extern "C" int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, int* status, void* stream) {
+// `scratch` (2 * rows * parts 32-bit words) and `counters` (one int per row, zero before the first
+// use; left at zero) let a row be cut into `parts` ranges; without them parts is 1.
+extern "C" int hb_argmax(const float* logits, long long stride, int* out, int n_rows, int vocab, int parts, void* scratch,
+                         int* counters, int* status, void* stream) {
     if (n_rows == 0) return 0;
     HB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
-    hb_launch(argmax_kernel, dim3(n_rows), dim3(SM_THREADS), 0, (cudaStream_t)stream, logits, stride, out, vocab, status);
+    HB_REQUIRE(n_rows <= 65535, "argmax: too many rows for one launch");
+    if (parts < 1 || scratch == nullptr || counters == nullptr) parts = 1;
+    int chunk = ((vocab + parts - 1) / parts + 3) & ~3;          // ranges start on 16 bytes when the row does
+    parts = (vocab + chunk - 1) / chunk;
+    float* part_val = (float*)scratch;
+    int* part_idx = (int*)scratch + (size_t)n_rows * parts;
+    hb_launch(argmax_kernel, dim3(parts, n_rows), dim3(SM_THREADS), 0, (cudaStream_t)stream, logits, stride, out, vocab, chunk,
+              part_val, part_idx, counters, status);
     return hb_check_launch("argmax");
 }
 

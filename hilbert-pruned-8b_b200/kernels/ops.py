@@ -51,7 +51,7 @@ _SIGNATURES = {
     "hb_attention_prefill_tc": [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_random_normal": [_c_ptr, _c_int, _c_ll, ctypes.c_ulonglong, _c_float, _c_float, _c_ptr],
-    "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
 }
 
@@ -192,6 +192,9 @@ class Ops:
         # split-K decode attention scratch: partial outputs with their maxima and sums
         self._decode_scratch = torch.empty(4 << 20, dtype=torch.float32, device=self.device)
         self._decode_counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
+        # greedy pick: (maximum, index) of each range of a row, and a counter per row (kept zero)
+        self._argmax_scratch = torch.empty(2 * 1024 * self.ARGMAX_MAX_PARTS, dtype=torch.int32, device=self.device)
+        self._argmax_counters = torch.zeros(1024, dtype=torch.int32, device=self.device)
         self._retired = []              # outgrown scratch, kept alive for graphs that captured it
         self._splits_cache = {}
         self.use_tcgen05_attention = True   # head size 128 prefill on tcgen05 (else the mma.sync kernel)
@@ -362,6 +365,7 @@ class Ops:
         self.status.zero_()
         self._splitk_counters.zero_()
         self._decode_counters.zero_()
+        self._argmax_counters.zero_()
 
     def check_errors(self) -> None:
         """Reads the device status words (this synchronises) and raises if a kernel noted a fault."""
@@ -577,12 +581,22 @@ class Ops:
         self.launches += 1
 
     # ------------------------------------------------------------------ sampling
+    ARGMAX_MAX_PARTS = 16
+
     def argmax(self, logits, out) -> None:
+        """``out[r]`` = index of the largest value of row r (the lowest index on ties).  A row is cut
+        over several blocks when there are fewer rows than the device has room for."""
         self._dev(logits, out)
-        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() != logits.shape[0]:
+        n = logits.shape[0]
+        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() != n:
             raise KernelError("argmax: float32 logits and one int32 per row expected")
-        self._call("hb_argmax", logits.data_ptr(), _rows(logits, "logits"), out.data_ptr(), logits.shape[0],
-                   logits.shape[1], self.status.data_ptr(), self._stream())
+        parts = max(1, min(self.ARGMAX_MAX_PARTS, (2 * self.sm_count) // max(n, 1), logits.shape[1] // 4096))
+        if n > self._argmax_counters.numel():
+            self._retired += [self._argmax_counters, self._argmax_scratch]      # a captured graph may still use them
+            self._argmax_counters = torch.zeros(n, dtype=torch.int32, device=self.device)
+            self._argmax_scratch = torch.empty(2 * n * self.ARGMAX_MAX_PARTS, dtype=torch.int32, device=self.device)
+        self._call("hb_argmax", logits.data_ptr(), _rows(logits, "logits"), out.data_ptr(), n, logits.shape[1], parts,
+                   self._argmax_scratch.data_ptr(), self._argmax_counters.data_ptr(), self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def sample(self, logits, temperature, seeds, request_ids, steps, out) -> None:

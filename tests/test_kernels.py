@@ -636,6 +636,31 @@ def test_argmax_lowest_index_on_ties(ops, vocab):
     assert out.tolist() == want
 
 
+@pytest.mark.parametrize("rows", [1, 8, 40, 300])
+def test_argmax_rows_cut_over_several_blocks(ops, rows):
+    """With few rows each row is cut into ranges for several blocks (the last one to finish takes
+    the best of them): the lowest index still wins a tie across ranges, the counters come back
+    to zero (twice in a row), rows whose storage is not 16-byte aligned work too."""
+    torch.manual_seed(13 + rows)
+    vocab = 128256
+    lg = torch.randn(rows, vocab, device=DEV)
+    lg[0, 100000] = lg[0, 20] = lg[0, 64200] = 30.0             # a tie across ranges
+    if rows > 1:
+        lg[1, vocab - 1] = 31.0
+        lg[rows - 1] = -5.0                                        # a constant row: index 0
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        out.fill_(-1)
+        ops.argmax(lg, out)
+        assert out[0].item() == 20 and torch.equal(out[1:].long(), lg[1:].argmax(dim=1))
+        assert int(ops._argmax_counters.abs().sum()) == 0
+    odd = torch.randn(3, vocab + 3, device=DEV)[:, 3:]
+    out3 = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax(odd, out3)
+    assert torch.equal(out3.long(), odd.argmax(dim=1))
+    assert ops.status.tolist() == [0, 0, 0, 0]
+
+
 @pytest.mark.parametrize("vocab", [11, 384, 50257])
 def test_temperature_sampling_follows_the_cdf(ops, vocab):
     from hilbert_pruned_8b_b200.sampling import uniform_from

@@ -92,6 +92,8 @@ def _batches(sizes, seed):
             prompt = int(torch.randint(1, 41, (1,), generator=g))
             if i == 0:
                 prompt = 70                              # one prompt over a page
+            if i == 1:
+                prompt = 600                             # and one over many: decode attention cuts its keys into several splits
             new = 4 + int(torch.randint(0, 7, (1,), generator=g))
             rid = f"b{b}r{i}"
             reqs[rid] = [int(t) for t in torch.randint(0, VOCAB, (prompt + new,), generator=g)]
