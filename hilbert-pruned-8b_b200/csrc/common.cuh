@@ -258,6 +258,13 @@ __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, 
 
 // silu(z) = z / (1 + exp(-z))  (cleanroom-transformer/src/ops_common.h:56)
 __device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
+// The same from the hardware's exp2 and reciprocal (relative error about 2^-21): for results
+// that are rounded to bfloat16 at once.  Very negative z gives -0, not NaN: exp2 overflows to +inf and z / inf = -0.
+__device__ __forceinline__ float silu_fast(float z) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * z));
+    return __fdividef(z, 1.0f + e);
+}
 
 // Address of token position `pos` of kv head `g` in a paged cache layer
 // [pages][kv_heads][HB_PAGE_TOKENS][head_dim]; `page` is the physical page.

@@ -74,6 +74,22 @@ int tc_make_map(CUtensorMap* map, const void* base, long long rows, long long co
     return 0;
 }
 
+int tc_make_out_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows, long long cols, long long ld,
+                    int box_rows, int box_cols) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return hb_fail("gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return hb_fail("gemm_tc: output tensor map encode failed with code %d (rows %lld cols %lld ld %lld)", (int)r, rows, cols, ld);
+    return 0;
+}
+
 // The map of a weight matrix: row-major [rows, K] with row stride ld, or packed tiles, which
 // read as a matrix of 64-column rows (ceil(rows / 128) * ceil(K / 64) * 128 of them).
 int tc_make_weight_map(CUtensorMap* map, const void* w, long long rows, long long K, long long ld, int box_rows, int packed) {
@@ -226,7 +242,9 @@ static int dispatch_bn(int bn, bool cluster, int mode, const CUtensorMap& mw, co
 }
 
 // mode: 0 store bf16, 1 store f32, 2 add into f32, 3 silu(gate) * up -> bf16 (W holds the gate
-// rows [0, N) and the up rows [up_row0, up_row0 + N)).  `partials` and `tile_counters` are the
+// rows [0, N) and the up rows [up_row0, up_row0 + N); up_row0 = -1: W holds them in bands of 128
+// rows, the gate rows of features 64 b .. 64 b + 63 followed by their up rows, which a tile
+// reads as one box instead of two).  `partials` and `tile_counters` are the
 // scratch described above (capacities in floats and ints); `error_flag` is a device int the
 // kernel sets when a wait ran out.  `packed`: W is stored as contiguous 128 x 64 tiles (see
 // tc_w_coords; w_rows is then the number of rows before padding and ldw is not used).
@@ -241,9 +259,12 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
     HB_REQUIRE(lda % 8 == 0 && (packed || ldw % 8 == 0), "gemm_tc: row strides %lld and %lld must be multiples of 8 elements", lda, ldw);
     HB_REQUIRE(lda >= K && (packed || ldw >= K) && ldc >= N, "gemm_tc: a row stride is smaller than its row");
     HB_REQUIRE(!packed || N <= w_rows, "gemm_tc: %d output features from a packed matrix of %lld rows", N, w_rows);
-    HB_REQUIRE(!packed || mode != TC_SWIGLU_BF16 || up_row0 % 64 == 0, "gemm_tc: packed up rows must start at a multiple of 64");
+    HB_REQUIRE(!packed || mode != TC_SWIGLU_BF16 || up_row0 % 64 == 0 || up_row0 == -1, "gemm_tc: packed up rows must start at a multiple of 64");
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 >= -1, "gemm_tc: up rows start at %d", up_row0);
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 != -1 || (N % 64 == 0 && 2LL * N <= w_rows),
+               "gemm_tc: [gate; up] in bands needs a multiple of 64 features and both halves in the matrix");
     HB_REQUIRE(error_flag != nullptr, "gemm_tc: no error flag");
-    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 + N <= w_rows, "gemm_tc: up rows lie outside the weight matrix");
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 < 0 || up_row0 + N <= w_rows, "gemm_tc: up rows lie outside the weight matrix");
     HB_REQUIRE(mode != TC_SWIGLU_BF16 || (ldc % 8 == 0 && ((uintptr_t)out & 15) == 0),
                "gemm_tc: the SwiGLU output needs 16-byte aligned rows");
     const TcPlan pl = make_plan(M, N, K, mode, schedule);
@@ -252,7 +273,7 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
                    "gemm_tc: stream-K needs %lld scratch floats and %lld counters", pl.scratch_floats, pl.tiles);
     }
     CUtensorMap mw, ma;
-    if (tc_make_weight_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM, packed)) return 1;
+    if (tc_make_weight_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 && up_row0 >= 0 ? 64 : TC_BM, packed)) return 1;
     if (tc_make_map(&ma, a, M, K, lda, pl.bn)) return 1;
     TcParams prm;
     prm.out = out;

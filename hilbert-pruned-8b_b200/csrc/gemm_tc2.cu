@@ -9,16 +9,30 @@
 // work in the single-CTA kernel: the single-CTA kernel is bound by the bytes it pulls from L2
 // at this tile size, this one is not.  No multicast loads: each CTA loads its own halves.
 //
-// Per CTA, 192 threads, as in the single-CTA kernel:
+// Per CTA, 320 threads:
 //   warp 0     TMA producer (both CTAs): own weight rows and own token half into own shared
-//              memory; the bytes of both CTAs are counted on the LEADER's full[s]
+//              memory; the bytes of both CTAs are counted on the LEADER's full[s].  What this
+//              one thread does per K block is on the pipeline's critical path: the tile's
+//              coordinates are computed once per tile, not per K block (with two integer
+//              divisions per K block the whole kernel was 15 % slower)
 //   warp 1     tensor memory owner (both CTAs allocate together); in the leader one thread
 //              issues the MMAs and commits to empty[s] / acc_full[buffer] of BOTH CTAs
-//   warps 2-5  epilogue (both CTAs) on their own accumulator rows; they hand a buffer back by
-//              arriving on the LEADER's acc_empty[buffer] (256 arrivals)
-// Work: whole 256 x 256 tiles round-robin over the pairs (persistent), token tiles fastest so
-// that neighbouring pairs share a weight tile in L2.  Epilogues as in the single-CTA kernel
-// (store, residual add, SwiGLU with 64 gate + 64 up rows per CTA).
+//   warps 2-9  epilogue (both CTAs), two teams of four warps (a warp reads one quarter of the
+//              tensor memory's lanes) that take turns on pieces of 16 or 32 tokens of their own
+//              accumulator rows: registers -> shared memory laid out as the output's rows ->
+//              ONE tile store (cp.async.bulk.tensor, or cp.reduce...add for the residual add,
+//              where the memory side adds) per piece.  Stores of full lines, nothing waits for
+//              a load: a 128 x 256 half tile leaves in 5 to 9 us, against 11 to 24 us with one
+//              element per thread and store (bfloat16 stores of 64 bytes per warp, residual
+//              loads whose round trips serialise).  They hand a buffer back by arriving on the
+//              LEADER's acc_empty[buffer] (512 arrivals)
+// Work: whole 256 x 256 tiles round-robin over the pairs (persistent), in the order of
+// t2_tile_coords.  Epilogues: store, residual add, SwiGLU with 64 gate + 64 up rows per CTA.
+//
+// Measured and left out: tiles of 512 tokens (two MMAs of 256 tokens per K step, 48 KB per
+// stage, 0.75 of the bytes per flop): the one accumulator pair fills the tensor memory, so the
+// epilogue is not hidden, and its K loop needs 0.82 us per block against 2 x 0.375 us: slower
+// at every size of the 8B shape from 1024 to 8192 tokens.
 //
 // Every wait is bounded; a wait that runs out sets *error_flag and both CTAs drain and leave.
 #include "api.h"
@@ -26,6 +40,7 @@
 
 #define T2_TOKENS 256          // tokens per pair tile (MMA N)
 #define T2_HALF 128            // tokens loaded by each CTA
+#define T2_GROUP_TILES 8       // token tiles (2048 tokens) that are walked together (t2_tile_coords)
 #define T2_STAGE_BYTES (TC_BM * TC_BK * 2 + T2_HALF * TC_BK * 2)     // 32 KB per CTA and stage
 // 6 stages of 32 KB; a 7th (measured) changes nothing, and asking L2 ahead for the weight tiles
 // of later K blocks (cp.async.bulk.prefetch) made the kernel slower.  Cutting the tiles of the
@@ -40,20 +55,50 @@
 // for the qkv product against 82 us: with six stages the chain stage free -> copies -> barrier
 // -> forwarder -> MMA is twice as long as TMA's.  (A loader thread that arrives remotely
 // itself waits, with the release, for all its copies in flight: 261 us.)
-#define T2_STAGES(MODE) 6
-// SwiGLU epilogue: gates and ups handed over [2][32][64] float32, products [64][64] bfloat16
-#define T2_XCHG_BYTES (2 * 32 * 64 * 4 + 64 * 64 * 2)
+#define T2_STAGES 6
+// Warp 0 loads, warp 1 issues the MMAs, warps 2-9 are two epilogue teams of four warps (one warp
+// per quarter of the tensor memory's lanes in each).
+#define T2_THREADS 320
+// Shared memory of the epilogue: 16 KB per team.  Tile stores: two buffers of 8 KB ([16 tokens]
+// [128 features] float32, or [32][128] bfloat16); SwiGLU: gates and ups handed over [2][16][64]
+// float32, then two buffers [32 tokens][64 features] bfloat16.  The path of plain stores uses
+// the first team's and the start of the second's ([2][32][64] float32 + [64][64] bfloat16).
+#define T2_TEAM_BYTES (16 * 1024)
+#define T2_XCHG_BYTES (2 * T2_TEAM_BYTES)
 
-template <int MODE, int STAGES>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
+// Tile t of the persistent loop -> token tile tm, feature tile tn.  The token tiles come in
+// groups of p.group_m; inside a group the token tiles run fastest (neighbouring pairs share a
+// weight tile in L2), then the feature tiles, then the next group: the activations of a group
+// (2048 tokens) stay in L2 while the weights stream past them, instead of all activations being
+// read again for every few weight tiles (8192 tokens x 4096: 67 MB per wave of tiles).
+__device__ __forceinline__ void t2_tile_coords(const TcParams& p, int t, int& tm, int& tn) {
+    const int per_group = p.group_m * p.tiles_n, full = p.tiles_m / p.group_m;
+    const int g = t / per_group;
+    if (g < full) {
+        const int local = t - g * per_group;
+        tm = g * p.group_m + local % p.group_m;
+        tn = local / p.group_m;
+    } else {
+        const int rest = p.tiles_m - full * p.group_m, local = t - full * per_group;
+        tm = full * p.group_m + local % rest;
+        tn = local / rest;
+    }
+}
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                const __grid_constant__ CUtensorMap map_o, const TcParams p, const int tma_out) {
     constexpr bool SWIGLU = MODE == TC_SWIGLU_BF16;
+    constexpr int STAGES = T2_STAGES;
+    constexpr int STAGE_BYTES = T2_STAGE_BYTES;
+    constexpr int TOKENS = T2_TOKENS;
     constexpr int FEAT = SWIGLU ? 64 : TC_BM;                     // output features per CTA
     constexpr int W_BYTES = TC_BM * TC_BK * 2;
-    constexpr int XCHG = SWIGLU ? T2_XCHG_BYTES : 0;
+    constexpr int XCHG = T2_XCHG_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* xchg = smem + STAGES * T2_STAGE_BYTES;
+    uint8_t* xchg = smem + STAGES * STAGE_BYTES;
     uint64_t* bars = (uint64_t*)(xchg + XCHG);                    // full[S], empty[S], acc_full[2], acc_empty[2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -74,7 +119,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(accf0 + 8 * b, 1);
-            mbar_init(acce0 + 8 * b, 256);
+            mbar_init(acce0 + 8 * b, 2 * (T2_THREADS - 64));       // every epilogue thread of both CTAs
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -93,36 +138,39 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            auto load_w = [&](int s, int t, int kb) {
-                const int n0 = (t / p.tiles_m) * (2 * FEAT) + (int)rank * FEAT;
-                const uint32_t stage = smem_base + s * T2_STAGE_BYTES;
+            // tile coordinates once per tile: this thread's time per K block is the pipeline's
+            auto load_w = [&](int s, int tn, int kb) {
+                const int n0 = tn * (2 * FEAT) + (int)rank * FEAT;
+                const uint32_t stage = smem_base + s * STAGE_BYTES;
                 int x, y;
-                tc_w_coords(p, n0, kb, x, y);
+                tc_w_coords(p, SWIGLU && p.up_row0 < 0 ? 2 * n0 : n0, kb, x, y);       // up_row0 < 0: [gate; up] in bands, one box
                 tma_load_2d_pair(stage, &map_w, lead_full0 + 8 * s, x, y);
-                if (SWIGLU) {
+                if (SWIGLU && p.up_row0 >= 0) {
                     tc_w_coords(p, p.up_row0 + n0, kb, x, y);
                     tma_load_2d_pair(stage + W_BYTES / 2, &map_w, lead_full0 + 8 * s, x, y);
                 }
             };
-            auto load_a = [&](int s, int t, int kb) {
-                tma_load_2d_pair(smem_base + s * T2_STAGE_BYTES + W_BYTES, &map_a, lead_full0 + 8 * s, kb * TC_BK,
-                                 (t % p.tiles_m) * T2_TOKENS + (int)rank * T2_HALF);
+            auto load_a = [&](int s, int tm, int kb) {
+                tma_load_2d_pair(smem_base + s * STAGE_BYTES + W_BYTES, &map_a, lead_full0 + 8 * s, kb * TC_BK,
+                                 tm * TOKENS + (int)rank * T2_HALF);
             };
             // weights first: no kernel of a step writes them, so they are requested before
             // waiting for the kernel in front
-            int early = 0;
+            int early = 0, tm = 0, tn = 0;
             if (pair < tiles) {
+                t2_tile_coords(p, pair, tm, tn);
                 early = min(p.kb_total, STAGES);
                 for (int j = 0; j < early; j++) {
-                    if (rank == 0) mbar_expect_tx(full0 + 8 * j, 2 * T2_STAGE_BYTES);
-                    load_w(j, pair, j);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * j, 2 * STAGE_BYTES);
+                    load_w(j, tn, j);
                 }
             }
             pdl_wait();
-            for (int j = 0; j < early; j++) load_a(j, pair, j);
+            for (int j = 0; j < early; j++) load_a(j, tm, j);
             int g = 0;
             bool alive = true;
             for (int t = pair; t < tiles && alive; t += n_pairs) {
+                t2_tile_coords(p, t, tm, tn);
                 for (int kb = 0; kb < p.kb_total; kb++, g++) {
                     if (g < early) continue;
                     const int s = g % STAGES;
@@ -132,9 +180,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         alive = false;
                         break;
                     }
-                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * T2_STAGE_BYTES);
-                    load_w(s, t, kb);
-                    load_a(s, t, kb);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                    load_w(s, tn, kb);
+                    load_a(s, tm, kb);
                 }
             }
             // the copies into THIS CTA's shared memory must land before it may exit.  Their bytes
@@ -151,7 +199,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             constexpr uint32_t idesc = instr_desc_bf16_mn(256, T2_TOKENS);
             const uint64_t desc0 = smem_desc_sw128(smem_base);
             const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
-            constexpr uint32_t STAGE_STEP = T2_STAGE_BYTES >> 4, A_OFF = W_BYTES >> 4;
+            constexpr uint32_t STAGE_STEP = STAGE_BYTES >> 4, A_OFF = W_BYTES >> 4;
             int s = 0, item = 0;
             uint32_t ph = 0;
             bool alive = true;
@@ -163,7 +211,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     break;
                 }
                 tc_fence_after();
-                const uint32_t acc_addr = tmem_base + buf * T2_TOKENS;
+                const uint32_t acc_addr = tmem_base + buf * TOKENS;
                 for (int kb = 0; kb < p.kb_total; kb++) {
                     if (!mbar_wait(full0 + 8 * s, ph)) {
                         atomicExch(p.error_flag, 13);
@@ -186,10 +234,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
         }
     } else {
-        // ---------------------------------------------------------------- epilogue
-        const int q = warp & 3;
+        // ---------------------------------------------------------------- epilogue: two teams of four warps
+        const int q = warp & 3;                                   // the quarter of the tensor memory's lanes this warp may read
+        const int team = (warp - 2) >> 2;
         const int row = q * 32 + lane;
-        const int et = (warp - 2) * 32 + lane;
+        const int et = ((warp - 2) & 3) * 32 + lane;              // thread of the team
+        const bool issuer = et == 0;                              // issues and tracks the team's tile stores
+        const int team_bar = 1 + team;
+        uint8_t* stage_mem = xchg + team * T2_TEAM_BYTES;
+        int issued = 0;                                           // tile stores of this team so far (chooses the buffer)
         pdl_wait();
         int item = 0;
         for (int t = pair; t < tiles; t += n_pairs, item++) {
@@ -201,94 +254,123 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             }
             if (*abort_flag) break;
             tc_fence_after();
-            const uint32_t lane_addr = tmem_base + buf * T2_TOKENS + ((uint32_t)(q * 32) << 16);
-            const int m0 = (t % p.tiles_m) * T2_TOKENS;
-            const int n0 = (t / p.tiles_m) * (2 * FEAT) + (int)rank * FEAT;
-            if (MODE == TC_ADD_F32) {
-                // residual add: 64 tokens at a time, all 64 old values requested before the first
-                // store (16 at a time the loads' round trips, 16 per tile, outlast a short K loop)
-                const int f = n0 + row;
+            const uint32_t lane_addr = tmem_base + buf * TOKENS + ((uint32_t)(q * 32) << 16);
+            int tm, tn;
+            t2_tile_coords(p, t, tm, tn);
+            const int m0 = tm * TOKENS;
+            const int n0 = tn * (2 * FEAT) + (int)rank * FEAT;
+            if (tma_out) {
+                // CH tokens at a time, the teams taking turns: accumulators -> registers -> shared
+                // memory laid out as the output's rows -> one tile store (or tile add) by the
+                // team's issuer.  Two buffers per team: a buffer is written again once the store
+                // before the last has read it.
+                constexpr int CH = MODE == TC_STORE_BF16 || SWIGLU ? 32 : 16;
 #pragma unroll 1
-                for (int c = 0; c < T2_TOKENS; c += 64) {
+                for (int c = team * CH; c < TOKENS; c += 2 * CH) {
                     if (m0 + c >= p.M) break;
-                    float v[4][16], r[4][16];
+                    const int b = issued & 1;
+                    issued++;
+                    if (issuer) bulk_wait_read<1>();
+                    asm volatile("bar.sync %0, 128;" ::"r"(team_bar) : "memory");
+                    if (SWIGLU) {
+                        // Rows 0..63 of this CTA's half tile are gate rows, rows 64..127 the up rows
+                        // of the same 64 features.  The gate threads hand the gates of tokens
+                        // 16..31 to the up threads and take the ups of tokens 0..15 from them, so
+                        // that all four warps share the activation.
+                        float* xf = (float*)stage_mem;                               // [2][16 tokens][64 features] float32
+                        bf16* yb = (bf16*)(stage_mem + 2 * 16 * 64 * 4) + b * (32 * 64);   // [32 tokens][64 features]
+                        const bool gate_thread = row < 64;
+                        const int f = row & 63;
+                        float v[2][16];
+                        tmem_ld16(lane_addr + c, v[0]);
+                        tmem_ld16(lane_addr + c + 16, v[1]);
+                        float* mine = xf + (gate_thread ? 0 : 16 * 64);
 #pragma unroll
-                    for (int u = 0; u < 4; u++) tmem_ld16(lane_addr + c + 16 * u, v[u]);
-                    if (f < p.N) {
-                        float* po = (float*)p.out + (size_t)(m0 + c) * p.ldc + f;
-#pragma unroll
-                        for (int u = 0; u < 4; u++)
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                r[u][j] = (m0 + c + 16 * u + j < p.M) ? __ldcg(po + (size_t)(16 * u + j) * p.ldc) : 0.0f;
-#pragma unroll
-                        for (int u = 0; u < 4; u++)
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (m0 + c + 16 * u + j < p.M) po[(size_t)(16 * u + j) * p.ldc] = r[u][j] + v[u][j];
-                    }
-                }
-            } else if (MODE == TC_SWIGLU_BF16) {
-                // 64 tokens at a time.  Rows 0..63 of this CTA's half tile are gate rows, rows
-                // 64..127 the up rows of the same 64 features.  The gate threads hand the gates
-                // of tokens 32..63 to the up threads and take the ups of tokens 0..31 from them
-                // (through shared memory), so that all four warps share the activation; the
-                // products go to shared memory as bfloat16 [token][feature] and leave with
-                // 16-byte stores.  Two block barriers per 64 tokens.
-                float* xf = (float*)xchg;                                  // [2][32 tokens][64 features] float32
-                bf16* yb = (bf16*)(xchg + 2 * 32 * 64 * 4);                // [64 tokens][64 features]
-                const bool gate_thread = row < 64;
-                const int f = row & 63;
-#pragma unroll 1
-                for (int c = 0; c < T2_TOKENS; c += 64) {
-                    if (m0 + c >= p.M) break;
-                    float v[4][16];
-#pragma unroll
-                    for (int u = 0; u < 4; u++) tmem_ld16(lane_addr + c + 16 * u, v[u]);
-                    // gates of tokens 32..63 -> xf[0], ups of tokens 0..31 -> xf[1]
-                    float* mine = xf + (gate_thread ? 0 : 32 * 64);
-#pragma unroll
-                    for (int u = 0; u < 2; u++)
-#pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            mine[(16 * u + j) * 64 + f] = gate_thread ? v[2 + u][j] : v[u][j];
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    const float* theirs = xf + (gate_thread ? 32 * 64 : 0);
-#pragma unroll
-                    for (int u = 0; u < 2; u++)
+                        for (int j = 0; j < 16; j++) mine[j * 64 + f] = gate_thread ? v[1][j] : v[0][j];
+                        asm volatile("bar.sync %0, 128;" ::"r"(team_bar) : "memory");
+                        const float* theirs = xf + (gate_thread ? 16 * 64 : 0);
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
-                            const float other = theirs[(16 * u + j) * 64 + f];
-                            const float y = gate_thread ? silu_f32(v[u][j]) * other : silu_f32(other) * v[2 + u][j];
-                            yb[((gate_thread ? 0 : 32) + 16 * u + j) * 64 + f] = __float2bfloat16_rn(y);
+                            const float other = theirs[j * 64 + f];
+                            const float y = gate_thread ? silu_fast(v[0][j]) * other : silu_fast(other) * v[1][j];
+                            yb[((gate_thread ? 0 : 16) + j) * 64 + f] = __float2bfloat16_rn(y);
                         }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                        fence_async_shared();
+                        asm volatile("bar.sync %0, 128;" ::"r"(team_bar) : "memory");
+                        if (issuer) {
+                            tma_store_2d(&map_o, smem_u32(yb), n0, m0 + c);
+                            bulk_commit();
+                        }
+                    } else if (MODE == TC_STORE_BF16) {
+                        bf16* yb = (bf16*)stage_mem + b * (32 * TC_BM);              // [32 tokens][128 features]
+                        float v[2][16];
+                        tmem_ld16(lane_addr + c, v[0]);
+                        tmem_ld16(lane_addr + c + 16, v[1]);
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const int idx = et + 128 * k, r = idx >> 3, ch = idx & 7;     // token of the group, 8-feature piece
-                        const int m = m0 + c + r, n = n0 + ch * 8;
-                        if (m < p.M && n < p.N) {
-                            bf16* o = (bf16*)p.out + (size_t)m * p.ldc + n;
-                            if (n + 8 <= p.N) {
-                                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(yb + r * 64 + ch * 8);
-                            } else {
-                                for (int e = 0; e < p.N - n; e++) o[e] = yb[r * 64 + ch * 8 + e];
-                            }
+                        for (int u = 0; u < 2; u++)
+#pragma unroll
+                            for (int j = 0; j < 16; j++) yb[(16 * u + j) * TC_BM + row] = __float2bfloat16_rn(v[u][j]);
+                        fence_async_shared();
+                        asm volatile("bar.sync %0, 128;" ::"r"(team_bar) : "memory");
+                        if (issuer) {
+                            tma_store_2d(&map_o, smem_u32(yb), n0, m0 + c);
+                            bulk_commit();
+                        }
+                    } else {
+                        float* yf = (float*)stage_mem + b * (16 * TC_BM);            // [16 tokens][128 features]
+                        float v[16];
+                        tmem_ld16(lane_addr + c, v);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) yf[j * TC_BM + row] = v[j];
+                        fence_async_shared();
+                        asm volatile("bar.sync %0, 128;" ::"r"(team_bar) : "memory");
+                        if (issuer) {
+                            if (MODE == TC_ADD_F32) tma_reduce_add_2d(&map_o, smem_u32(yf), n0, m0 + c);
+                            else tma_store_2d(&map_o, smem_u32(yf), n0, m0 + c);
+                            bulk_commit();
                         }
                     }
                 }
-            } else {
+            } else if (team == 0 && !SWIGLU) {
+                // An output whose rows a tile store cannot address (base, row stride or row length
+                // no multiple of 16 bytes): the first team writes the tile element by element.
+                if (MODE == TC_ADD_F32) {
+                    // residual add: 64 tokens at a time, all 64 old values requested before the first store
+                    const int f = n0 + row;
 #pragma unroll 1
-                for (int c = 0; c < T2_TOKENS; c += 16) {
-                    if (m0 + c >= p.M) break;
-                    float v[16];
-                    tmem_ld16(lane_addr + c, v);
-                    tc_emit_chunk<MODE>(p, m0, n0, c, v, xchg, q, row, et);
+                    for (int c = 0; c < TOKENS; c += 64) {
+                        if (m0 + c >= p.M) break;
+                        float v[4][16], r[4][16];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) tmem_ld16(lane_addr + c + 16 * u, v[u]);
+                        if (f < p.N) {
+                            float* po = (float*)p.out + (size_t)(m0 + c) * p.ldc + f;
+#pragma unroll
+                            for (int u = 0; u < 4; u++)
+#pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    r[u][j] = (m0 + c + 16 * u + j < p.M) ? __ldcg(po + (size_t)(16 * u + j) * p.ldc) : 0.0f;
+#pragma unroll
+                            for (int u = 0; u < 4; u++)
+#pragma unroll
+                                for (int j = 0; j < 16; j++)
+                                    if (m0 + c + 16 * u + j < p.M) po[(size_t)(16 * u + j) * p.ldc] = r[u][j] + v[u][j];
+                        }
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < TOKENS; c += 16) {
+                        if (m0 + c >= p.M) break;
+                        float v[16];
+                        tmem_ld16(lane_addr + c, v);
+                        tc_emit_chunk<MODE>(p, m0, n0, c, v, xchg, q, row, et);
+                    }
                 }
             }
             tc_fence_before();
             mbar_arrive_cluster(lead_acce0 + 8 * buf);
         }
+        if (issuer) bulk_wait_read<0>();                          // the stores must have read this CTA's shared memory
     }
     tc_fence_before();
     __syncthreads();
@@ -299,18 +381,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
 }
 
+constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + T2_XCHG_BYTES + (2 * T2_STAGES + 4) * 8 + 16 + 1024;
+static_assert(T2_SMEM_BYTES <= 227 * 1024, "tile pipeline does not fit shared memory");
+
 template <int MODE>
-static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int pairs, cudaStream_t s) {
-    constexpr int STAGES = T2_STAGES(MODE);
-    constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? T2_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
-    static_assert(SMEM <= 227 * 1024, "tile pipeline does not fit shared memory");
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<MODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& ma, const CUtensorMap& mo, const TcParams& prm, int tma_out, int pairs,
+                      cudaStream_t s) {
+    constexpr int SMEM = T2_SMEM_BYTES;
+    static bool attr_set[HB_MAX_DEVICES] = {};
+    const int slot = hb_device_slot();
+    if (!attr_set[slot]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return hb_fail("gemm_tc2: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
-        attr_set = true;
+        attr_set[slot] = true;
     }
-    cudaError_t e = hb_launch(gemm_tc2_kernel<MODE, STAGES>, dim3(2 * pairs), dim3(TC_THREADS), SMEM, s, mw, ma, prm);
+    cudaError_t e = hb_launch(gemm_tc2_kernel<MODE>, dim3(2 * pairs), dim3(T2_THREADS), SMEM, s, mw, ma, mo, prm, tma_out);
     if (e != cudaSuccess) return hb_fail("gemm_tc2: launch failed: %s", cudaGetErrorString(e));
     return hb_check_launch("gemm_tc2");
 }
@@ -319,34 +404,37 @@ static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& ma, const TcPara
 // leaves one without a partner): the persistent grid must not be larger.
 template <int MODE>
 static int query_pairs() {
-    constexpr int STAGES = T2_STAGES(MODE);
-    constexpr int SMEM = STAGES * T2_STAGE_BYTES + (MODE == TC_SWIGLU_BF16 ? T2_XCHG_BYTES : 0) + (2 * STAGES + 4) * 8 + 16 + 1024;
-    cudaFuncSetAttribute(gemm_tc2_kernel<MODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    constexpr int SMEM = T2_SMEM_BYTES;
+    cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     cudaLaunchConfig_t cfg = {};
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cfg.gridDim = dim3(sms & ~1);
-    cfg.blockDim = dim3(TC_THREADS);
+    cfg.blockDim = dim3(T2_THREADS);
     cfg.dynamicSmemBytes = SMEM;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc2_kernel<MODE, STAGES>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc2_kernel<MODE>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     return clusters < sms / 2 ? clusters : sms / 2;
 }
 static int resident_pairs(int mode) {
-    static int cached[4] = {-1, -1, -1, -1};
-    if (cached[mode] < 0) {
+    static int cached[HB_MAX_DEVICES][4];
+    static bool known[HB_MAX_DEVICES][4] = {};
+    const int slot = hb_device_slot();
+    int& c = cached[slot][mode];
+    if (!known[slot][mode]) {
         switch (mode) {
-            case TC_STORE_BF16: cached[mode] = query_pairs<TC_STORE_BF16>(); break;
-            case TC_STORE_F32: cached[mode] = query_pairs<TC_STORE_F32>(); break;
-            case TC_ADD_F32: cached[mode] = query_pairs<TC_ADD_F32>(); break;
-            default: cached[mode] = query_pairs<TC_SWIGLU_BF16>(); break;
+            case TC_STORE_BF16: c = query_pairs<TC_STORE_BF16>(); break;
+            case TC_STORE_F32: c = query_pairs<TC_STORE_F32>(); break;
+            case TC_ADD_F32: c = query_pairs<TC_ADD_F32>(); break;
+            default: c = query_pairs<TC_SWIGLU_BF16>(); break;
         }
+        known[slot][mode] = true;
     }
-    return cached[mode];
+    return c;
 }
 extern "C" int hb_gemm_tc2_resident_pairs(int mode) { return resident_pairs(mode & 3); }
 
@@ -367,11 +455,14 @@ extern "C" int hb_gemm_tc2(const void* a, long long lda, const void* w, long lon
     HB_REQUIRE(lda % 8 == 0 && (packed || ldw % 8 == 0), "gemm_tc2: row strides %lld and %lld must be multiples of 8 elements", lda, ldw);
     HB_REQUIRE(lda >= K && (packed || ldw >= K) && ldc >= N, "gemm_tc2: a row stride is smaller than its row");
     HB_REQUIRE(!packed || N <= w_rows, "gemm_tc2: %d output features from a packed matrix of %lld rows", N, w_rows);
-    HB_REQUIRE(!packed || mode != TC_SWIGLU_BF16 || up_row0 % 64 == 0, "gemm_tc2: packed up rows must start at a multiple of 64");
+    HB_REQUIRE(!packed || mode != TC_SWIGLU_BF16 || up_row0 % 64 == 0 || up_row0 == -1, "gemm_tc2: packed up rows must start at a multiple of 64");
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 >= -1, "gemm_tc2: up rows start at %d", up_row0);
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 != -1 || (N % 64 == 0 && 2LL * N <= w_rows),
+               "gemm_tc2: [gate; up] in bands needs a multiple of 64 features and both halves in the matrix");
     HB_REQUIRE(error_flag != nullptr, "gemm_tc2: no error flag");
-    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 + N <= w_rows, "gemm_tc2: up rows lie outside the weight matrix");
-    HB_REQUIRE(mode != TC_SWIGLU_BF16 || (ldc % 8 == 0 && ((uintptr_t)out & 15) == 0),
-               "gemm_tc2: the SwiGLU output needs 16-byte aligned rows");
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || up_row0 < 0 || up_row0 + N <= w_rows, "gemm_tc2: up rows lie outside the weight matrix");
+    HB_REQUIRE(mode != TC_SWIGLU_BF16 || (ldc % 8 == 0 && N % 8 == 0 && ((uintptr_t)out & 15) == 0),
+               "gemm_tc2: the SwiGLU output needs 16-byte aligned rows of a multiple of 8 features (the single-CTA kernel takes others)");
     const int feat = mode == TC_SWIGLU_BF16 ? 64 : TC_BM;
     TcParams prm;
     prm.out = out;
@@ -390,18 +481,30 @@ extern "C" int hb_gemm_tc2(const void* a, long long lda, const void* w, long lon
     prm.counters = nullptr;
     prm.error_flag = error_flag;
     prm.packed = packed ? 1 : 0;
+    prm.group_m = T2_GROUP_TILES;
     const long long tiles = (long long)prm.tiles_m * prm.tiles_n;
     int pairs = resident_pairs(mode);
     if (pairs < 1) return hb_fail("gemm_tc2: no CTA pair can be resident on this device");
     if (tiles < pairs) pairs = (int)tiles;
-    CUtensorMap mw, ma;
-    if (tc_make_weight_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 ? 64 : TC_BM, packed)) return 1;
+    // Tile stores need a 16-byte aligned base and row stride, and rows of a multiple of 16 bytes:
+    // a store that the tensor's edge cuts is cut at a 16-byte boundary, not at the last element
+    // (seen with bfloat16 rows of 1100 elements: the four elements behind each row were written).
+    // Other outputs are written with plain stores.
+    const int elem = (mode == TC_STORE_BF16 || mode == TC_SWIGLU_BF16) ? 2 : 4;
+    const int tma_out = ((uintptr_t)out & 15) == 0 && (ldc * elem) % 16 == 0 && ((long long)N * elem) % 16 == 0;
+    CUtensorMap mw, ma, mo;
+    if (tma_out) {
+        if (tc_make_out_map(&mo, out, elem, M, N, ldc, elem == 4 ? 16 : 32, feat)) return 1;
+    } else {
+        memset(&mo, 0, sizeof(mo));
+    }
+    if (tc_make_weight_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 && up_row0 >= 0 ? 64 : TC_BM, packed)) return 1;
     if (tc_make_map(&ma, a, M, K, lda, T2_HALF)) return 1;
     cudaStream_t s = (cudaStream_t)stream;
     switch (mode) {
-        case TC_STORE_BF16: return launch_tc2<TC_STORE_BF16>(mw, ma, prm, pairs, s);
-        case TC_STORE_F32: return launch_tc2<TC_STORE_F32>(mw, ma, prm, pairs, s);
-        case TC_ADD_F32: return launch_tc2<TC_ADD_F32>(mw, ma, prm, pairs, s);
-        default: return launch_tc2<TC_SWIGLU_BF16>(mw, ma, prm, pairs, s);
+        case TC_STORE_BF16: return launch_tc2<TC_STORE_BF16>(mw, ma, mo, prm, tma_out, pairs, s);
+        case TC_STORE_F32: return launch_tc2<TC_STORE_F32>(mw, ma, mo, prm, tma_out, pairs, s);
+        case TC_ADD_F32: return launch_tc2<TC_ADD_F32>(mw, ma, mo, prm, tma_out, pairs, s);
+        default: return launch_tc2<TC_SWIGLU_BF16>(mw, ma, mo, prm, tma_out, pairs, s);
     }
 }

@@ -139,19 +139,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     TcSchedule sched;
     sched.init(p);
     int tile, kb0, kb1;
-    auto load_w = [&](int s, int t, int kb) {
-        const int n0 = (t / p.tiles_m) * L::FEAT;
+    // n0: the tile's first feature, m0: its first token (computed once per work item: the
+    // producer's instructions per K block are on the pipeline's critical path)
+    auto load_w = [&](int s, int n0, int kb) {
         const uint32_t stage = smem_base + s * L::STAGE_BYTES;
         int x, y;
-        tc_w_coords(p, n0, kb, x, y);
+        // [gate; up] in bands (up_row0 < 0): the 64 gate rows and the 64 up rows of the tile's
+        // features are one 128-row band, one box
+        tc_w_coords(p, SWIGLU && p.up_row0 < 0 ? 2 * n0 : n0, kb, x, y);
         tma_load_2d(stage, &map_w, full0 + 8 * s, x, y);
-        if (SWIGLU) {
+        if (SWIGLU && p.up_row0 >= 0) {
             tc_w_coords(p, p.up_row0 + n0, kb, x, y);
             tma_load_2d(stage + L::W_BYTES / 2, &map_w, full0 + 8 * s, x, y);
         }
     };
-    auto load_a = [&](int s, int t, int kb) {
-        tma_load_2d(smem_base + s * L::STAGE_BYTES + L::W_BYTES, &map_a, full0 + 8 * s, kb * TC_BK, (t % p.tiles_m) * BN);
+    auto load_a = [&](int s, int m0, int kb) {
+        tma_load_2d(smem_base + s * L::STAGE_BYTES + L::W_BYTES, &map_a, full0 + 8 * s, kb * TC_BK, m0);
     };
 
     int early = 0;              // K blocks whose weight tiles thread 0 requests right away
@@ -179,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             early = min(kb1 - kb0, STAGES);
             for (int j = 0; j < early; j++) {
                 mbar_expect_tx(full0 + 8 * j, L::STAGE_BYTES);
-                load_w(j, tile, kb0 + j);
+                load_w(j, (tile / p.tiles_m) * L::FEAT, kb0 + j);
             }
         }
     }
@@ -203,10 +206,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) {
             pdl_wait();
             TL_EVENT(1);
-            for (int j = 0; j < early; j++) load_a(j, tile, kb0 + j);
+            for (int j = 0; j < early; j++) load_a(j, (tile % p.tiles_m) * BN, kb0 + j);
             int g = 0;                    // K blocks issued so far (all work items)
             bool alive = true;
             while (alive && sched.next(tile, kb0, kb1)) {
+                const int n0 = (tile / p.tiles_m) * L::FEAT, m0 = (tile % p.tiles_m) * BN;
                 for (int kb = kb0; kb < kb1; kb++, g++) {
                     if (g < early) continue;
                     const int s = g % STAGES;
@@ -217,8 +221,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         break;
                     }
                     mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
-                    load_w(s, tile, kb);
-                    load_a(s, tile, kb);
+                    load_w(s, n0, kb);
+                    load_a(s, m0, kb);
                 }
             }
             // copies in flight must land before the CTA may exit: wait (bounded) for the

@@ -150,6 +150,21 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc,
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Tile stores from shared memory (rows as in global memory, no swizzle); what lies outside the
+// tensor is not written.  The issuing thread tracks them as bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+// the same, adding the tile to what global memory holds (the addition is done at the memory side)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's bulk groups still READ their shared memory
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // arrives (once the MMAs issued so far have finished) on the barrier at the same offset in
 // every CTA of `cta_mask`
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
@@ -164,7 +179,7 @@ struct TcParams {
     void* out;
     long long ldc;
     int M, N, K;
-    int up_row0;          // SWIGLU: row of W where the up rows start
+    int up_row0;          // SWIGLU: row of W where the up rows start; -1: bands of 64 gate rows + their 64 up rows
     int tiles_m, tiles_n;
     int kb_total;         // K blocks per tile
     int stream_k;         // 0: whole tiles round-robin; 1: contiguous (tile, K block) ranges per CTA;
@@ -177,6 +192,7 @@ struct TcParams {
     int* error_flag;
     int cluster;          // stream_k == 2 only: the `split` CTAs of a tile are one cluster and sum through shared memory
     int packed;           // W is stored as tiles [row / 128][K block][128 rows][64 columns] (see tc_w_coords)
+    int group_m;          // pair kernel: token tiles per group (see t2_tile_coords)
 };
 
 // TMA coordinates of the box of weight rows that starts at `row`, K block kb.  Row-major W:
@@ -214,7 +230,7 @@ __device__ __forceinline__ void tc_emit_chunk(const TcParams& p, int m0, int n0,
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (q < 2) {
 #pragma unroll
-            for (int j = 0; j < 16; j++) yb[j * 64 + row] = __float2bfloat16_rn(silu_f32(v[j]) * xf[j * 64 + row]);
+            for (int j = 0; j < 16; j++) yb[j * 64 + row] = __float2bfloat16_rn(silu_fast(v[j]) * xf[j * 64 + row]);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int r = et >> 3, ch = et & 7;                 // token row of the chunk, 8-feature group
@@ -293,7 +309,7 @@ __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, 
             if (lane < 16 && n < p.N) {
                 bf16 y[4];
 #pragma unroll
-                for (int e = 0; e < 4; e++) y[e] = __float2bfloat16_rn(silu_f32(v[e]) * u[e]);
+                for (int e = 0; e < 4; e++) y[e] = __float2bfloat16_rn(silu_fast(v[e]) * u[e]);
                 bf16* o = (bf16*)p.out + (size_t)m * p.ldc + n;
                 if (n + 4 <= p.N) {
                     *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(y);
@@ -333,4 +349,9 @@ __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, 
 // Tensor map of a row-major bf16 matrix [rows, cols] with row stride ld (elements): boxes of
 // box_rows x 64 elements, 128-byte swizzle, zeros outside.
 int tc_make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows);
+// Tensor map of a row-major output [rows, cols] of float32 (elem_bytes 4) or bfloat16 (2) with
+// row stride ld (elements), for stores of boxes of box_rows x box_cols elements, no swizzle.
+// The base must be 16-byte aligned and ld * elem_bytes a multiple of 16.
+int tc_make_out_map(CUtensorMap* map, const void* base, int elem_bytes, long long rows, long long cols, long long ld,
+                    int box_rows, int box_cols);
 int tc_make_weight_map(CUtensorMap* map, const void* w, long long rows, long long K, long long ld, int box_rows, int packed);

@@ -254,10 +254,13 @@ def test_gemm_tensor_core_stream_k_and_tiles(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(512, 256, 64), (300, 640, 256), (1000, 1100, 520), (2048, 1024, 1024), (1, 128, 64),
-                                   (257, 129, 72)])
+                                   (257, 129, 72), (2600, 520, 128)])
 def test_gemm_tensor_core_cta_pairs(ops, M, N, K):
     """The cta_group::2 kernel (256 x 256 tiles on pairs of CTAs) with every epilogue, at sizes
-    with partial tiles in every dimension, against the plain product and the single-CTA kernel."""
+    with partial tiles in every dimension (2600 tokens: two groups of token tiles, the second
+    short), against the plain product and the single-CTA kernel.  The epilogue writes whole
+    tiles through shared memory (tile stores, tile adds) where the output's rows allow it and
+    element by element where they do not: the two give the same bits."""
     torch.manual_seed(15)
     a, w = _bf(torch.randn(M, K, device=DEV)), _bf(torch.randn(N, K, device=DEV))
     ref = a.double() @ w.double().t()
@@ -277,6 +280,19 @@ def test_gemm_tensor_core_cta_pairs(ops, M, N, K):
     ops.linear(a, w, two, schedule="pairs")
     assert _rel(two, one) < 1e-6 * math.sqrt(K)
     assert ops.lib.hb_gemm_tc2_resident_pairs(0) >= 32
+    # rows of N elements against rows a tile store cannot address (an odd stride) and rows it can
+    for out_dtype, accumulate in ((torch.bfloat16, False), (torch.float32, False), (torch.float32, True)):
+        results = []
+        for pad in (0, 1, 8 - N % 8):
+            wide = torch.full((M, N + pad), 3.0, device=DEV, dtype=out_dtype)
+            view = wide[:, :N]
+            if accumulate:
+                view.copy_(res)
+            ops.linear(a, w, view, accumulate=accumulate, schedule="pairs")
+            ops.check_errors()
+            assert pad == 0 or bool((wide[:, N:] == 3.0).all()), "the kernel wrote beside the output's rows"
+            results.append(view.clone())
+        assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
 
 
 @pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (3, 3072, 3072), (16, 6144, 4096), (8, 2560, 2048), (8, 2304, 2112),
@@ -354,7 +370,12 @@ def test_linear_swiglu_packed_weights(ops, M, K, I):
     h = _bf(torch.randn(M, K, device=DEV))
     w = _bf(torch.randn(2 * I, K, device=DEV) / math.sqrt(K))
     pw = ops.pack_weight(w, swiglu=True)
-    assert not isinstance(pw, torch.Tensor)
+    assert not isinstance(pw, torch.Tensor) and pw.gate_up_bands and torch.equal(pw.unpacked(), w)
+    # band b: the gate rows of features 64 b .. 64 b + 63, then their up rows
+    b = I // 64 - 1
+    assert torch.equal(pw.data[b, 0, :64], w[64 * b:64 * b + 64, :64]) and torch.equal(pw.data[b, 0, 64:], w[I + 64 * b:I + 64 * b + 64, :64])
+    with pytest.raises(Exception, match="linear_swiglu only"):
+        ops.linear(h, pw, torch.empty(M, 2 * I, device=DEV))
     assert isinstance(ops.pack_weight(_bf(torch.randn(2 * 100, K, device=DEV)), swiglu=True), torch.Tensor)   # halves of 100 rows: not packed
     ws = Workspace(torch.device(DEV))
     for schedule in ("tiles", "stream_k", "pairs"):
@@ -366,7 +387,7 @@ def test_linear_swiglu_packed_weights(ops, M, K, I):
 
 
 @pytest.mark.parametrize("schedule", ["tiles", "stream_k", "pairs", "cut_first"])
-@pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 304), (8, 4096, 512), (300, 512, 1000)])
+@pytest.mark.parametrize("M,K,I", [(3, 160, 416), (40, 64, 176), (130, 256, 304), (8, 4096, 512), (300, 512, 1000), (1100, 192, 264)])
 def test_linear_swiglu(ops, M, K, I, schedule):
     from hilbert_pruned_8b_b200.engine.workspace import Workspace
     torch.manual_seed(8)
