@@ -532,6 +532,82 @@ def test_attention_tensor_core_kernels(ops, nh, nkv, hd, window):
         assert _rel(out, gen.double()) < 2 ** -7
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 128, None), (6, 2, 64, None), (4, 1, 128, 300), (2, 2, 64, 65),
+                                              (2, 1, 128, 128)])
+def test_attention_prefill_long_prompts(ops, nh, nkv, hd, window):
+    """The tcgen05 prefill kernel on prompts of several query tiles and many key tiles: full and
+    short last tiles, new tokens behind a long context that starts inside a key tile, windows
+    shorter and longer than a tile, pages in a shuffled order.  One key of the longest prompt is
+    made to stand out for one query far behind it."""
+    torch.manual_seed(41)
+    dtype = torch.bfloat16
+    scale = 1.0 / math.sqrt(hd)
+    lens_before, new = [100, 0, 64, 1000, 0], [257, 600, 128, 5, 384]
+    total = [a + b for a, b in zip(lens_before, new)]
+    keys = [torch.randn(n, nkv, hd, device=DEV).to(dtype) for n in total]
+    values = [torch.randn(n, nkv, hd, device=DEV).to(dtype) for n in total]
+    T = sum(new)
+    q = torch.randn(T, nh, hd, device=DEV).to(dtype)
+    # sequence 1 (600 new tokens from position 0): query 570 of head nh - 1 looks for key 9
+    needle_q, needle_k = new[0] + 570, 9
+    keys[1][needle_k, nkv - 1] = 2.0
+    q[needle_q, nh - 1] = 4.0
+    pages_of = [(n + 63) // 64 for n in total]
+    n_pages = sum(pages_of) + 3
+    order = torch.randperm(n_pages).tolist()
+    tables = torch.full((len(total), max(pages_of) + 1), -1, dtype=torch.int32)
+    cache = _cache(n_pages, nkv, hd, dtype)
+    cache.k.normal_()
+    cache.v.normal_()
+    for b, n in enumerate(total):
+        for i in range(pages_of[b]):
+            page = order.pop()
+            tables[b, i] = page
+            seg = slice(64 * i, min(n, 64 * i + 64))
+            cache.k[page, :, :seg.stop - seg.start] = keys[b][seg].transpose(0, 1)
+            cache.v[page, :, :seg.stop - seg.start] = values[b][seg].transpose(0, 1)
+    tables = tables.to(DEV)
+    qkv = torch.zeros(T, (nh + 2 * nkv) * hd, device=DEV, dtype=dtype)
+    qkv[:, :nh * hd] = q.reshape(T, nh * hd)
+    step = _step(torch.tensor(sum(([b] * n for b, n in enumerate(new)), []), dtype=torch.int32, device=DEV),
+                 torch.tensor(sum((list(range(l, l + n)) for l, n in zip(lens_before, new)), []), dtype=torch.int32, device=DEV),
+                 tables)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    step.seq_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    step.seq_pos0 = torch.tensor(lens_before, dtype=torch.int32, device=DEV)
+    step.host_new, step.num_seqs, step.max_len = new, len(new), max(total)
+    out = torch.full((T, nh * hd), 9.0, device=DEV, dtype=dtype)
+    ops.call_log = []
+    try:
+        ops.attention(qkv, nh, nkv, hd, cache, step, out, scale, window)
+        ops.check_errors()
+        assert "hb_attention_prefill_tc" in ops.call_log
+    finally:
+        ops.call_log = None
+    # the plain statement in float64 on the device, sequence by sequence
+    group = nh // nkv
+    for b, n in enumerate(new):
+        qb = q[starts[b]:starts[b + 1]].double()                                   # [n, nh, hd]
+        kb = keys[b].double().repeat_interleave(group, dim=1)                        # [total, nh, hd]
+        vb = values[b].double().repeat_interleave(group, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", qb, kb) * scale
+        pos = torch.arange(lens_before[b], lens_before[b] + n, device=DEV).view(1, n, 1)
+        kpos = torch.arange(total[b], device=DEV).view(1, 1, -1)
+        seen = kpos <= pos
+        if window:
+            seen = seen & (kpos > pos - window)
+        ref = torch.einsum("hqk,khd->qhd", torch.softmax(sc.masked_fill(~seen, float("-inf")), dim=-1), vb)
+        got = out[starts[b]:starts[b + 1]].view(n, nh, hd).double()
+        assert _rel(got, ref) < 2 ** -7, f"sequence {b}"
+        worst = (got - ref).abs().amax(dim=(1, 2))
+        assert worst.max() < 0.05, f"sequence {b}: row {int(worst.argmax())} is off by {float(worst.max()):.3f}"
+    if window is None:
+        far = out[needle_q].view(nh, hd)[nh - 1].float()
+        assert (far - values[1][needle_k, nkv - 1].float()).abs().max() < 0.03
+
+
 def test_decode_attention_split_choice(ops):
     """The number of key splits: one wave of CTAs that fills the device where there is one, whole
     waves where one split per (sequence, kv head) would leave a third of a wave idle, never
