@@ -439,11 +439,12 @@ static int resident_pairs(int mode) {
 extern "C" int hb_gemm_tc2_resident_pairs(int mode) { return resident_pairs(mode & 3); }
 
 // Whether the pair kernel should take a product: enough tokens to fill 256-token tiles.
-// From 768 tokens on.  Below, a product has too few 256 x 256 tiles for 74 pairs (512 tokens x 4096
-// features: 32) and the single-CTA kernel, which cuts K when tiles are few, is faster: a prompt of
-// 512 tokens through 4 layers of the 8B sizes 1.64 against 1.77 ms, 768 tokens 1.92 either way,
-// 1024 tokens 2.42 against 2.23 ms.
-extern "C" int hb_gemm_tc2_wanted(int M, int N, int K) { return M >= 768 && N >= 256 && K >= 64; }
+// Above 512 tokens.  Up to there a product has too few 256 x 256 tiles for 74 pairs (512 tokens x
+// 4096 features: 32) and the single-CTA kernel, which cuts K when tiles are few, is as fast or
+// faster: a prompt through 4 layers of the 8B sizes, single-CTA against pairs: 256 tokens 1.21
+// against 1.27 ms, 512 tokens 1.54 either way, 640 tokens 1.76 against 1.63, 768 tokens 1.82
+// against 1.70, 1024 tokens 2.38 against 1.94 ms.
+extern "C" int hb_gemm_tc2_wanted(int M, int N, int K) { return M > 512 && N >= 256 && K >= 64; }
 
 // Arguments as hb_gemm_tc (no scratch: whole tiles only).
 extern "C" int hb_gemm_tc2(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,

@@ -1,5 +1,7 @@
 """Makes tests/golden/reference_logits.json: logits of the reference's own CPU engine on two
-tiny models, to anchor tests/plain_llama.py once.
+tiny models, to anchor tests/plain_llama.py once; and tests/golden/reference_shapes.json: what
+the reference's ``shapes`` command (cleanroom-transformer/src/main.c:528-536, src/shapes.c) prints
+for the two configurations, to anchor the weight table.
 
 Run from the repository root:  python tests/golden/make_golden.py /path/to/reference
 
@@ -31,9 +33,12 @@ def main() -> None:
     subprocess.run(["make", "CC=/usr/bin/gcc"], cwd=src, check=True, stdout=subprocess.DEVNULL)
     exe = os.path.join(src, "build", "cleanroom-transformer")
     out = {"source": "reference CPU backend, `logits --backend cpu`", "cases": []}
+    shapes = {}
     for name, spec in GOLDEN_MODELS.items():
         mdir = os.path.join(work, name)
         write_golden_model(mdir, spec)
+        res = subprocess.run([exe, "shapes", "--model", mdir], check=True, capture_output=True, text=True)
+        shapes[name] = json.loads(res.stdout)
         vocab = spec["config"]["vocab_size"]
         toks = golden_tokens(spec)
         ids = list(range(0, vocab, max(1, vocab // 24)))
@@ -50,8 +55,14 @@ def main() -> None:
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_logits.json")
     with open(dst, "w") as f:
         json.dump(out, f)
+    dst_shapes = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_shapes.json")
+    with open(dst_shapes, "w") as f:
+        f.write('{"source": "reference `shapes --model DIR`", "models": {\n')
+        for i, (k, v) in enumerate(shapes.items()):
+            f.write(f' "{k}": {json.dumps(v)}' + (",\n" if i + 1 < len(shapes) else "\n"))
+        f.write("}}\n")
     shutil.rmtree(work)
-    print("wrote", dst, len(out["cases"]), "cases")
+    print("wrote", dst, len(out["cases"]), "cases;", dst_shapes)
 
 
 if __name__ == "__main__":

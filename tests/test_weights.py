@@ -33,6 +33,39 @@ def test_table_names_and_shapes_follow_the_reference():
     assert len(t) == 1 + 3 * 9 + 2
 
 
+def test_table_equals_the_shape_table_the_reference_prints():
+    """The reference's own ``shapes`` command (cleanroom-transformer/src/shapes.c:12-40,
+    src/main.c:528-536), run once on the two golden configurations and stored under
+    tests/golden/: every per-layer matrix of its list is in the weight table under the same name
+    with the same rows and columns, in every layer, and the table has no other layer matrices;
+    the head sizes it derives are the model specification's."""
+    import json
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(here, "golden"))
+    from golden_models import GOLDEN_MODELS
+    with open(os.path.join(here, "golden", "reference_shapes.json")) as f:
+        ref = json.load(f)["models"]
+    for name, spec in GOLDEN_MODELS.items():
+        cfg = hb.LlamaConfig.from_dict(spec["config"])
+        ms = cfg.model_spec()
+        table = weight_table(ms)
+        r = ref[name]
+        assert r["arch"] == "llama" and r["hidden"] == ms.hidden_size and len(r["layers"]) == 1
+        layer = r["layers"][0]
+        assert layer["type"] == "full" and layer["count"] == len(ms.layers) == spec["config"]["num_hidden_layers"]
+        mixer = ms.layers[0].mixer.params
+        assert (r["n_heads"], r["n_kv_heads"], r["head_dim"]) == (mixer["num_heads"], mixer["num_kv_heads"], mixer["head_dim"])
+        assert r["rot_dim"] == mixer["position"].params["rotary_dim"]
+        matrices = {w["name"]: (w["rows"], w["cols"]) for w in layer["weights"]}
+        for i in range(layer["count"]):
+            prefix = f"model.layers.{i}."
+            ours = {k[len(prefix):]: tuple(v.shape) for k, v in table.items() if k.startswith(prefix) and len(v.shape) == 2}
+            assert ours == matrices, (name, i)
+        act = layer["activations"]
+        assert act["q_gate"][1] == matrices["self_attn.q_proj.weight"][0] and act["mlp_act"][1] == matrices["mlp.down_proj.weight"][1]
+
+
 def test_random_model_folder_loads_and_is_seeded(tmp_path):
     cfg = hb.LlamaConfig.from_dict(TINY_A)
     d1 = write_random_model(str(tmp_path / "m1"), cfg, seed=5)
