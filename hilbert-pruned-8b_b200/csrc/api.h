@@ -38,6 +38,22 @@ int hb_gemm_tc_resident_clusters(int mode, int size);
 int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,
                int M, int N, int K, int mode, int up_row0, int schedule, float* partials, long long partials_capacity,
                int* tile_counters, long long counters_capacity, int* error_flag, int packed, void* stream);
+// A norm between two products, folded into them (hb_gemm_tc_fold; null pointers: that side is not used).
+typedef struct {
+    const float* prep_w;        // producer (mode 2): the norm's weight; the factor is prep_offset + prep_w[feature]
+    float prep_offset;
+    void* prep_out;             // bfloat16 [M, prep_ld]: the new residual values times the factor
+    long long prep_ld;
+    float* prep_sumsq;          // [M, sumsq_ld]: per token, the sums of squares of each 32 features
+    const float* scale_sumsq;   // consumer (modes 0, 1, 3): such sums, written by the producer
+    int scale_parts;            // how many of them per token
+    float scale_inv_size;       // 1 / (features of the normed vector)
+    float scale_eps;
+    int sumsq_ld;
+} HbNormFold;
+int hb_gemm_tc_fold(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,
+               int M, int N, int K, int mode, int up_row0, int schedule, float* partials, long long partials_capacity,
+               int* tile_counters, long long counters_capacity, int* error_flag, int packed, const HbNormFold* fold, void* stream);
 int hb_gemm_tc2_wanted(int M, int N, int K);
 int hb_gemm_tc2_resident_pairs(int mode);
 int hb_gemm_tc2(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out, long long ldc,

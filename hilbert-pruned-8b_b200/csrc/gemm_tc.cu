@@ -248,10 +248,15 @@ static int dispatch_bn(int bn, bool cluster, int mode, const CUtensorMap& mw, co
 // scratch described above (capacities in floats and ints); `error_flag` is a device int the
 // kernel sets when a wait ran out.  `packed`: W is stored as contiguous 128 x 64 tiles (see
 // tc_w_coords; w_rows is then the number of rows before padding and ldw is not used).
-extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,
-                          long long ldc, int M, int N, int K, int mode, int up_row0, int schedule, float* partials,
-                          long long partials_capacity, int* tile_counters, long long counters_capacity, int* error_flag,
-                          int packed, void* stream) {
+//
+// `fold` (may be null): a norm between two products folded into them, for up to TC_SCALE_ROWS
+// tokens.  The product that writes the residual stream (mode 2) also writes bf16(x * (offset +
+// weight)) and per token the sums of squares of each 32 features; the product that reads it
+// (modes 0, 1, 3) multiplies every token's row by rsqrt(sum * inv_size + eps).
+extern "C" int hb_gemm_tc_fold(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,
+                               long long ldc, int M, int N, int K, int mode, int up_row0, int schedule, float* partials,
+                               long long partials_capacity, int* tile_counters, long long counters_capacity, int* error_flag,
+                               int packed, const HbNormFold* fold, void* stream) {
     if (M == 0 || N == 0) return 0;
     HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     HB_REQUIRE(mode >= 0 && mode <= 3, "gemm_tc: unknown epilogue %d", mode);
@@ -275,7 +280,31 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
     CUtensorMap mw, ma;
     if (tc_make_weight_map(&mw, w, w_rows, K, ldw, mode == TC_SWIGLU_BF16 && up_row0 >= 0 ? 64 : TC_BM, packed)) return 1;
     if (tc_make_map(&ma, a, M, K, lda, pl.bn)) return 1;
-    TcParams prm;
+    TcParams prm = {};
+    if (fold != nullptr && fold->prep_w != nullptr) {
+        HB_REQUIRE(mode == TC_ADD_F32 && M <= TC_SCALE_ROWS && pl.tiles_m == 1, "gemm_tc: a norm is prepared by the product that adds to the residual, for up to %d tokens", TC_SCALE_ROWS);
+        HB_REQUIRE(N % 4 == 0 && ldc % 4 == 0 && ((uintptr_t)out & 15) == 0, "gemm_tc: preparing a norm needs 16-byte aligned output rows");
+        HB_REQUIRE(fold->prep_out != nullptr && fold->prep_sumsq != nullptr && ((uintptr_t)fold->prep_out & 7) == 0 && fold->prep_ld % 4 == 0 &&
+                       fold->prep_ld >= N && ((uintptr_t)fold->prep_w & 15) == 0,
+                   "gemm_tc: the prepared norm input needs 8-byte aligned rows of at least %d elements", N);
+        HB_REQUIRE(fold->sumsq_ld >= (N + 31) / 32, "gemm_tc: %d sums of squares per token do not fit rows of %d", (N + 31) / 32, fold->sumsq_ld);
+        prm.prep_w = fold->prep_w;
+        prm.prep_offset = fold->prep_offset;
+        prm.prep_out = (bf16*)fold->prep_out;
+        prm.prep_ld = fold->prep_ld;
+        prm.prep_sumsq = fold->prep_sumsq;
+        prm.sumsq_ld = fold->sumsq_ld;
+    }
+    if (fold != nullptr && fold->scale_sumsq != nullptr) {
+        HB_REQUIRE(mode != TC_ADD_F32 && M <= TC_SCALE_ROWS && pl.tiles_m == 1, "gemm_tc: rows are scaled for up to %d tokens, not in the residual add", TC_SCALE_ROWS);
+        HB_REQUIRE(fold->scale_parts > 0 && fold->scale_parts <= fold->sumsq_ld && fold->sumsq_ld % 4 == 0 && ((uintptr_t)fold->scale_sumsq & 15) == 0,
+                   "gemm_tc: %d sums of squares per token in rows of %d floats", fold->scale_parts, fold->sumsq_ld);
+        prm.scale_sumsq = fold->scale_sumsq;
+        prm.scale_parts = fold->scale_parts;
+        prm.scale_inv_size = fold->scale_inv_size;
+        prm.scale_eps = fold->scale_eps;
+        prm.sumsq_ld = fold->sumsq_ld;
+    }
     prm.out = out;
     prm.ldc = ldc;
     prm.M = M;
@@ -296,4 +325,12 @@ extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long
     prm.cluster = cluster ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     return dispatch_bn(pl.bn, cluster, mode, mw, ma, prm, pl.grid, s);
+}
+
+extern "C" int hb_gemm_tc(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,
+                          long long ldc, int M, int N, int K, int mode, int up_row0, int schedule, float* partials,
+                          long long partials_capacity, int* tile_counters, long long counters_capacity, int* error_flag,
+                          int packed, void* stream) {
+    return hb_gemm_tc_fold(a, lda, w, ldw, w_rows, out, ldc, M, N, K, mode, up_row0, schedule, partials, partials_capacity, tile_counters,
+                           counters_capacity, error_flag, packed, nullptr, stream);
 }

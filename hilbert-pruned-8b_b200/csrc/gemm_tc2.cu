@@ -465,7 +465,7 @@ extern "C" int hb_gemm_tc2(const void* a, long long lda, const void* w, long lon
     HB_REQUIRE(mode != TC_SWIGLU_BF16 || (ldc % 8 == 0 && N % 8 == 0 && ((uintptr_t)out & 15) == 0),
                "gemm_tc2: the SwiGLU output needs 16-byte aligned rows of a multiple of 8 features (the single-CTA kernel takes others)");
     const int feat = mode == TC_SWIGLU_BF16 ? 64 : TC_BM;
-    TcParams prm;
+    TcParams prm = {};
     prm.out = out;
     prm.ldc = ldc;
     prm.M = M;

@@ -114,7 +114,9 @@ struct TcSchedule {
 // With 16 tokens the partial tiles have a region of their own; with 32 and 64 they lie over
 // the first CTA's pipeline stages, which a first cluster barrier declares free (every CTA's
 // MMAs have finished).
-template <int BN, int MODE, int STAGES, bool CLUSTER>
+// FOLD: the variant that serves a norm folded into the products around it (TcParams); launched
+// only when a call asks for it, so that the plain variants keep their registers and schedule.
+template <int BN, int MODE, int STAGES, bool CLUSTER, bool FOLD = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const TcParams p) {
     using L = TcLayout<BN, MODE>;
@@ -130,6 +132,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* last_flag = (int*)(tmem_slot + 2);
+    float* srow = (float*)(tmem_slot + 4);         // a folded norm's per-token factors (tc_row_scales), TC_SCALE_ROWS floats
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t smem_base = smem_u32(smem);
@@ -281,6 +284,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;                    // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;             // weight row of the tile = TMEM lane
         pdl_wait();                                // the output, the scratch and the counters belong to earlier kernels until now
+        if (FOLD) tc_row_scales(p, srow, et);      // (while the first accumulator is still being computed)
         int item = 0;
         while (sched.next(tile, kb0, kb1)) {
             const int buf = item & 1;
@@ -402,7 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             acc[i].w += t[i].w;
                         }
                     }
-                    tc_emit_flat<MODE, GROUP>(p, m0 + g0, n0, acc, et, res, have_res);     // read ahead: one group only
+                    tc_emit_flat<MODE, GROUP, FOLD>(p, m0 + g0, n0, acc, et, res, have_res, srow);     // read ahead: one group only
                 }
             } else if (finish) {
 #pragma unroll 1
@@ -410,7 +414,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (m0 + c >= p.M) break;
                     float v[16];
                     tmem_ld16(lane_addr + c, v);
-                    tc_emit_chunk<MODE>(p, m0, n0, c, v, xchg, q, row, et);
+                    tc_emit_chunk<MODE, FOLD>(p, m0, n0, c, v, xchg, q, row, et, srow);
                 }
             }
             if (whole) {
@@ -455,7 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
             if (et == 0) TL_EVENT(6);
-            tc_emit_flat<MODE, BN <= 64 ? BN : 4>(p, cl_m0, cl_n0, acc, et, cl_res, cl_have_res);
+            tc_emit_flat<MODE, BN <= 64 ? BN : 4, FOLD>(p, cl_m0, cl_n0, acc, et, cl_res, cl_have_res, srow);
             if (et == 0) TL_EVENT(7);
         }
     }
@@ -471,11 +475,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
-template <int BN, int MODE, int STAGES, bool CLUSTER>
+template <int BN, int MODE, int STAGES, bool CLUSTER, bool FOLD = false>
 struct TcLaunch {
     using L = TcLayout<BN, MODE>;
     static constexpr int SMEM = STAGES * L::STAGE_BYTES + L::XCHG_BYTES + (CLUSTER && BN == 16 ? TC_MAX_CLUSTER * L::PART_BYTES : 0) +
-                                (2 * STAGES + 4) * 8 + 16 + 1024;
+                                (2 * STAGES + 4) * 8 + 16 + (FOLD ? TC_SCALE_ROWS * 4 : 0) + 1024;
     // CLUSTER: the most K ranges of a tile: what fits over the first CTA's stages (above 16 tokens)
     static constexpr int MAX_PARTS = BN == 16 || STAGES * L::STAGE_BYTES / L::PART_BYTES >= TC_MAX_CLUSTER
                                          ? TC_MAX_CLUSTER : STAGES * L::STAGE_BYTES / L::PART_BYTES;
@@ -483,7 +487,7 @@ struct TcLaunch {
     static int prepare() {
         static bool attr_set = false;
         if (!attr_set) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
             if (e != cudaSuccess) return hb_fail("gemm_tc: cannot reserve %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
             attr_set = true;
         }
@@ -491,9 +495,9 @@ struct TcLaunch {
     }
     static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid, cudaStream_t s) {
         if (prepare()) return 1;
-        cudaError_t e = CLUSTER ? hb_launch_clusters(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, dim3(grid), dim3(TC_THREADS), SMEM, s,
+        cudaError_t e = CLUSTER ? hb_launch_clusters(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER, FOLD>, dim3(grid), dim3(TC_THREADS), SMEM, s,
                                                      (unsigned)prm.split, mw, ma, prm)
-                                : hb_launch(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, dim3(grid), dim3(TC_THREADS), SMEM, s, mw, ma, prm);
+                                : hb_launch(gemm_tc_kernel<BN, MODE, STAGES, CLUSTER, FOLD>, dim3(grid), dim3(TC_THREADS), SMEM, s, mw, ma, prm);
         if (e != cudaSuccess) return hb_fail("gemm_tc: launch failed: %s", cudaGetErrorString(e));
         return hb_check_launch("gemm_tc");
     }
@@ -512,7 +516,7 @@ struct TcLaunch {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, MODE, STAGES, CLUSTER>, &cfg) != cudaSuccess) {
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, MODE, STAGES, CLUSTER, FOLD>, &cfg) != cudaSuccess) {
             cudaGetLastError();
             return 0;
         }
@@ -523,8 +527,8 @@ struct TcLaunch {
 // The cluster variants.  16 tokens: fewer stages, room for the partial tiles beside them (a
 // step of 8 layers at batch 8: 1305 us; with the partial tiles over 11 stages and the second
 // cluster barrier that needs: 1327 us).  32 and 64 tokens: the stages of the plain kernels.
-template <int BN, int MODE>
-using TcClusterLaunch = TcLaunch<BN, MODE, BN == 16 ? (MODE == TC_SWIGLU_BF16 ? 7 : 8) : BN == 32 ? 10 : 8, true>;
+template <int BN, int MODE, bool FOLD = false>
+using TcClusterLaunch = TcLaunch<BN, MODE, BN == 16 ? (MODE == TC_SWIGLU_BF16 ? 7 : 8) : BN == 32 ? 10 : 8, true, FOLD>;
 
 template <int BN, int MODE>
 static bool clusters_fit(int size, long long tiles) {
@@ -547,28 +551,39 @@ static bool clusters_fit_bn(int mode, int size, long long tiles) {
     }
 }
 
-// One token tile, every epilogue: the cluster variant or the plain one with `STAGES` stages.
-template <int BN, int STAGES>
-static int tc_launch_bn(bool cluster, int mode, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid,
-                        cudaStream_t s) {
+// One token tile, every epilogue: the cluster variant or the plain one with `STAGES` stages;
+// the variants that serve a folded norm when the call brings one (up to 64 tokens).
+template <int BN, int STAGES, bool FOLD>
+static int tc_launch_bn_fold(bool cluster, int mode, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid,
+                             cudaStream_t s) {
     if (cluster) {
         if constexpr (BN <= 64) {
             switch (mode & 3) {
-                case TC_STORE_BF16: return TcClusterLaunch<BN, TC_STORE_BF16>::launch(mw, ma, prm, grid, s);
-                case TC_STORE_F32: return TcClusterLaunch<BN, TC_STORE_F32>::launch(mw, ma, prm, grid, s);
-                case TC_ADD_F32: return TcClusterLaunch<BN, TC_ADD_F32>::launch(mw, ma, prm, grid, s);
-                default: return TcClusterLaunch<BN, TC_SWIGLU_BF16>::launch(mw, ma, prm, grid, s);
+                case TC_STORE_BF16: return TcClusterLaunch<BN, TC_STORE_BF16, FOLD>::launch(mw, ma, prm, grid, s);
+                case TC_STORE_F32: return TcClusterLaunch<BN, TC_STORE_F32, FOLD>::launch(mw, ma, prm, grid, s);
+                case TC_ADD_F32: return TcClusterLaunch<BN, TC_ADD_F32, FOLD>::launch(mw, ma, prm, grid, s);
+                default: return TcClusterLaunch<BN, TC_SWIGLU_BF16, FOLD>::launch(mw, ma, prm, grid, s);
             }
         } else {
             return hb_fail("gemm_tc: no cluster variant for token tile %d", BN);
         }
     }
     switch (mode & 3) {
-        case TC_STORE_BF16: return TcLaunch<BN, TC_STORE_BF16, STAGES, false>::launch(mw, ma, prm, grid, s);
-        case TC_STORE_F32: return TcLaunch<BN, TC_STORE_F32, STAGES, false>::launch(mw, ma, prm, grid, s);
-        case TC_ADD_F32: return TcLaunch<BN, TC_ADD_F32, STAGES, false>::launch(mw, ma, prm, grid, s);
-        default: return TcLaunch<BN, TC_SWIGLU_BF16, STAGES, false>::launch(mw, ma, prm, grid, s);
+        case TC_STORE_BF16: return TcLaunch<BN, TC_STORE_BF16, STAGES, false, FOLD>::launch(mw, ma, prm, grid, s);
+        case TC_STORE_F32: return TcLaunch<BN, TC_STORE_F32, STAGES, false, FOLD>::launch(mw, ma, prm, grid, s);
+        case TC_ADD_F32: return TcLaunch<BN, TC_ADD_F32, STAGES, false, FOLD>::launch(mw, ma, prm, grid, s);
+        default: return TcLaunch<BN, TC_SWIGLU_BF16, STAGES, false, FOLD>::launch(mw, ma, prm, grid, s);
     }
+}
+
+template <int BN, int STAGES>
+static int tc_launch_bn(bool cluster, int mode, const CUtensorMap& mw, const CUtensorMap& ma, const TcParams& prm, int grid,
+                        cudaStream_t s) {
+    if (prm.prep_w != nullptr || prm.scale_sumsq != nullptr) {
+        if constexpr (BN <= TC_SCALE_ROWS) return tc_launch_bn_fold<BN, STAGES, true>(cluster, mode, mw, ma, prm, grid, s);
+        else return hb_fail("gemm_tc: a folded norm with a token tile of %d", BN);
+    }
+    return tc_launch_bn_fold<BN, STAGES, false>(cluster, mode, mw, ma, prm, grid, s);
 }
 
 // Token tiles 64, 128 and 256 live in gemm_tc_wide.cu.

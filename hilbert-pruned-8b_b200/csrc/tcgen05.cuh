@@ -193,7 +193,39 @@ struct TcParams {
     int cluster;          // stream_k == 2 only: the `split` CTAs of a tile are one cluster and sum through shared memory
     int packed;           // W is stored as tiles [row / 128][K block][128 rows][64 columns] (see tc_w_coords)
     int group_m;          // pair kernel: token tiles per group (see t2_tile_coords)
+    // A norm between two products, folded into them (few tokens; single-CTA kernel only).
+    // y = W (x * g * s) with the per-token s = rsqrt(mean(x^2) + eps) is computed as
+    // s * (W bf16(x * g)): the product that WRITES x (TC_ADD_F32) also writes bf16(x * g) and,
+    // per token, partial sums of x^2 (one per 32 features: slot = feature / 32); the product that
+    // READS it multiplies its rows by s.  Sums and s in float32.
+    const float* prep_w;  // producer: the norm's weight [N], nullptr: none; the factor is prep_offset + prep_w[f]
+    float prep_offset;
+    bf16* prep_out;       // [M, prep_ld]
+    long long prep_ld;
+    float* prep_sumsq;    // [M, sumsq_ld]
+    int sumsq_ld;         // floats per token in prep_sumsq and in scale_sumsq
+    const float* scale_sumsq;   // consumer: nullptr: none
+    int scale_parts;      // slots per token to add
+    float scale_inv_size, scale_eps;
 };
+
+// The consumer's per-token factors for the tokens of a tile column block that starts at token 0
+// (folding is used with one token tile only): thread t < M adds its token's partial sums.
+// `srow` is shared memory of at least M floats.  All 128 epilogue threads call it once.
+__device__ __forceinline__ void tc_row_scales(const TcParams& p, float* srow, int et) {
+    if (p.scale_sumsq == nullptr) return;
+    if (et < p.M) {
+        const float4* src = reinterpret_cast<const float4*>(p.scale_sumsq + (size_t)et * p.sumsq_ld);
+        float acc = 0.0f;
+        for (int i = 0; i < p.scale_parts / 4; i++) {
+            const float4 t = __ldcg(src + i);
+            acc += (t.x + t.y) + (t.z + t.w);
+        }
+        for (int i = p.scale_parts & ~3; i < p.scale_parts; i++) acc += __ldcg(p.scale_sumsq + (size_t)et * p.sumsq_ld + i);
+        srow[et] = rsqrtf(acc * p.scale_inv_size + p.scale_eps);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
 
 // TMA coordinates of the box of weight rows that starts at `row`, K block kb.  Row-major W:
 // column kb * 64 of row `row`.  Packed W: every 128-row x 64-column tile is one contiguous
@@ -211,13 +243,24 @@ __device__ __forceinline__ void tc_w_coords(const TcParams& p, int row, int kb, 
 }
 
 #define TC_XCHG_BYTES (2 * 16 * 64 * 4 + 2 * 16 * 64 * 2)
+// The most tokens of a product that serves a folded norm: the 16-token tile.  Measured per decode step,
+// folded against norm kernels: 8B sizes batch 1 -5.1 %, batch 8 -2.4 %, batch 16 -1.0 %, batch 32 -0.4 %,
+// batch 48 +0.4 %; 1B sizes batch 32 -0.5 %, batch 64 +2.4 %; 3B sizes batch 16 -4.5 %, batch 32 +2.2 %:
+// with more tokens the longer epilogues of the residual products cost more than the two kernels saved.
+#define TC_SCALE_ROWS 16
 
 // Epilogue of 16 token columns [m0 + c, m0 + c + 16) of a tile: v[j] is the accumulator of
 // weight row `row` (0..127, = TMEM lane) and token column c + j.  n0 is the first output
 // feature of the tile.  Called by all 128 epilogue threads (et = 0..127, q = row / 32).
-template <int MODE>
-__device__ __forceinline__ void tc_emit_chunk(const TcParams& p, int m0, int n0, int c, const float (&v)[16], uint8_t* xchg,
-                                              int q, int row, int et) {
+template <int MODE, bool FOLD = false>
+__device__ __forceinline__ void tc_emit_chunk(const TcParams& p, int m0, int n0, int c, const float (&v_in)[16], uint8_t* xchg,
+                                              int q, int row, int et, const float* srow = nullptr) {
+    // FOLD: the kernel variant that serves a folded norm (a variant of its own, so that the
+    // others keep their registers and schedule).  The consumer side: every token's row times its factor
+    float v[16];
+    const bool scaled = FOLD && MODE != TC_ADD_F32 && p.scale_sumsq != nullptr;
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = (FOLD && scaled) ? v_in[j] * srow[min(m0 + c + j, p.M - 1)] : v_in[j];
     if (MODE == TC_SWIGLU_BF16) {
         // rows 0..63 of the tile are gate rows, rows 64..127 the up rows of the same
         // features: pair them through shared memory, then store 16 bytes per thread
@@ -245,7 +288,34 @@ __device__ __forceinline__ void tc_emit_chunk(const TcParams& p, int m0, int n0,
         }
     } else {
         const int f = n0 + row;
-        if (f < p.N) {
+        if (FOLD && MODE == TC_ADD_F32 && p.prep_w != nullptr) {
+            // the producer side of a folded norm: the new values, their products with the
+            // norm's weight as bfloat16, and per token the sum of squares of this warp's 32 features
+            float r[16];
+            float* po = (float*)p.out + (size_t)(m0 + c) * p.ldc + f;
+            const bool here = f < p.N;
+#pragma unroll
+            for (int j = 0; j < 16; j++) r[j] = (here && m0 + c + j < p.M) ? __ldcg(po + (size_t)j * p.ldc) : 0.0f;
+            const float g = here ? p.prep_offset + __ldg(p.prep_w + f) : 0.0f;
+            const int lane = et & 31;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int m = m0 + c + j;
+                if (m >= p.M) break;                          // the same for the whole warp
+                const float nv = here ? r[j] + v[j] : 0.0f;
+                if (here) {
+                    po[(size_t)j * p.ldc] = nv;
+                    p.prep_out[(size_t)m * p.prep_ld + f] = __float2bfloat16_rn(nv * g);
+                }
+                float ss = nv * nv;
+                ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+                if (lane == 0) p.prep_sumsq[(size_t)m * p.sumsq_ld + (n0 >> 5) + q] = ss;
+            }
+        } else if (f < p.N) {
             if (MODE == TC_ADD_F32) {
                 // all loads of the residual first, then the stores: written one by one
                 // the compiler must keep each load behind the store before it
@@ -276,10 +346,50 @@ __device__ __forceinline__ void tc_emit_chunk(const TcParams& p, int m0, int n0,
 // i * 4 + (et >> 5).  The same results as tc_emit_chunk, with 16-byte accesses.
 // `res`: for TC_ADD_F32, the values of the output read ahead of time (have_res; they are then
 // not read again).
-template <int MODE, int BN>
+template <int MODE, int BN, bool FOLD = false>
 __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, const float4 (&acc)[BN / 4], int et,
-                                             const float4 (&res)[BN / 4], bool have_res) {
+                                             const float4 (&res)[BN / 4], bool have_res, const float* srow = nullptr) {
     const int lane = et & 31, tw = et >> 5;
+    const bool scaled = FOLD && MODE != TC_ADD_F32 && p.scale_sumsq != nullptr;     // the consumer side of a folded norm
+    if (FOLD && MODE == TC_ADD_F32 && p.prep_w != nullptr) {
+        // The producer side of a folded norm (the host passes it only with a 16-byte aligned
+        // output and N a multiple of 4): new values, their products with the norm's weight as
+        // bfloat16, and the sums of squares of each 32 features (8 lanes) of a token.
+        const int n = n0 + lane * 4;
+        const bool here = n < p.N;
+        float4 g = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (here) {
+            g = __ldg(reinterpret_cast<const float4*>(p.prep_w + n));
+            g = make_float4(g.x + p.prep_offset, g.y + p.prep_offset, g.z + p.prep_offset, g.w + p.prep_offset);
+        }
+        float4 old[BN / 4];
+#pragma unroll
+        for (int i = 0; i < BN / 4; i++) {
+            const int m = m0 + i * 4 + tw;
+            old[i] = have_res ? res[i]
+                              : (here && m < p.M) ? __ldcg(reinterpret_cast<const float4*>((const float*)p.out + (size_t)m * p.ldc + n))
+                                                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int i = 0; i < BN / 4; i++) {
+            const int m = m0 + i * 4 + tw;                      // uniform in a warp
+            if (m >= p.M) continue;
+            float4 nv = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (here) {
+                nv = make_float4(old[i].x + acc[i].x, old[i].y + acc[i].y, old[i].z + acc[i].z, old[i].w + acc[i].w);
+                *reinterpret_cast<float4*>((float*)p.out + (size_t)m * p.ldc + n) = nv;
+                bf16 h[4] = {__float2bfloat16_rn(nv.x * g.x), __float2bfloat16_rn(nv.y * g.y), __float2bfloat16_rn(nv.z * g.z),
+                             __float2bfloat16_rn(nv.w * g.w)};
+                *reinterpret_cast<uint2*>(p.prep_out + (size_t)m * p.prep_ld + n) = *reinterpret_cast<const uint2*>(h);
+            }
+            float ss = (nv.x * nv.x + nv.y * nv.y) + (nv.z * nv.z + nv.w * nv.w);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+            if ((lane & 7) == 0) p.prep_sumsq[(size_t)m * p.sumsq_ld + (n0 >> 5) + (lane >> 3)] = ss;
+        }
+        return;
+    }
     // TC_ADD_F32 without values read ahead: all loads of the old output first, then the stores
     // (written one by one the compiler must keep each load behind the store before it: one
     // round trip per token instead of one in all)
@@ -299,7 +409,9 @@ __device__ __forceinline__ void tc_emit_flat(const TcParams& p, int m0, int n0, 
     for (int i = 0; i < BN / 4; i++) {
         const int m = m0 + i * 4 + tw;                      // uniform in a warp
         if (m >= p.M) continue;
-        const float v[4] = {acc[i].x, acc[i].y, acc[i].z, acc[i].w};
+        const float sc = scaled ? srow[m] : 1.0f;
+        const float v[4] = {FOLD ? acc[i].x * sc : acc[i].x, FOLD ? acc[i].y * sc : acc[i].y, FOLD ? acc[i].z * sc : acc[i].z,
+                            FOLD ? acc[i].w * sc : acc[i].w};
         if (MODE == TC_SWIGLU_BF16) {
             // lanes 0..15 hold gate rows 4 * lane .. + 3, lanes 16..31 the up rows of the same features
             float u[4];

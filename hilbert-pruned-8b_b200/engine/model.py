@@ -127,9 +127,21 @@ class DecoderModel:
         H, V = self.spec.hidden_size, self.spec.vocab_size
         x = ws.buffer("model.x", (cap, H), torch.float32)[:T]
         self.embedding.forward(step.tokens, x)
-        for i, e in enumerate(self.spec.plan):
+        # Norms at the seam between two blocks may be folded into the products around them: a block
+        # that can says what it needs (fold_request), the block in front prepares it and hands on
+        # what it prepared.
+        plan, prepared = self.spec.plan, None
+        for i, e in enumerate(plan):
             owner = i if e.cache_of is None else e.cache_of
-            self.blocks[e.layer].forward(x, step, cache.view(owner), cache.state_view(i), e.cache_of is None)
+            block = self.blocks[e.layer]
+            args = (x, step, cache.view(owner), cache.state_view(i), e.cache_of is None)
+            if getattr(block, "folds_norms", False):
+                nxt = self.blocks[plan[i + 1].layer] if i + 1 < len(plan) else None
+                request = nxt.fold_request(step) if nxt is not None and getattr(nxt, "folds_norms", False) else None
+                prepared = block.forward(*args, prepared=prepared, prepare_next=request)
+            else:
+                block.forward(*args)
+                prepared = None
         n = step.num_wanted
         if n == 0:
             return None

@@ -35,6 +35,8 @@ _SIGNATURES = {
                         _c_int, _c_ptr],
     "hb_gemm_tc": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr],
+    "hb_gemm_tc_fold": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                        _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "hb_gemm_tc2": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int,
                     _c_ptr],
     "hb_attention_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
@@ -104,6 +106,24 @@ def _rows(t: torch.Tensor, what: str) -> int:
         raise KernelError(f"{what}: expected a 2-D tensor with contiguous rows, got shape {tuple(t.shape)} "
                           f"strides {t.stride()}")
     return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+class _NormFold(ctypes.Structure):
+    """HbNormFold of csrc/api.h."""
+    _fields_ = [("prep_w", ctypes.c_void_p), ("prep_offset", ctypes.c_float), ("prep_out", ctypes.c_void_p),
+                ("prep_ld", ctypes.c_longlong), ("prep_sumsq", ctypes.c_void_p), ("scale_sumsq", ctypes.c_void_p),
+                ("scale_parts", ctypes.c_int), ("scale_inv_size", ctypes.c_float), ("scale_eps", ctypes.c_float),
+                ("sumsq_ld", ctypes.c_int)]
+
+
+class PreparedNorm:
+    """A norm whose input the product in front has prepared: the buffer it was asked to fill
+    holds ``x * (offset + weight)`` without the per-token factor ``rsqrt(mean(x^2) + eps)``, and
+    ``sumsq[token, :parts]`` add up to the token's sum of squares.  The product that reads the
+    buffer multiplies its rows by the factor (``Ops.linear(..., scale=...)``)."""
+
+    def __init__(self, sumsq: torch.Tensor, parts: int, size: int, eps: float):
+        self.sumsq, self.parts, self.size, self.eps = sumsq, int(parts), int(size), float(eps)
 
 
 class PackedWeight:
@@ -195,6 +215,9 @@ class Ops:
         self.launches = 0  # kernels launched through this object (a claim bench.py reports)
         self.use_tensor_cores = True   # tests switch this off to compare the two matrix-product kernels
         self.use_pair_gemm = True      # many-token products on CTA pairs (cta_group::2)
+        # few-token steps: a norm between two products is folded into them (HILBERT_B200_FOLD_NORMS=0: norm kernels)
+        self.fold_norms = os.environ.get("HILBERT_B200_FOLD_NORMS", "1") != "0"
+        self._sumsq = None             # [FOLD_MAX_TOKENS, slots]: the partial sums of squares of a folded norm
         # weights as contiguous tiles (PackedWeight); HILBERT_B200_PACK=0 keeps them row-major
         self.use_packed_weights = os.environ.get("HILBERT_B200_PACK", "1") != "0"
         # device status words (csrc/common.cuh): a kernel that meets a fault notes the first one of
@@ -405,12 +428,12 @@ class Ops:
 
     SCHEDULES = {None: 0, "auto": 0, "tiles": 1, "stream_k": 2, "cut_first": 3}
 
-    def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None) -> None:
+    def _gemm_tc(self, a, w, out, mode: int, N: int, up_row0: int = 0, schedule=None, fold=None) -> None:
         M, K = a.shape
         packed = 1 if isinstance(w, PackedWeight) else 0
         ldw = 64 if packed else _rows(w, "linear weight")
-        if schedule == "pairs" or (schedule is None and self.use_pair_gemm and self.lib.hb_gemm_tc2_wanted(M, N, K)
-                                   and not (mode == 3 and N % 8)):
+        if fold is None and (schedule == "pairs" or (schedule is None and self.use_pair_gemm and self.lib.hb_gemm_tc2_wanted(M, N, K)
+                                                     and not (mode == 3 and N % 8))):
             # many tokens: CTA pairs (cta_group::2) on 256 x 256 tiles
             self._call("hb_gemm_tc2", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), ldw, w.shape[0], out.data_ptr(),
                        _rows(out, "linear output"), M, N, K, mode, up_row0, self.error_flag.data_ptr(), packed, self._stream())
@@ -425,15 +448,65 @@ class Ops:
         if tiles > self._splitk_counters.numel():
             self._retired.append(self._splitk_counters)
             self._splitk_counters = torch.zeros(tiles, dtype=torch.int32, device=self.device)
-        self._call("hb_gemm_tc", a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), ldw,
-                   w.shape[0], out.data_ptr(), _rows(out, "linear output"), M, N, K, mode, up_row0, sched,
-                   self._splitk_partials.data_ptr(), self._splitk_partials.numel(), self._splitk_counters.data_ptr(),
-                   self._splitk_counters.numel(), self.error_flag.data_ptr(), packed, self._stream())
+        args = (a.data_ptr(), _rows(a, "linear input"), w.data_ptr(), ldw,
+                w.shape[0], out.data_ptr(), _rows(out, "linear output"), M, N, K, mode, up_row0, sched,
+                self._splitk_partials.data_ptr(), self._splitk_partials.numel(), self._splitk_counters.data_ptr(),
+                self._splitk_counters.numel(), self.error_flag.data_ptr(), packed)
+        if fold is None:
+            self._call("hb_gemm_tc", *args, self._stream())
+        else:
+            self._call("hb_gemm_tc_fold", *args, ctypes.byref(fold), self._stream())    # the library copies the values
         self.launches += 1
 
-    def linear(self, a, w, out, accumulate: bool = False, schedule=None) -> None:
+    # ------------------------------------------------------------------ a norm folded into the products around it
+    FOLD_MAX_TOKENS = 16           # TC_SCALE_ROWS of csrc/tcgen05.cuh: beyond, norm kernels are faster
+
+    def can_fold_norm(self, tokens: int, size: int, dtype: torch.dtype) -> bool:
+        """Whether a step of ``tokens`` tokens may fold a norm over vectors of ``size`` into the
+        products around it: few tokens (the few-token tensor-core kernel), bfloat16 activations."""
+        return bool(self.fold_norms and self.use_tensor_cores and dtype == torch.bfloat16 and 0 < tokens <= self.FOLD_MAX_TOKENS
+                    and size % 8 == 0)
+
+    def _sumsq_buffer(self, size: int) -> torch.Tensor:
+        ld = (-(-size // 32) + 3) // 4 * 4
+        if self._sumsq is None or self._sumsq.shape[1] < ld:
+            if self._sumsq is not None:
+                self._retired.append(self._sumsq)            # a captured graph may still write there
+            self._sumsq = torch.zeros(self.FOLD_MAX_TOKENS, ld, dtype=torch.float32, device=self.device)
+        return self._sumsq
+
+    def _prepare_fold(self, out, prepare) -> Optional[_NormFold]:
+        """The producer's half of HbNormFold, or None when this product cannot prepare the norm."""
+        weight, offset, eps, h_out = prepare
+        M, N = out.shape
+        if not (self.can_fold_norm(M, N, h_out.dtype) and out.dtype == torch.float32 and out.data_ptr() % 16 == 0
+                and _rows(out, "linear output") % 4 == 0 and weight.dtype == torch.float32 and weight.numel() == N
+                and weight.data_ptr() % 16 == 0 and tuple(h_out.shape) == (M, N) and h_out.data_ptr() % 8 == 0
+                and _rows(h_out, "norm output") % 4 == 0):
+            return None
+        sumsq = self._sumsq_buffer(N)
+        fold = _NormFold()
+        fold.prep_w, fold.prep_offset, fold.prep_out = weight.data_ptr(), float(offset), h_out.data_ptr()
+        fold.prep_ld, fold.prep_sumsq, fold.sumsq_ld = _rows(h_out, "norm output"), sumsq.data_ptr(), sumsq.shape[1]
+        return fold
+
+    def _scale_fold(self, scale: PreparedNorm, tokens: int) -> _NormFold:
+        if tokens > self.FOLD_MAX_TOKENS:
+            raise KernelError(f"a prepared norm serves up to {self.FOLD_MAX_TOKENS} tokens, not {tokens}")
+        fold = _NormFold()
+        fold.scale_sumsq, fold.scale_parts, fold.sumsq_ld = scale.sumsq.data_ptr(), scale.parts, scale.sumsq.shape[1]
+        fold.scale_inv_size, fold.scale_eps = 1.0 / scale.size, scale.eps
+        return fold
+
+    def linear(self, a, w, out, accumulate: bool = False, schedule=None, prepare=None, scale: Optional[PreparedNorm] = None):
         """``out[M,N] (+)= a[M,K] @ w[N,K]^T`` with float32 accumulation.  ``schedule`` forces
-        the tensor-core kernel's work split ("tiles" or "stream_k"; default: by shape)."""
+        the tensor-core kernel's work split ("tiles" or "stream_k"; default: by shape).
+
+        A norm folded into the products around it (few tokens, bfloat16): with ``accumulate`` and
+        ``prepare = (norm weight, offset, eps, buffer)`` the product also fills ``buffer`` with
+        ``out * (offset + weight)`` and returns a ``PreparedNorm`` (None when it cannot: the
+        caller then runs the norm).  ``scale``: ``a`` is such a buffer; the rows of the result are
+        multiplied by the norm's per-token factor."""
         self._dev(a, w, out)
         M, K = a.shape
         N = w.shape[0]
@@ -443,8 +516,19 @@ class Ops:
             raise KernelError("linear: a [gate; up] matrix stored in bands is an operand of linear_swiglu only")
         if self._tensor_core_operands(a, w) and (out.dtype == torch.float32 or not accumulate):
             mode = 2 if accumulate else (1 if out.dtype == torch.float32 else 0)
-            self._gemm_tc(a, w, out, mode, N, 0, schedule)
-            return
+            fold = None
+            if prepare is not None and accumulate and schedule != "pairs":
+                fold = self._prepare_fold(out, prepare)
+            if scale is not None:
+                if accumulate:
+                    raise KernelError("linear: the product that adds to the residual does not scale its rows")
+                fold = self._scale_fold(scale, M)
+            self._gemm_tc(a, w, out, mode, N, 0, schedule, fold=fold)
+            if fold is not None and scale is None:
+                return PreparedNorm(self._sumsq, -(-N // 32), N, prepare[2])
+            return None
+        if scale is not None:
+            raise KernelError("linear: operands that the tensor-core product refuses cannot take a prepared norm")
         if isinstance(w, PackedWeight):
             w = w.unpacked()           # not a product path: only operands the tensor-core kernels refuse get here
         self._call("hb_gemm_general", a.data_ptr(), _code(a), _rows(a, "linear input"), w.data_ptr(), _code(w),
@@ -452,8 +536,8 @@ class Ops:
                    1 if accumulate else 0, self._stream())
         self.launches += 1
 
-    def linear_swiglu(self, h, w_gate_up, act, workspace, cap: int, schedule=None) -> None:
-        """``act = silu(h Wg^T) * (h Wu^T)`` with ``w_gate_up = [Wg; Wu]``."""
+    def linear_swiglu(self, h, w_gate_up, act, workspace, cap: int, schedule=None, scale: Optional[PreparedNorm] = None) -> None:
+        """``act = silu(h Wg^T) * (h Wu^T)`` with ``w_gate_up = [Wg; Wu]``; ``scale`` as in ``linear``."""
         T = h.shape[0]
         inter = act.shape[1]
         if w_gate_up.shape[0] != 2 * inter or act.shape[0] != T:
@@ -461,8 +545,11 @@ class Ops:
         if (self._tensor_core_operands(h, w_gate_up) and act.dtype == torch.bfloat16 and act.data_ptr() % 16 == 0
                 and _rows(act, "swiglu output") % 8 == 0):
             bands = isinstance(w_gate_up, PackedWeight) and w_gate_up.gate_up_bands
-            self._gemm_tc(h, w_gate_up, act, 3, inter, up_row0=-1 if bands else inter, schedule=schedule)
+            self._gemm_tc(h, w_gate_up, act, 3, inter, up_row0=-1 if bands else inter, schedule=schedule,
+                          fold=self._scale_fold(scale, T) if scale is not None else None)
             return
+        if scale is not None:
+            raise KernelError("linear_swiglu: operands that the tensor-core product refuses cannot take a prepared norm")
         if isinstance(w_gate_up, PackedWeight):
             w_gate_up = w_gate_up.unpacked()
         gu = workspace.buffer("swiglu.gate_up", (cap, 2 * inter), torch.float32 if act.dtype == torch.float32

@@ -64,17 +64,19 @@ class Attention(Mixer):
     def cache_need(self) -> CacheNeed:
         return CacheNeed(self.kv_heads, self.head_dim, self.window)
 
-    def forward(self, h, residual, step, cache, state, append: bool) -> None:
+    folds_norms = True
+
+    def forward(self, h, residual, step, cache, state, append: bool, prepared=None, prepare=None):
         ops, ws, T = self.ctx.ops, self.ctx.workspace, step.num_tokens
         cap = self.ctx.max_step_tokens
         width = self.q_width + 2 * self.kv_width
         qkv = ws.buffer("attention.qkv", (cap, width), self.ctx.dtype)[:T]
         if append:
-            ops.linear(h, self.w_qkv, qkv)
+            ops.linear(h, self.w_qkv, qkv, scale=prepared)
         else:
             # a layer that reads another layer's cache needs its queries only
             w_q = self.w_qkv.first_rows(self.q_width) if hasattr(self.w_qkv, "first_rows") else self.w_qkv[: self.q_width]
-            ops.linear(h, w_q, qkv[:, : self.q_width])
+            ops.linear(h, w_q, qkv[:, : self.q_width], scale=prepared)
         # positions: a table of rotations that the kernels apply, or the part turns q and k itself
         table, rot = None, 0
         fusable = self.fuse_decode
@@ -95,4 +97,4 @@ class Attention(Mixer):
         else:
             ops.rope_kv_append(qkv, table, rot, self.heads, self.kv_heads, self.head_dim, cache, step, append)
             ops.attention(qkv, self.heads, self.kv_heads, self.head_dim, cache, step, attn, self.scale, self.window)
-        ops.linear(attn, self.w_o, residual, accumulate=True)
+        return ops.linear(attn, self.w_o, residual, accumulate=True, prepare=prepare)

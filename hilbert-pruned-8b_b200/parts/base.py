@@ -105,18 +105,35 @@ class Part:
 
 
 class Mixer(Part):
+    """Reads the normed input ``h``, adds its result to the 32-bit ``residual``.
+
+    A part with ``folds_norms = True`` also takes two keyword arguments, by which a block folds
+    the norms around it into its matrix products for steps of few tokens (no norm kernel):
+    ``prepared`` (a ``kernels.ops.PreparedNorm``: ``h`` holds the norm's input times the norm's
+    weight WITHOUT the per-token factor, which the part's first product applies to its rows),
+    and ``prepare`` (what ``Norm.fold_request`` returned for the norm that reads ``residual``
+    next: the part's last product fills that norm's buffer).  ``forward`` then returns the
+    ``PreparedNorm`` for the next reader, or None when it prepared nothing (the block runs the
+    norm).  Parts without the attribute are called without the two arguments."""
+
+    folds_norms = False
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
     def state_need(self) -> Optional[StateNeed]:
         return None
 
-    def forward(self, h, residual, step, cache, state, append: bool) -> None:
+    def forward(self, h, residual, step, cache, state, append: bool):
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    def forward(self, h, residual, step) -> None:
+    """As ``Mixer``: reads ``h``, adds to ``residual``; ``folds_norms`` as there."""
+
+    folds_norms = False
+
+    def forward(self, h, residual, step):
         raise NotImplementedError
 
 
@@ -125,6 +142,12 @@ class Norm(Part):
 
     def forward(self, x, out, rows=None) -> None:
         raise NotImplementedError
+
+    def fold_request(self, out):
+        """What the product that writes this norm's input needs in order to prepare it
+        (``Ops.linear(..., prepare=...)``): ``(weight, offset, eps, out)`` for a norm of the form
+        ``x * rsqrt(mean(x^2) + eps) * (offset + weight)``; None: the norm cannot be folded."""
+        return None
 
 
 class PositionEncoding(Part):

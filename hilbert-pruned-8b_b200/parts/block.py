@@ -43,7 +43,19 @@ class Block:
         mixer = self.parts.get("mixer")
         return mixer.state_need() if mixer is not None else None
 
-    def forward(self, x, step, cache, state, append: bool) -> None:
+    # A block with ``folds_norms = True`` takes two more keyword arguments and returns a value, by
+    # which norms at the seam between two blocks are folded into the products around them (see
+    # ``parts.base.Mixer``): ``prepared`` is what the block in front returned (None: nothing
+    # prepared, the block runs its first norm), ``prepare_next`` what the next block's
+    # ``fold_request`` said (None: nobody asks).  Other blocks are called without them.
+    folds_norms = False
+
+    def fold_request(self, step):
+        """What the block in front has to prepare so that this block need not run its first
+        norm (``Norm.fold_request`` of that norm, on the buffer this block reads), or None."""
+        return None
+
+    def forward(self, x, step, cache, state, append: bool):
         raise NotImplementedError
 
 
@@ -56,10 +68,40 @@ class PreNormBlock(Block):
         self.mixer_norm, self.mixer = self.parts["mixer_norm"], self.parts["mixer"]
         self.feed_forward_norm, self.feed_forward = self.parts["feed_forward_norm"], self.parts["feed_forward"]
 
-    def forward(self, x, step, cache, state, append: bool) -> None:
-        ws, T = self.ctx.workspace, step.num_tokens
-        h = ws.buffer("block.h", (self.ctx.max_step_tokens, x.shape[1]), self.ctx.dtype)[:T]
-        self.mixer_norm.forward(x, h)
-        self.mixer.forward(h, x, step, cache, state, append)
-        self.feed_forward_norm.forward(x, h)
+    folds_norms = True
+
+    def _normed(self, step, size: int):
+        """The buffer the norms write and the mixer and the feed-forward read."""
+        return self.ctx.workspace.buffer("block.h", (self.ctx.max_step_tokens, size), self.ctx.dtype)[:step.num_tokens]
+
+    def _may_fold(self, step, size: int) -> bool:
+        ops = self.ctx.ops
+        return ops is not None and hasattr(ops, "can_fold_norm") and ops.can_fold_norm(step.num_tokens, size, self.ctx.dtype)
+
+    def fold_request(self, step):
+        # the mixer must be able to apply the prepared norm's factor; the norm says how wide the residual stream is
+        size = getattr(self.mixer_norm, "size", None)
+        if not getattr(self.mixer, "folds_norms", False) or size is None or not self._may_fold(step, size):
+            return None
+        return self.mixer_norm.fold_request(self._normed(step, size))
+
+    def forward(self, x, step, cache, state, append: bool, prepared=None, prepare_next=None):
+        h = self._normed(step, x.shape[1])
+        fold = self._may_fold(step, x.shape[1])
+        mixer_folds, ff_folds = getattr(self.mixer, "folds_norms", False), getattr(self.feed_forward, "folds_norms", False)
+        # x += mixer(norm(x)); the mixer's last product prepares the next norm if the feed-forward can use it
+        if prepared is None:
+            self.mixer_norm.forward(x, h)
+        if mixer_folds:
+            request = self.feed_forward_norm.fold_request(h) if fold and ff_folds else None
+            prepared = self.mixer.forward(h, x, step, cache, state, append, prepared=prepared, prepare=request)
+        else:
+            self.mixer.forward(h, x, step, cache, state, append)
+            prepared = None
+        # x += feed_forward(norm(x)); its last product prepares the next block's first norm if that block asked
+        if prepared is None:
+            self.feed_forward_norm.forward(x, h)
+        if ff_folds:
+            return self.feed_forward.forward(h, x, step, prepared=prepared, prepare=prepare_next if fold else None)
         self.feed_forward.forward(h, x, step)
+        return None

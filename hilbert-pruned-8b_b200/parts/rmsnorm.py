@@ -36,3 +36,6 @@ class RMSNorm(Norm):
     def forward(self, x, out, rows=None) -> None:
         """``out[i] = norm(x[rows[i]])`` (``rows`` None: every row of ``x``)."""
         self.ctx.ops.rmsnorm(x, self.weight, self.eps, self.offset, out, rows)
+
+    def fold_request(self, out):
+        return (self.weight, self.offset, self.eps, out)

@@ -40,9 +40,11 @@ class SwiGLU(FeedForward):
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
 
-    def forward(self, h, residual, step) -> None:
+    folds_norms = True
+
+    def forward(self, h, residual, step, prepared=None, prepare=None):
         ops, ws, T = self.ctx.ops, self.ctx.workspace, step.num_tokens
         cap = self.ctx.max_step_tokens
         act = ws.buffer("swiglu.act", (cap, self.inter), self.ctx.dtype)[:T]
-        ops.linear_swiglu(h, self.w_gate_up, act, ws, cap)
-        ops.linear(act, self.w_down, residual, accumulate=True)
+        ops.linear_swiglu(h, self.w_gate_up, act, ws, cap, scale=prepared)
+        return ops.linear(act, self.w_down, residual, accumulate=True, prepare=prepare)

@@ -125,6 +125,38 @@ def test_other_arrangements_of_decode_attention_in_the_engine(model_folders, mod
     tt.compare(got, tt.plain_logits(_plain(model_folders[model], "bfloat16"), reqs), "bfloat16", f"decode attention fuse={fuse} inside={inside}")
 
 
+@pytest.mark.parametrize("model", ["strong_b", "strong_d"])
+def test_norms_folded_into_the_products_of_few_token_steps(model_folders, model):
+    """Steps of up to 16 tokens fold every norm between two products into them (the product that
+    adds to the residual prepares the next norm's input, the product that reads it applies the
+    per-token factor): only the first layer's first norm and the final norm run as kernels.  The
+    logits are the plain model's either way, in steps of few tokens, in prompts, and when the two
+    alternate (a prompt of 70 tokens, then single tokens; three sequences of unequal lengths)."""
+    require_gpu()
+    reqs = _requests(model, [70, 12, 130], seed=660)
+    steps, peak = tt.trace_batches([{rid: (t, 3 + 9 * i) for i, (rid, t) in enumerate(reqs.items())}])
+    want = tt.plain_logits(_plain(model_folders[model], "bfloat16"), reqs)
+    layers = {"strong_b": TINY_B, "strong_d": TINY_D}[model]["num_hidden_layers"]
+    for fold in (True, False):
+        eng = _engine(model_folders[model], "bfloat16", peak)
+        ops = eng.ctx.ops
+        ops.fold_norms = fold
+        ops.call_log = []
+        got = tt.run_in_process(eng, steps)
+        log, ops.call_log = ops.call_log, None
+        tt.compare(got, want, "bfloat16", f"norms folded={fold}")
+        assert ("hb_gemm_tc_fold" in log) == fold
+        if fold:
+            # The prompts' step runs every norm; a decode step (up to three tokens) the first layer's first
+            # one and the final one.  (Replayed graphs do not pass through the log: it holds the prompts'
+            # step and the decode steps that were captured, one per batch size and page-table width.)
+            decode_steps = sum(1 for s in steps if all(len(e["tokens"]) == 1 for e in s["entries"]))
+            assert decode_steps > 20
+            logged_decode = log.count("hb_gemm_tc_fold") // (2 * (2 * layers - 1))
+            assert logged_decode >= 1 and log.count("hb_gemm_tc_fold") == logged_decode * 2 * (2 * layers - 1)
+            assert log.count("hb_rmsnorm") == (2 * layers + 1) * (len(steps) - decode_steps) + 2 * logged_decode
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("model", ["strong_c", "strong_d"])
 def test_hundreds_of_keys_through_the_tensor_core_attention(model_folders, model, dtype):

@@ -331,6 +331,74 @@ def test_gemm_tensor_core_cluster_split(ops, M, N, K):
         assert _rel(act, g / (1 + torch.exp(-g)) * u) < 2 ** -7
 
 
+@pytest.mark.parametrize("schedule", [None, "tiles", "stream_k", "cut_first"])
+@pytest.mark.parametrize("M,H,K,I", [(8, 4096, 4096, 1024), (1, 2048, 8192, 512), (16, 264, 520, 192), (13, 3072, 1024, 256),
+                                     (16, 2048, 2048, 640), (5, 1000, 320, 128)])
+def test_norm_folded_into_the_products_around_it(ops, M, H, K, I, schedule):
+    """Few tokens: the product that adds to the residual stream x also writes bf16(x * (offset + g))
+    and partial sums of squares; the products that read that buffer multiply their rows by
+    rsqrt(mean(x^2) + eps).  Against the plain statement in float64 and against the norm kernel
+    followed by the plain products, in every work split of both sides (whole tiles, cut tiles,
+    clusters) and every consumer epilogue (bfloat16, float32, SwiGLU)."""
+    from hilbert_pruned_8b_b200.engine.workspace import Workspace
+    torch.manual_seed(51)
+    eps, offset = 1e-5, 0.25
+    a = _bf(torch.randn(M, K, device=DEV))
+    w = _bf(torch.randn(H, K, device=DEV) / math.sqrt(K))
+    g = torch.randn(H, device=DEV) * 0.3 + 1.0
+    x0 = torch.randn(M, H, device=DEV) * 3.0
+    x0[M - 1] *= 40.0                                            # one token far larger than the others: the factor is per token
+    w2 = _bf(torch.randn(2 * I, H, device=DEV) / math.sqrt(H))
+    assert ops.can_fold_norm(M, H, torch.bfloat16)
+    x = x0.clone()
+    h = torch.full((M, H), 7.0, device=DEV, dtype=torch.bfloat16)
+    prepared = ops.linear(a, w, x, accumulate=True, schedule=schedule, prepare=(g, offset, eps, h))
+    ops.check_errors()
+    assert prepared is not None
+    # the residual itself: the same bits as without the preparation
+    x_plain = x0.clone()
+    ops.linear(a, w, x_plain, accumulate=True, schedule=schedule)
+    assert torch.equal(x, x_plain)
+    xd = x.double()
+    assert torch.equal(h, _bf(x * (offset + g)))                 # the buffer: x * (offset + g), rounded once
+    sums = prepared.sumsq[:M, :prepared.parts].double().sum(dim=1)
+    assert ((sums - (xd * xd).sum(dim=1)).abs() / (xd * xd).sum(dim=1)).max() < 1e-6
+    s = torch.rsqrt((xd * xd).mean(dim=1, keepdim=True) + eps)
+    ref = (h.double() @ w2.double().t()) * s
+    ws = Workspace(torch.device(DEV))
+    for sched2 in (None, "tiles", "stream_k"):
+        for dtype, tol in ((torch.bfloat16, 2 ** -8), (torch.float32, 2e-6 * math.sqrt(H))):
+            y = torch.empty(M, 2 * I, device=DEV, dtype=dtype)
+            ops.linear(h, w2, y, schedule=sched2, scale=prepared)
+            ops.check_errors()
+            assert _rel(y, ref) < tol, (sched2, dtype)
+            worst = ((y.double() - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max()
+            assert worst < 4 * tol, f"a token's rows are off by {float(worst):.2e} of its own scale ({sched2}, {dtype})"
+        act = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+        ops.linear_swiglu(h, w2, act, ws, M, schedule=sched2, scale=prepared)
+        ops.check_errors()
+        gate, up = ref[:, :I], ref[:, I:]
+        want = gate / (1 + torch.exp(-gate)) * up
+        assert ((act.double() - want).abs().amax(dim=1) / want.abs().amax(dim=1)).max() < 2 ** -6, sched2
+    # against the norm kernel + plain products: the same up to the place of one rounding (bf16(x g s) there,
+    # bf16(x g) s here).  Two independent bfloat16 roundings of every element of a row of H terms differ,
+    # per output, by about 2^-9 of the row's scale; the largest of M * 2I such differences, as a fraction of
+    # the row's largest output, comes to 0.0027-0.0037 at these sizes when both sides are computed in float64.
+    hn = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
+    ops.rmsnorm(x, g, eps, offset, hn)
+    y1, y2 = torch.empty(M, 2 * I, device=DEV), torch.empty(M, 2 * I, device=DEV)
+    ops.linear(hn, w2, y1)
+    ops.linear(h, w2, y2, scale=prepared)
+    assert ((y1 - y2).abs().amax(dim=1) / y1.abs().amax(dim=1)).max() < 2 ** -7
+    with pytest.raises(Exception, match="does not scale"):
+        ops.linear(a, w, x, accumulate=True, scale=prepared)
+    # more tokens than the fold serves, or another dtype: the product says so and prepares nothing
+    more = ops.FOLD_MAX_TOKENS + 1
+    big = torch.zeros(more, H, device=DEV)
+    assert ops.linear(_bf(torch.randn(more, K, device=DEV)), w, big, accumulate=True,
+                      prepare=(g, offset, eps, torch.empty(more, H, device=DEV, dtype=torch.bfloat16))) is None
+
+
 @pytest.mark.parametrize("M,N,K", [(8, 512, 1024), (5, 100, 416), (64, 300, 2048), (16, 1000, 72), (600, 640, 520)])
 def test_gemm_tensor_core_packed_weights(ops, M, N, K):
     """A weight stored as contiguous 128 x 64 tiles gives bit for bit the results of the
