@@ -229,22 +229,22 @@ def _register_toy():
 
 
 class PlainToyHybrid(pl.PlainLlama):
-    def __init__(self, folder, decay):
-        super().__init__(folder)
+    def __init__(self, folder, decay, round_to=None):
+        super().__init__(folder, round_to=round_to)
         self.decay = decay
 
     def layer(self, x, i, positions):
         if i % 2:
             return super().layer(x, i, positions)
         c, w, p = self.cfg, self.w, f"{self.prefix}layers.{i}."
-        h = pl.rms_norm(x, w[p + "input_layernorm.weight"], c["rms_norm_eps"])
+        h = self.rnd(pl.rms_norm(x, w[p + "input_layernorm.weight"], c["rms_norm_eps"]))
         s = torch.zeros(x.shape[1], dtype=x.dtype)
         rows = []
         for t in range(x.shape[0]):
             s = s * self.decay + h[t]
             rows.append(s @ w[p + "toy.mix.weight"].t())
         x = x + torch.stack(rows)
-        h = pl.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["rms_norm_eps"])
+        h = self.rnd(pl.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["rms_norm_eps"]))
         return x + pl.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"],
                              self.rnd)
 
@@ -271,6 +271,17 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
             steps, _ = make(reqs)
             tt.compare(tt.run_in_process(eng, steps), ref, "float32", "toy hybrid")
         assert eng.cache.slots.num_held == 0
+        # In bfloat16 the steps of few tokens fold the norms into the products around them where both
+        # neighbours can: the toy mixer cannot (its block runs the norm kernels around it), the
+        # attention layers between the toy layers can, and the two kinds hand over at every seam.
+        eng16 = Engine.from_folder(folder, "bfloat16", max_tokens=1024)
+        ops = eng16.ctx.ops
+        ops.call_log = []
+        steps, _ = tt.trace_tail(reqs, 16)
+        got = tt.run_in_process(eng16, steps)
+        log, ops.call_log = ops.call_log, None
+        tt.compare(got, tt.plain_logits(PlainToyHybrid(folder, 0.75, round_to=torch.bfloat16), reqs), "bfloat16", "toy hybrid, folded norms")
+        assert "hb_gemm_tc_fold" in log and "hb_rmsnorm" in log
     finally:
         unregister_architecture(ToyConfig)
         MIXERS.unregister("toy_decay")
