@@ -24,6 +24,9 @@ What a part must provide:
   themselves), else ``apply(q, k, step)`` which turns them in place; see ``PositionEncoding``.
 * blocks (``parts/block.py``): ``ROLES``, ``named_parts()``, ``cache_need()``, ``state_need()``,
   ``forward(x, step, cache, state, append)``.
+* optional, ``folds_norms = True`` on mixers, feed-forwards and blocks: the norms between two
+  matrix products may be folded into them for steps of few tokens; see ``Mixer`` and
+  ``Norm.fold_request`` below and ``Block`` in ``parts/block.py``.
 * ``graph_safe`` (class attribute, default True): whether ``forward`` only enqueues work on
   the current stream, so that a decode step can be captured in a CUDA graph.
 """
