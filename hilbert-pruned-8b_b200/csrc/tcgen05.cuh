@@ -209,34 +209,41 @@ struct TcParams {
     float scale_inv_size, scale_eps;
 };
 
+// The most tokens of a product that serves a folded norm: token tiles of 16 and 32.  Measured per decode
+// step, folded against norm kernels: 8B sizes batch 1 -5.7 %, batch 8 -3.6 %, batch 24 -1.3 %, batch 32
+// -0.9 %, batch 48 and 64 +0.4 %; 3B sizes batch 16 -5.5 %, batch 32 -0.1 %, batch 64 +3.2 %; 1B sizes
+// batch 32 -1.0 %, batch 48 -1.4 %, batch 64 0: with 64 tokens the longer epilogues of the residual
+// products cost what the two kernels saved, or more.
+#define TC_SCALE_ROWS 32
+
 // The consumer's per-token factors for the tokens of a tile column block that starts at token 0
-// (folding is used with one token tile only).  Eight threads per token (TC_SCALE_ROWS = 16 tokens,
-// 128 epilogue threads): each adds every eighth group of four partial sums, the eight add up
-// through shuffles in a fixed order; all loads of a thread are in flight at once, so the factors
+// (folding is used with one token tile only).  128 / TC_SCALE_ROWS threads per token: each adds
+// its share of the groups of four partial sums, the threads of a token add up through shuffles
+// in a fixed order; all loads of a thread are in flight at once, so the factors
 // cost one or two round trips to L2, not one per four slots.  `srow` is shared memory of
 // TC_SCALE_ROWS floats.  All 128 epilogue threads call it once.
 __device__ __forceinline__ void tc_row_scales(const TcParams& p, float* srow, int et) {
     if (p.scale_sumsq == nullptr) return;
-    const int token = et >> 3, sub = et & 7;
+    constexpr int TPT = 128 / TC_SCALE_ROWS;           // threads per token
+    const int token = et / TPT, sub = et % TPT;
     float acc = 0.0f;
     if (token < p.M) {
         const float4* src = reinterpret_cast<const float4*>(p.scale_sumsq + (size_t)token * p.sumsq_ld);
         const int groups = p.scale_parts >> 2;
         float4 t[4];
 #pragma unroll 1
-        for (int i0 = sub; i0 < groups; i0 += 32) {
+        for (int i0 = sub; i0 < groups; i0 += 4 * TPT) {
 #pragma unroll
             for (int u = 0; u < 4; u++)
-                t[u] = i0 + 8 * u < groups ? __ldcg(src + i0 + 8 * u) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                t[u] = i0 + TPT * u < groups ? __ldcg(src + i0 + TPT * u) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
             for (int u = 0; u < 4; u++) acc += (t[u].x + t[u].y) + (t[u].z + t[u].w);
         }
         if (sub == 0)
             for (int i = p.scale_parts & ~3; i < p.scale_parts; i++) acc += __ldcg(p.scale_sumsq + (size_t)token * p.sumsq_ld + i);
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+#pragma unroll
+    for (int d = 1; d < TPT; d <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
     if (token < p.M && sub == 0) srow[token] = rsqrtf(acc * p.scale_inv_size + p.scale_eps);
     asm volatile("bar.sync 1, 128;" ::: "memory");
 }
@@ -257,11 +264,6 @@ __device__ __forceinline__ void tc_w_coords(const TcParams& p, int row, int kb, 
 }
 
 #define TC_XCHG_BYTES (2 * 16 * 64 * 4 + 2 * 16 * 64 * 2)
-// The most tokens of a product that serves a folded norm: the 16-token tile.  Measured per decode step,
-// folded against norm kernels: 8B sizes batch 1 -5.7 %, batch 8 -3.6 %, batch 16 -1.0 %, batch 32 -0.4 %,
-// batch 48 +0.4 %; 1B sizes batch 32 -0.5 %, batch 64 +2.4 %; 3B sizes batch 16 -4.5 %, batch 32 +2.2 %:
-// with more tokens the longer epilogues of the residual products cost more than the two kernels saved.
-#define TC_SCALE_ROWS 16
 
 // Epilogue of 16 token columns [m0 + c, m0 + c + 16) of a tile: v[j] is the accumulator of
 // weight row `row` (0..127, = TMEM lane) and token column c + j.  n0 is the first output

@@ -459,7 +459,7 @@ class Ops:
         self.launches += 1
 
     # ------------------------------------------------------------------ a norm folded into the products around it
-    FOLD_MAX_TOKENS = 16           # TC_SCALE_ROWS of csrc/tcgen05.cuh: beyond, norm kernels are faster
+    FOLD_MAX_TOKENS = 32           # TC_SCALE_ROWS of csrc/tcgen05.cuh: beyond, norm kernels are as fast or faster
 
     def can_fold_norm(self, tokens: int, size: int, dtype: torch.dtype) -> bool:
         """Whether a step of ``tokens`` tokens may fold a norm over vectors of ``size`` into the

@@ -127,7 +127,7 @@ def test_other_arrangements_of_decode_attention_in_the_engine(model_folders, mod
 
 @pytest.mark.parametrize("model", ["strong_b", "strong_d"])
 def test_norms_folded_into_the_products_of_few_token_steps(model_folders, model):
-    """Steps of up to 16 tokens fold every norm between two products into them (the product that
+    """Steps of up to 32 tokens fold every norm between two products into them (the product that
     adds to the residual prepares the next norm's input, the product that reads it applies the
     per-token factor): only the first layer's first norm and the final norm run as kernels.  The
     logits are the plain model's either way, in steps of few tokens, in prompts, and when the two

@@ -333,7 +333,7 @@ def test_gemm_tensor_core_cluster_split(ops, M, N, K):
 
 @pytest.mark.parametrize("schedule", [None, "tiles", "stream_k", "cut_first"])
 @pytest.mark.parametrize("M,H,K,I", [(8, 4096, 4096, 1024), (1, 2048, 8192, 512), (16, 264, 520, 192), (13, 3072, 1024, 256),
-                                     (16, 2048, 2048, 640), (5, 1000, 320, 128)])
+                                     (32, 2048, 2048, 640), (5, 1000, 320, 128), (23, 4096, 1024, 256)])
 def test_norm_folded_into_the_products_around_it(ops, M, H, K, I, schedule):
     """Few tokens: the product that adds to the residual stream x also writes bf16(x * (offset + g))
     and partial sums of squares; the products that read that buffer multiply their rows by
