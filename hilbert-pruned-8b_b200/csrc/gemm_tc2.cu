@@ -438,13 +438,21 @@ static int resident_pairs(int mode) {
 }
 extern "C" int hb_gemm_tc2_resident_pairs(int mode) { return resident_pairs(mode & 3); }
 
-// Whether the pair kernel should take a product: enough tokens to fill 256-token tiles.
-// Above 512 tokens.  Up to there a product has too few 256 x 256 tiles for 74 pairs (512 tokens x
-// 4096 features: 32) and the single-CTA kernel, which cuts K when tiles are few, is as fast or
-// faster: a prompt through 4 layers of the 8B sizes, single-CTA against pairs: 256 tokens 1.21
-// against 1.27 ms, 512 tokens 1.54 either way, 640 tokens 1.76 against 1.63, 768 tokens 1.82
-// against 1.70, 1024 tokens 2.38 against 1.94 ms.
-extern "C" int hb_gemm_tc2_wanted(int M, int N, int K) { return M > 512 && N >= 256 && K >= 64; }
+// Whether the pair kernel should take a product: from 256 tokens on, unless K is long and the tiles
+// are few (there the single-CTA kernel, which cuts K, is faster).  Measured per product, single-CTA
+// kernel / pairs, us.  8B sizes: q,k,v (K 4096) 256 tokens 34 / 32, 512 tokens 44 / 34; o (K 4096) 38 / 32,
+// 40 / 34; gate/up (K 4096) 83 / 69, 122 / 103; down (K 14336; 16 pair tiles per 256 tokens) 256 tokens
+// 65 / 77, 512 tokens 81 / 81, 640 tokens 107 / 83.  1B sizes at 384 tokens: q,k,v 26 / 21, o (16 tiles,
+// K 2048) 32 / 23, gate/up 50 / 40, down (K 8192, 16 tiles) 42 / 50, at 1024 tokens (32 tiles) 58 / 52.
+// 3B sizes, down (K 8192): 512 tokens (24 tiles) 48 / 50, 640 tokens (36 tiles) 54 / 52.  At 128 tokens
+// the single-CTA kernel wins everywhere.  A prompt through 4 layers of the 8B sizes, single-CTA only
+// against this rule: 256 tokens 1.22 / 1.14 ms, 384 tokens 1.51 / 1.36, 512 tokens 1.51 / 1.40 (with the
+// down projection on pairs at 512 tokens, 32 tiles: 1.44; hence 40 tiles).
+extern "C" int hb_gemm_tc2_wanted(int M, int N, int K) {
+    if (M < 256 || N < 256 || K < 64) return 0;
+    const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    return K <= 4096 || tiles >= 40;
+}
 
 // Arguments as hb_gemm_tc (no scratch: whole tiles only).
 extern "C" int hb_gemm_tc2(const void* a, long long lda, const void* w, long long ldw, long long w_rows, void* out,

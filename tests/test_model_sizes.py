@@ -44,7 +44,7 @@ def test_one_layer_at_real_sizes(size_folders, shape, dtype):
     require_gpu()
     from hilbert_pruned_8b_b200.engine.step import Engine
     vocab = SHAPES[shape]["vocab_size"]
-    lengths = [862, 102, 35]        # the prompts of one step: over 512 tokens, the CTA-pair product
+    lengths = [862, 102, 35]        # the prompts of one step: 999 tokens, the CTA-pair product
     toks = {f"r{i}": tt.random_tokens(n, vocab, 900 + i) for i, n in enumerate(lengths)}
     steps, peak = tt.trace_batches([{rid: (t, len(t) - 32) for rid, t in toks.items()}])
     eng = Engine.from_folder(size_folders[shape], dtype, max_tokens=peak)
